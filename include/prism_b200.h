@@ -1,0 +1,143 @@
+/*
+ * prism_b200 -- C ABI of the B200 (sm_100a) kernels that stand in for the
+ * three kernel families of the Prism evaluation harnesses.
+ *
+ * Every entry point is `extern "C"`, takes plain device pointers and sizes,
+ * enqueues its work on the given CUDA stream and returns immediately with a
+ * status code (0 = PRISM_B200_OK).  Nothing here calls exit()/abort(); no
+ * device code traps.  Device-side waits are bounded: a wait that runs out
+ * writes a code into a status word that prism_b200_last_error() reports after
+ * the stream has been synchronised.
+ *
+ * Ownership: the caller allocates and frees every device buffer, including
+ * the scan workspace.  The library owns only cached TMA tensor maps and one
+ * pinned status word per process.
+ *
+ * `stream` is a cudaStream_t passed as void* so that this header needs no
+ * CUDA include (NULL = the legacy default stream).
+ */
+#ifndef PRISM_B200_H
+#define PRISM_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes -------------------------------------------------------- */
+enum {
+    PRISM_B200_OK = 0,
+    PRISM_B200_ERR_INVALID_ARGUMENT = 1, /* null pointer, negative size, bad kernel id   */
+    PRISM_B200_ERR_UNSUPPORTED_SHAPE = 2,/* shape outside what the chosen kernel accepts  */
+    PRISM_B200_ERR_MISALIGNED = 3,       /* pointer not aligned for 16-byte accesses      */
+    PRISM_B200_ERR_CUDA = 4,             /* a CUDA runtime/driver call failed             */
+    PRISM_B200_ERR_DEVICE_TIMEOUT = 5,   /* a bounded device-side wait ran out            */
+    PRISM_B200_ERR_TOO_LARGE = 6         /* size beyond a stated maximum                  */
+};
+
+/* ---- library ------------------------------------------------------------- */
+
+/* Version as major*10000 + minor*100 + patch. */
+int prism_b200_version(void);
+
+/*
+ * Last error seen by this process.  `code` receives the most recent non-zero
+ * status returned by an entry point or raised by a kernel (device-side
+ * timeouts become visible once the stream is synchronised); `msg` receives a
+ * short text.  Returns the same code.  Either pointer may be NULL.
+ * Replaces the reference's `cudaCheck` -> `exit(EXIT_FAILURE)` policy
+ * (evals/4090_sgemm/runner.cu:16-22, evals/4090_scan/scan_harness.cuh:15-25).
+ */
+int prism_b200_last_error(int* code, char* msg, size_t len);
+
+/* Clears the sticky error state (host side and the device status word). */
+void prism_b200_clear_error(void);
+
+/* Number of kernels this library has launched since load (all entry points). */
+unsigned long long prism_b200_launch_count(void);
+
+/* ---- FP32 SGEMM: C = alpha * A * B + beta * C ----------------------------- */
+
+/*
+ * Replaces `run_my_kernel(int my_kernel_num, M, N, K, alpha, A, B, beta, C)`
+ * (evals/4090_sgemm/runner.cu:245-267, declared in runner.cuh:28-29).
+ * A is M x K, B is K x N, C is M x N, all row-major fp32 in device memory, C is
+ * updated in place.  kernel_id follows the evaluation harness:
+ *   1  one thread per C element              (generated/my_sgemm_kernel_1.cu)
+ *   2  32x32-tile thread remap, coalesced    (generated/my_sgemm_kernel_2.cu)
+ *   3  32x32 shared-memory tiles             (generated/sgemm_shared_mem_block.cu,
+ *                                             which evals/run_4090.sh:67-69 renames to kernel 3)
+ *   4  128x128x8 tiles, 8x8 register tile, 128-bit accesses
+ *                                            (generated/my_sgemm_kernel_4.cu)
+ *   5  warp-tiled 128x128 tile, 8x16 accumulators per thread; on B200 a
+ *      bulk-copy (TMA) staged, mbarrier-pipelined FFMA kernel
+ *                                            (generated/my_sgemm_kernel_5.cu)
+ *   6  register-tiled, scalar accesses       (generated/my_sgemm_kernel_3.cu,
+ *                                             emitted by the reference but never launched by its harness)
+ * Shapes: ids 1, 2 and 6 accept any positive M, N, K.  Ids 3, 4, 5 use their tiled
+ * kernels when the shape divides the tile (3: multiples of 32; 4: M, N multiples of
+ * 128, K of 8; 5: M, N multiples of 128, K of 32) and a bounds-checked tiled kernel
+ * otherwise, so no shape is rejected and no shape reads out of bounds.
+ * No TF32 and no tensor cores anywhere on this path.
+ */
+int prism_b200_sgemm(int kernel_id, int M, int N, int K, float alpha,
+                     const float* A, const float* B, float beta, float* C,
+                     void* stream);
+
+/* ---- uint32 inclusive scan (single pass, decoupled look-back) ------------- */
+
+/*
+ * Replaces `get_workspace_size(n)` (evals/4090_scan/main.cu:63-66).
+ * Bytes of device scratch prism_b200_scan needs for n elements.
+ */
+int prism_b200_scan_workspace_size(size_t n, size_t* bytes);
+
+/*
+ * Replaces `launch_scan(n, x, workspace)` (evals/4090_scan/main.cu:68-86).
+ * In-place inclusive prefix sum of n uint32 (wrap-around adds, bit-identical to
+ * int32).  Any n >= 0 is accepted (the reference needs n % 16384 == 0); n must
+ * be below 2^32.  x must be 16-byte aligned.  The workspace may hold anything on
+ * entry: it is re-armed on the stream before the kernel, as the reference does.
+ */
+int prism_b200_scan(size_t n, uint32_t* x, void* workspace, void* stream);
+
+/*
+ * Sharded scan helpers (no counterpart in the reference, which is single-GPU).
+ * A rank that owns the r-th contiguous chunk of a longer array
+ *   1. prism_b200_reduce_u32: total of its chunk -> *total (device),
+ *   2. exchanges totals with the other ranks (an all-gather of one word each),
+ *   3. prism_b200_scan_seeded: scans its chunk starting from
+ *      totals[0] + ... + totals[rank-1] (read on the device, wrap-around adds).
+ * prism_b200_scan_add_carry adds the same carry to an already scanned chunk
+ * (the two-pass form: local scan, exchange, carry add).
+ */
+int prism_b200_reduce_u32(size_t n, const uint32_t* x, uint32_t* total, void* stream);
+int prism_b200_scan_seeded(size_t n, uint32_t* x, void* workspace,
+                           const uint32_t* totals, int rank, void* stream);
+int prism_b200_scan_add_carry(size_t n, uint32_t* x, const uint32_t* totals,
+                              int rank, void* stream);
+
+/* ---- bf16 GEMM: C = A * B^T, fp32 accumulate ------------------------------ */
+
+/*
+ * Replaces `runmyh100(M, N, K, A, B, C, DB)` (evals/h100_bench/utils.cuh:504-533),
+ * the launcher of `cutlass_my_h100_match_no_tail`
+ * (generated/cutlass_my_h100_match_no_tail.cu:1-370).
+ * A is M x K and B is N x K, both K-major (row-major) bf16; C is M x N bf16 stored
+ * COLUMN-major, C[n * M + m], as the reference kernel writes it
+ * (generated/cutlass_my_h100_match_no_tail.cu:313,347-354).  fp32 accumulation,
+ * round-to-nearest-even on store.  Requires M % 128 == 0, N % 128 == 0, K % 64 == 0
+ * (the reference needs M % 2048 == 0, N % 2048 == 0, K % 256 == 0).
+ * Tensor maps are cached on (device, pointer, rows, K) so a new buffer never reuses a
+ * stale map (the reference caches on M alone, utils.cuh:512-518).
+ * bf16 values are passed as uint16_t bit patterns to keep this header free of CUDA types.
+ */
+int prism_b200_gemm_bf16(int M, int N, int K, const uint16_t* A, const uint16_t* B,
+                         uint16_t* C, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PRISM_B200_H */

@@ -1,0 +1,78 @@
+"""Builds the checkers under oracle/ -- TEST INFRASTRUCTURE ONLY.
+
+    python oracle/build_ref.py [--reference /path/to/prism]
+
+1. oracle/liboracle_cpu.so     the plain-C restatement (oracle_cpu.c), gcc + OpenMP.
+2. oracle/_ref/libref_cpu.so   the reference's own CPU scan loop (scan_harness.cuh) behind a C symbol.
+3. oracle/_ref/libprism_ref.so the reference's generated SGEMM and scan kernels with the harness launch
+                               geometry, compiled for sm_100 with the reference Makefile's flags
+                               (-O3 --use_fast_math -w; evals/4090_sgemm/Makefile:12-18, evals/4090_scan/Makefile:3-4).
+
+Steps 2 and 3 compile the reference's sources from where they lie (include path
+= the reference root); nothing is copied.  They are skipped when the reference
+tree is absent (e.g. on a GPU box, which uses the files built beforehand).
+The bf16 kernel is not built: wgmma does not assemble for sm_100.
+"""
+from __future__ import annotations
+
+import argparse
+import os
+import shutil
+import subprocess
+import sys
+from pathlib import Path
+
+HERE = Path(__file__).resolve().parent
+REF_OUT = HERE / "_ref"
+DEFAULT_REFERENCE = os.environ.get("PRISM_REFERENCE", "/root/reference")
+
+
+def _run(cmd: list[str]) -> None:
+    r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if r.returncode != 0:
+        sys.stdout.write(r.stdout)
+        raise RuntimeError("command failed: " + " ".join(cmd))
+
+
+def _newer(target: Path, deps: list[Path]) -> bool:
+    return target.exists() and all(target.stat().st_mtime >= d.stat().st_mtime for d in deps if d.exists())
+
+
+def build_oracle_c(force: bool = False) -> Path:
+    out = HERE / "liboracle_cpu.so"
+    src = HERE / "oracle_cpu.c"
+    if not force and _newer(out, [src]):
+        return out
+    _run(["gcc", "-O3", "-march=native", "-fopenmp", "-shared", "-fPIC", str(src), "-o", str(out)])
+    return out
+
+
+def build_reference(reference: str = DEFAULT_REFERENCE, force: bool = False) -> dict[str, Path] | None:
+    ref = Path(reference)
+    if not (ref / "generated" / "scan_kernel.cu").exists():
+        return None
+    REF_OUT.mkdir(exist_ok=True)
+    built = {}
+    cpu_out = REF_OUT / "libref_cpu.so"
+    cpu_src = HERE / "ref_cpu_shim.cpp"
+    if force or not _newer(cpu_out, [cpu_src]):
+        cuda_inc = Path(shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc").resolve().parent.parent / "include"
+        _run(["g++", "-O2", "-w", "-shared", "-fPIC", f"-I{ref}", f"-I{cuda_inc}", str(cpu_src), "-o", str(cpu_out)])
+    built["cpu"] = cpu_out
+    gpu_out = REF_OUT / "libprism_ref.so"
+    gpu_src = HERE / "ref_shim.cu"
+    if force or not _newer(gpu_out, [gpu_src]):
+        nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+        _run([nvcc, "-arch=sm_100", "-O3", "--use_fast_math", "-w", "-cudart", "static", "-shared", "-Xcompiler", "-fPIC",
+              f"-I{ref}", str(gpu_src), "-o", str(gpu_out)])
+    built["gpu"] = gpu_out
+    return built
+
+
+if __name__ == "__main__":
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--reference", default=DEFAULT_REFERENCE)
+    ap.add_argument("--force", action="store_true")
+    a = ap.parse_args()
+    print(build_oracle_c(a.force))
+    print(build_reference(a.reference, a.force) or "reference tree absent: oracle/_ref not (re)built")

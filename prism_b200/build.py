@@ -1,0 +1,92 @@
+"""In-tree build of libprism_b200.so (sm_100a) with nvcc.
+
+    python -m prism_b200.build [--force] [--verbose]
+
+The library is written next to this file so that it travels with the source
+tree; nothing is installed into site-packages and nothing is cached elsewhere.
+nvcc cross-compiles without a GPU.
+"""
+from __future__ import annotations
+
+import argparse
+import os
+import shutil
+import subprocess
+import sys
+from pathlib import Path
+
+PKG_DIR = Path(__file__).resolve().parent
+CSRC = PKG_DIR / "csrc"
+LIB_PATH = PKG_DIR / "libprism_b200.so"
+SOURCES = ["api.cu", "scan.cu", "sgemm.cu", "gemm_bf16.cu"]
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a",
+    "-O3", "-std=c++17", "-lineinfo",
+    "-Xcompiler", "-fPIC",
+    "-cudart", "static",
+]
+
+
+def _nvcc() -> str:
+    exe = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(exe):
+        raise RuntimeError("nvcc not found; libprism_b200.so cannot be built")
+    return exe
+
+
+def sources() -> list[Path]:
+    return [CSRC / s for s in SOURCES if (CSRC / s).exists()]
+
+
+def _stale() -> bool:
+    if not LIB_PATH.exists():
+        return True
+    t = LIB_PATH.stat().st_mtime
+    deps = list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + [PKG_DIR.parent / "include" / "prism_b200.h"]
+    return any(d.stat().st_mtime > t for d in deps if d.exists())
+
+
+def build_library(force: bool = False, verbose: bool = False) -> Path:
+    """Compile every kernel source into one shared library; returns its path."""
+    if not force and not _stale():
+        return LIB_PATH
+    objdir = PKG_DIR / "build"
+    objdir.mkdir(exist_ok=True)
+    nvcc = _nvcc()
+    objs = []
+    procs = []
+    for src in sources():
+        obj = objdir / (src.stem + ".o")
+        cmd = [nvcc, *NVCC_FLAGS, "-c", str(src), "-o", str(obj)]
+        if verbose:
+            cmd.insert(1, "-Xptxas=-v")
+            print(" ".join(cmd), flush=True)
+        procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
+        objs.append(str(obj))
+    failed = False
+    for src, p in procs:
+        out, _ = p.communicate()
+        if verbose or p.returncode != 0:
+            sys.stdout.write(out)
+        if p.returncode != 0:
+            failed = True
+            print(f"nvcc failed on {src.name}", file=sys.stderr)
+    if failed:
+        raise RuntimeError("libprism_b200.so: compilation failed")
+    tmp = LIB_PATH.with_suffix(".so.tmp")
+    link = [nvcc, *NVCC_FLAGS, "-shared", *objs, "-o", str(tmp)]
+    r = subprocess.run(link, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if r.returncode != 0:
+        sys.stdout.write(r.stdout)
+        raise RuntimeError("libprism_b200.so: link failed")
+    os.replace(tmp, LIB_PATH)
+    return LIB_PATH
+
+
+if __name__ == "__main__":
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--force", action="store_true")
+    ap.add_argument("--verbose", action="store_true")
+    a = ap.parse_args()
+    print(build_library(force=a.force, verbose=a.verbose))

@@ -1,0 +1,453 @@
+// bf16 GEMM for B200: C = A * B^T with fp32 accumulation on the 5th-generation
+// tensor cores (tcgen05.mma, accumulators in tensor memory), operands staged by
+// TMA, persistent CTAs.
+//
+// What it stands in for: `cutlass_my_h100_match_no_tail`
+// (generated/cutlass_my_h100_match_no_tail.cu:1-370), a Hopper kernel built on
+// wgmma/setmaxnreg that does not assemble for sm_100a, and its launcher
+// `runmyh100` (evals/h100_bench/utils.cuh:504-533).  Same data contract:
+//   A  M x K  bf16, K contiguous         B  N x K  bf16, K contiguous
+//   C  M x N  bf16, COLUMN-major: C[n * M + m]   (cutlass_my_h100_match_no_tail.cu:313,347-354)
+// and the same kernel parameter list (M, N, K, C, tensorMapA, tensorMapB).
+//
+// Design.
+//   * Column-major C is row-major C^T = B * A^T, so the kernel computes C^T: the
+//     rows of B index the 128 TMEM lanes of an accumulator and the rows of A index
+//     its columns.  A thread that reads one TMEM lane then holds consecutive m of a
+//     single n, which are consecutive in memory, so the epilogue writes 16-byte
+//     vectors straight from registers with no transpose.
+//   * CTA tile: 128 (n) x BLOCK_Q (m, 256 or 128) x 64 (k).  One tcgen05.mma covers
+//     128 x BLOCK_Q x 16; four of them consume a stage.  Operands sit in shared
+//     memory in the 128-byte-swizzled K-major layout that TMA writes and the MMA
+//     descriptors name (8-row groups 1024 B apart).
+//   * Warp roles: warp 0 issues TMA loads, warp 1 owns tensor memory and issues the
+//     MMAs, warps 2-5 drain accumulators (each warp can reach one 32-lane quarter
+//     of tensor memory, picked by warp index mod 4).
+//   * Two accumulators (2 x BLOCK_Q columns of the 512) alternate, so the epilogue
+//     of one tile overlaps the main loop of the next.
+//   * Four mbarrier rings: smem full/empty per stage, accumulator full/empty.
+//     tcgen05.commit makes the MMA completion arrive on a barrier.  Every wait is
+//     bounded; a wait that runs out raises DEV_GEMM_PIPE_TIMEOUT, all roles
+//     unwind, tensor memory is freed and the kernel returns.
+//   * Tiles are dealt round-robin to the resident CTAs in an order that walks 8
+//     m-tiles for each n-tile, so a wave of CTAs shares operand rows in L2.
+#include "common.cuh"
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+
+#include <mutex>
+#include <unordered_map>
+
+namespace prism_b200 {
+
+namespace g16 {
+constexpr int BLOCK_P = 128;     // rows of B (n) per tile -> TMEM lanes
+constexpr int BLOCK_K = 64;      // 64 bf16 = 128 bytes = one swizzle span
+constexpr int UMMA_K = 16;
+constexpr int THREADS = 192;
+constexpr int EPI_WARPS = 4;
+constexpr int GROUP_M = 8;       // m-tiles walked per n-tile
+constexpr int TMEM_COLS = 512;
+
+template <int BLOCK_Q>
+struct Cfg {
+    static constexpr int STAGES = BLOCK_Q == 256 ? 4 : 6;
+    static constexpr uint32_t P_BYTES = BLOCK_P * BLOCK_K * 2;
+    static constexpr uint32_t Q_BYTES = BLOCK_Q * BLOCK_K * 2;
+    static constexpr uint32_t STAGE_BYTES = P_BYTES + Q_BYTES;
+    // 1024 B of slack to align the ring, then barriers and the TMEM slot.
+    static constexpr size_t SMEM_BYTES = 1024 + static_cast<size_t>(STAGES) * STAGE_BYTES + (2 * STAGES + 4) * 8 + 16;
+};
+
+// Instruction descriptor for kind::f16: D = fp32, A = B = bf16, both K-major,
+// N at bits 17-22 (N >> 3), M at bits 24-28 (M >> 4).
+__host__ __device__ constexpr uint32_t instr_desc(int umma_m, int umma_n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(umma_n >> 3) << 17) |
+           (static_cast<uint32_t>(umma_m >> 4) << 24);
+}
+}  // namespace g16
+
+// Shared-memory matrix descriptor: K-major, 128-byte swizzle, 8-row groups 1024 B
+// apart (stride byte offset), descriptor version 1 (Blackwell).
+__device__ __forceinline__ uint64_t smem_desc_k_sw128(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+    d |= static_cast<uint64_t>(1) << 16;             // leading byte offset (unused with swizzle)
+    d |= static_cast<uint64_t>(1024 >> 4) << 32;     // stride byte offset
+    d |= static_cast<uint64_t>(1) << 46;             // version
+    d |= static_cast<uint64_t>(2) << 61;             // SWIZZLE_128B
+    return d;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                          uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        "}\n" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// Arrives on `bar` once every tcgen05.mma issued so far by this thread has finished.
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// 32 consecutive fp32 columns of this thread's TMEM lane.
+__device__ __forceinline__ void tmem_ld_32cols(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ uint32_t pack_bf16(uint32_t lo_f32_bits, uint32_t hi_f32_bits) {
+    const __nv_bfloat162 v = __float22bfloat162_rn(make_float2(__uint_as_float(lo_f32_bits), __uint_as_float(hi_f32_bits)));
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+// Tile t -> (n-tile, m-tile): GROUP_M m-tiles are walked for each n-tile before n advances.
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& tm, int& tn) {
+    const int per_group = g16::GROUP_M * tiles_n;
+    const int group = t / per_group;
+    const int first_m = group * g16::GROUP_M;
+    const int rows = min(g16::GROUP_M, tiles_m - first_m);
+    const int in = t - group * per_group;
+    tm = first_m + in % rows;
+    tn = in / rows;
+}
+
+template <int BLOCK_Q>
+__global__ void __launch_bounds__(g16::THREADS, 1)
+cutlass_my_h100_match_no_tail(int M, int N, int K, __nv_bfloat16* C, const __grid_constant__ CUtensorMap tensorMapA,
+                              const __grid_constant__ CUtensorMap tensorMapB) {
+    using namespace g16;
+    using C_ = Cfg<BLOCK_Q>;
+    constexpr int STAGES = C_::STAGES;
+    constexpr uint32_t IDESC = instr_desc(BLOCK_P, BLOCK_Q);
+
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    unsigned char* ring = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);  // 1024-byte aligned
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(ring + STAGES * C_::STAGE_BYTES);
+    uint64_t* empty_bar = full_bar + STAGES;
+    uint64_t* acc_full_bar = empty_bar + STAGES;   // [2]
+    uint64_t* acc_empty_bar = acc_full_bar + 2;    // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty_bar + 2);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+    volatile uint32_t* never_flag = tmem_slot + 2;  // stays 0: lets the unwind path wait although abort is set
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int tiles_m = M / BLOCK_Q;
+    const int tiles_n = N / BLOCK_P;
+    const int total_tiles = tiles_m * tiles_n;
+    const int k_blocks = K / BLOCK_K;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(&acc_full_bar[a], 1);
+            mbar_init(&acc_empty_bar[a], EPI_WARPS);
+        }
+        *abort_flag = 0;
+        *never_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        __syncwarp();
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"(static_cast<uint32_t>(TMEM_COLS))
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    bool timed_out = false;
+
+    if (warp == 0) {
+        // ------------------------- TMA producer -------------------------
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tensorMapA)) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tensorMapB)) : "memory");
+            int stage = 0;
+            uint32_t phase = 0;
+            int armed = 0;  // stages armed and not known to be consumed (for the unwind path)
+            for (int t = blockIdx.x; t < total_tiles && !timed_out; t += gridDim.x) {
+                int tm, tn;
+                tile_coords(t, tiles_m, tiles_n, tm, tn);
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag)) {
+                        timed_out = true;
+                        break;
+                    }
+                    unsigned char* p_dst = ring + stage * C_::STAGE_BYTES;
+                    unsigned char* q_dst = p_dst + C_::P_BYTES;
+                    mbar_arrive_expect_tx(&full_bar[stage], C_::STAGE_BYTES);
+                    tma_load_2d(p_dst, &tensorMapB, kb * BLOCK_K, tn * BLOCK_P, &full_bar[stage]);
+                    tma_load_2d(q_dst, &tensorMapA, kb * BLOCK_K, tm * BLOCK_Q, &full_bar[stage]);
+                    armed = armed < STAGES ? armed + 1 : STAGES;
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+            if (timed_out || *abort_flag) {
+                // Unwind: let loads already in flight land before shared memory is released.
+                int s = stage;
+                uint32_t ph = phase;
+                for (int i = 0; i < armed; ++i) {
+                    if (--s < 0) {
+                        s = STAGES - 1;
+                        ph ^= 1u;
+                    }
+                    mbar_wait_bounded(&full_bar[s], ph, never_flag, 2000000ull);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------- MMA issuer -------------------------
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc = 0;
+            uint32_t acc_phase = 0;
+            for (int t = blockIdx.x; t < total_tiles && !timed_out; t += gridDim.x) {
+                if (!mbar_wait_bounded(&acc_empty_bar[acc], acc_phase ^ 1u, abort_flag)) {
+                    timed_out = true;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BLOCK_Q);
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag)) {
+                        timed_out = true;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t p_addr = smem_u32(ring + stage * C_::STAGE_BYTES);
+                    const uint64_t p_desc = smem_desc_k_sw128(p_addr);
+                    const uint64_t q_desc = smem_desc_k_sw128(p_addr + C_::P_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
+                        // 16 bf16 = 32 bytes further along K inside the swizzle span: +2 in the address field.
+                        umma_bf16(d_tmem, p_desc + 2u * k, q_desc + 2u * k, IDESC, (kb | k) != 0 ? 1u : 0u);
+                    }
+                    umma_commit(&empty_bar[stage]);  // stage is free once these MMAs have read it
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (timed_out) break;
+                umma_commit(&acc_full_bar[acc]);  // accumulator complete
+                if (++acc == 2) {
+                    acc = 0;
+                    acc_phase ^= 1u;
+                }
+            }
+        }
+    } else {
+        // ------------------------- epilogue warps -------------------------
+        const int quarter = warp & 3;  // TMEM lanes 32*quarter .. +31 are reachable from this warp
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+            int tm, tn;
+            tile_coords(t, tiles_m, tiles_n, tm, tn);
+            // Warp-uniform outcome: the TMEM loads below need the whole warp converged.
+            const bool ready = mbar_wait_bounded(&acc_full_bar[acc], acc_phase, abort_flag);
+            if (!__all_sync(0xffffffffu, ready)) {
+                timed_out = true;
+                break;
+            }
+            tc_fence_after();
+            const size_t n = static_cast<size_t>(tn) * BLOCK_P + quarter * 32 + lane;
+            __nv_bfloat16* c_row = C + n * static_cast<size_t>(M) + static_cast<size_t>(tm) * BLOCK_Q;
+            const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                                   static_cast<uint32_t>(acc * BLOCK_Q);
+#pragma unroll 2
+            for (int c = 0; c < BLOCK_Q; c += 32) {
+                uint32_t r[32];
+                tmem_ld_32cols(t_row + c, r);
+                tmem_ld_wait();
+                uint4* dst = reinterpret_cast<uint4*>(c_row + c);
+#pragma unroll
+                for (int v = 0; v < 4; ++v) {
+                    uint4 o;
+                    o.x = pack_bf16(r[8 * v + 0], r[8 * v + 1]);
+                    o.y = pack_bf16(r[8 * v + 2], r[8 * v + 3]);
+                    o.z = pack_bf16(r[8 * v + 4], r[8 * v + 5]);
+                    o.w = pack_bf16(r[8 * v + 6], r[8 * v + 7]);
+                    dst[v] = o;
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty_bar[acc]);
+            if (++acc == 2) {
+                acc = 0;
+                acc_phase ^= 1u;
+            }
+        }
+    }
+
+    if (timed_out) {
+        *abort_flag = 1;
+        raise_device_status(DEV_GEMM_PIPE_TIMEOUT);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                     "r"(static_cast<uint32_t>(TMEM_COLS))
+                     : "memory");
+    }
+}
+
+namespace {
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+std::mutex g_map_mu;
+EncodeTiledFn g_encode = nullptr;
+
+struct MapKey {
+    int dev;
+    const void* ptr;
+    int rows, k, box_rows;
+    bool operator==(const MapKey& o) const {
+        return dev == o.dev && ptr == o.ptr && rows == o.rows && k == o.k && box_rows == o.box_rows;
+    }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        size_t h = reinterpret_cast<size_t>(k.ptr) * 0x9E3779B97F4A7C15ull;
+        h ^= (static_cast<size_t>(k.rows) << 32) ^ static_cast<size_t>(k.k) ^ (static_cast<size_t>(k.box_rows) << 20) ^
+             (static_cast<size_t>(k.dev) << 56);
+        return h;
+    }
+};
+// A tensor map is a pure function of its key, so a cached entry can never be stale.
+std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
+
+int get_tensor_map(int dev, const void* ptr, int rows, int k, int box_rows, CUtensorMap* out) {
+    std::lock_guard<std::mutex> lk(g_map_mu);
+    if (!g_encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+        if (e != cudaSuccess || !fn || q != cudaDriverEntryPointSuccess)
+            return set_error(PRISM_B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+        g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+    }
+    const MapKey key{dev, ptr, rows, k, box_rows};
+    auto it = g_maps.find(key);
+    if (it != g_maps.end()) {
+        *out = it->second;
+        return PRISM_B200_OK;
+    }
+    CUtensorMap m;
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(rows)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(k) * 2};
+    const cuuint32_t box[2] = {static_cast<cuuint32_t>(g16::BLOCK_K), static_cast<cuuint32_t>(box_rows)};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = g_encode(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return set_error(PRISM_B200_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d", (int)r);
+    if (g_maps.size() > 4096) g_maps.clear();
+    g_maps.emplace(key, m);
+    *out = m;
+    return PRISM_B200_OK;
+}
+
+template <int BLOCK_Q>
+int launch_gemm(int dev, int sms, int M, int N, int K, const void* A, const void* B, void* C, cudaStream_t s) {
+    using C_ = g16::Cfg<BLOCK_Q>;
+    CUtensorMap map_a, map_b;
+    if (int rc = get_tensor_map(dev, A, M, K, BLOCK_Q, &map_a)) return rc;
+    if (int rc = get_tensor_map(dev, B, N, K, g16::BLOCK_P, &map_b)) return rc;
+    auto kern = cutlass_my_h100_match_no_tail<BLOCK_Q>;
+    static bool attr_set[64] = {};
+    if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+        PRISM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            static_cast<int>(C_::SMEM_BYTES)));
+        if (dev >= 0 && dev < 64) attr_set[dev] = true;
+    }
+    const int tiles = (M / BLOCK_Q) * (N / g16::BLOCK_P);
+    const int grid = tiles < sms ? tiles : sms;
+    kern<<<grid, g16::THREADS, C_::SMEM_BYTES, s>>>(M, N, K, static_cast<__nv_bfloat16*>(C), map_a, map_b);
+    PRISM_CUDA_TRY(cudaGetLastError());
+    count_launch();
+    return PRISM_B200_OK;
+}
+
+}  // namespace
+}  // namespace prism_b200
+
+using namespace prism_b200;
+
+extern "C" int prism_b200_gemm_bf16(int M, int N, int K, const uint16_t* A, const uint16_t* B, uint16_t* C,
+                                    void* stream) {
+    if (M < 0 || N < 0 || K < 0) return set_error(PRISM_B200_ERR_INVALID_ARGUMENT, "gemm_bf16: negative dimension");
+    if (M == 0 || N == 0) return PRISM_B200_OK;
+    if (!A || !B || !C) return set_error(PRISM_B200_ERR_INVALID_ARGUMENT, "gemm_bf16: null pointer");
+    if (M % 128 || N % 128 || K % 64 || K == 0)
+        return set_error(PRISM_B200_ERR_UNSUPPORTED_SHAPE,
+                         "gemm_bf16: need M %% 128 == 0, N %% 128 == 0, K %% 64 == 0, K > 0 (got %d, %d, %d)", M, N, K);
+    if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15u)
+        return set_error(PRISM_B200_ERR_MISALIGNED, "gemm_bf16: A, B and C must be 16-byte aligned");
+    if (int rc = bind_status_word()) return rc;
+    int dev = 0;
+    PRISM_CUDA_TRY(cudaGetDevice(&dev));
+    static int sm_count[64] = {};
+    int sms = (dev >= 0 && dev < 64) ? sm_count[dev] : 0;
+    if (sms == 0) {
+        PRISM_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+        if (dev >= 0 && dev < 64) sm_count[dev] = sms;
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // 256-wide m-tiles halve the operand traffic per flop; fall back to 128 when M
+    // does not divide or when the wider tile would leave a poorly filled last wave.
+    bool wide = (M % 256 == 0);
+    if (wide) {
+        auto eff = [&](int tiles) { return static_cast<double>(tiles) / (((tiles + sms - 1) / sms) * sms); };
+        const int t256 = (M / 256) * (N / 128), t128 = (M / 128) * (N / 128);
+        if (eff(t256) + 0.10 < eff(t128)) wide = false;
+    }
+    return wide ? launch_gemm<256>(dev, sms, M, N, K, A, B, C, s) : launch_gemm<128>(dev, sms, M, N, K, A, B, C, s);
+}

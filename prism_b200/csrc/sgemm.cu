@@ -1,0 +1,533 @@
+// FP32 SGEMM family for B200, C = alpha * A * B + beta * C, row-major, pure FFMA
+// (no TF32, no tensor cores).
+//
+// The entry points keep the parameter lists of the emitted reference kernels
+// (generated/my_sgemm_kernel_{1,2,3,4,5}.cu, generated/sgemm_shared_mem_block.cu):
+//   (int M, int N, int K, float alpha, [const] float* A, [const] float* B,
+//    float beta, float* C, int <block_size | tile_size | num_blocks_N>)
+// with a 1-D grid and a linear block id, and the host dispatcher mirrors
+// `run_my_kernel` (evals/4090_sgemm/runner.cu:245-267).
+//
+// Kernels 1-4 and 6 are the small rungs of the ladder.  Kernel 5 is the one that
+// matters for throughput: its A and B tiles are brought into shared memory by
+// the bulk-copy engine (cp.async.bulk, one row per copy, completion counted on an
+// mbarrier), three stages deep, and four warps run an 8x16 register tile per lane
+// out of 128-bit shared-memory reads.
+#include "common.cuh"
+
+namespace prism_b200 {
+
+// ============================================================================
+// Kernel 1: one thread per element of C (generated/my_sgemm_kernel_1.cu:1-28).
+// The reference has no bounds check and needs M*N to be a multiple of the block
+// size; this one guards the tail.
+// ============================================================================
+__global__ void my_sgemm_kernel_1(int M, int N, int K, float alpha, const float* A, const float* B, float beta,
+                                  float* C, int block_size) {
+    const long long tid = static_cast<long long>(blockIdx.x) * block_size + threadIdx.x;
+    if (tid >= static_cast<long long>(M) * N) return;
+    const int row = static_cast<int>(tid / N);
+    const int col = static_cast<int>(tid % N);
+    const float* a = A + static_cast<size_t>(row) * K;
+    const float* b = B + col;
+    float acc = 0.f;
+    for (int k = 0; k < K; ++k) acc = fmaf(a[k], b[static_cast<size_t>(k) * N], acc);
+    float* c = C + static_cast<size_t>(row) * N + col;
+    *c = alpha * acc + beta * *c;
+}
+
+// ============================================================================
+// Kernel 2: same dot product, threads mapped through tile_size x tile_size tiles
+// so that a warp walks along a row of C (generated/my_sgemm_kernel_2.cu:1-32).
+// ============================================================================
+__global__ void my_sgemm_kernel_2(int M, int N, int K, float alpha, const float* A, const float* B, float beta,
+                                  float* C, int tile_size) {
+    const long long gtid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const int per_tile = tile_size * tile_size;
+    const int tiles_per_row = (N + tile_size - 1) / tile_size;
+    const long long tile = gtid / per_tile;
+    const int local = static_cast<int>(gtid % per_tile);
+    const long long row = (tile / tiles_per_row) * tile_size + local / tile_size;
+    const long long col = (tile % tiles_per_row) * tile_size + local % tile_size;
+    if (row >= M || col >= N) return;
+    const float* a = A + row * K;
+    const float* b = B + col;
+    float acc = 0.f;
+    for (int k = 0; k < K; ++k) acc = fmaf(a[k], b[static_cast<size_t>(k) * N], acc);
+    float* c = C + row * N + col;
+    *c = alpha * acc + beta * *c;
+}
+
+// ============================================================================
+// Kernel 3 of the evaluation: BLOCKSIZE x BLOCKSIZE shared-memory tiles, one
+// output per thread (generated/sgemm_shared_mem_block.cu:1-49).  Dimensions
+// must be multiples of BLOCKSIZE (the dispatcher checks).
+// ============================================================================
+template <int BLOCKSIZE>
+__global__ void __launch_bounds__(BLOCKSIZE* BLOCKSIZE)
+sgemm_shared_mem_block(int M, int N, int K, float alpha, const float* A, const float* B, float beta, float* C,
+                       int num_blocks_N) {
+    __shared__ float As[BLOCKSIZE][BLOCKSIZE];
+    __shared__ float Bs[BLOCKSIZE][BLOCKSIZE];
+    const int tile_row = blockIdx.x / num_blocks_N;
+    const int tile_col = blockIdx.x % num_blocks_N;
+    const int tr = threadIdx.x / BLOCKSIZE;
+    const int tc = threadIdx.x % BLOCKSIZE;
+    const float* a = A + static_cast<size_t>(tile_row * BLOCKSIZE + tr) * K + tc;
+    const float* b = B + static_cast<size_t>(tr) * N + tile_col * BLOCKSIZE + tc;
+    float acc = 0.f;
+    for (int k0 = 0; k0 < K; k0 += BLOCKSIZE) {
+        As[tr][tc] = a[k0];
+        Bs[tr][tc] = b[static_cast<size_t>(k0) * N];
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < BLOCKSIZE; ++k) acc = fmaf(As[tr][k], Bs[k][tc], acc);
+        __syncthreads();
+    }
+    float* c = C + static_cast<size_t>(tile_row * BLOCKSIZE + tr) * N + tile_col * BLOCKSIZE + tc;
+    *c = alpha * acc + beta * *c;
+}
+
+// ============================================================================
+// Kernel 6 (the reference's generated/my_sgemm_kernel_3.cu:1-83, which its
+// harness never launches): BM x BN tile, TM x TN outputs per thread, scalar
+// accesses.  Here every access is bounds-checked, so it doubles as the kernel
+// for shapes that the faster kernels do not divide.
+// ============================================================================
+template <int BM, int BN, int BK, int TM, int TN>
+__global__ void __launch_bounds__((BM * BN) / (TM * TN))
+my_sgemm_kernel_3(int M, int N, int K, float alpha, const float* A, const float* B, float beta, float* C,
+                  int num_blocks_N) {
+    constexpr int THREADS = (BM * BN) / (TM * TN);
+    __shared__ float As[BK][BM + 1];  // k-major so a thread's TM rows are contiguous
+    __shared__ float Bs[BK][BN];
+    const int row0 = (blockIdx.x / num_blocks_N) * BM;
+    const int col0 = (blockIdx.x % num_blocks_N) * BN;
+    const int ty = threadIdx.x / (BN / TN);
+    const int tx = threadIdx.x % (BN / TN);
+    float acc[TM][TN] = {};
+    for (int k0 = 0; k0 < K; k0 += BK) {
+        for (int e = threadIdx.x; e < BM * BK; e += THREADS) {
+            const int r = e / BK, k = e % BK;
+            const int gr = row0 + r, gk = k0 + k;
+            As[k][r] = (gr < M && gk < K) ? A[static_cast<size_t>(gr) * K + gk] : 0.f;
+        }
+        for (int e = threadIdx.x; e < BK * BN; e += THREADS) {
+            const int k = e / BN, c = e % BN;
+            const int gk = k0 + k, gc = col0 + c;
+            Bs[k][c] = (gk < K && gc < N) ? B[static_cast<size_t>(gk) * N + gc] : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < BK; ++k) {
+            float ra[TM], rb[TN];
+#pragma unroll
+            for (int i = 0; i < TM; ++i) ra[i] = As[k][ty * TM + i];
+#pragma unroll
+            for (int j = 0; j < TN; ++j) rb[j] = Bs[k][tx * TN + j];
+#pragma unroll
+            for (int i = 0; i < TM; ++i)
+#pragma unroll
+                for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(ra[i], rb[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < TM; ++i) {
+        const int gr = row0 + ty * TM + i;
+        if (gr >= M) continue;
+#pragma unroll
+        for (int j = 0; j < TN; ++j) {
+            const int gc = col0 + tx * TN + j;
+            if (gc < N) {
+                float* c = C + static_cast<size_t>(gr) * N + gc;
+                *c = alpha * acc[i][j] + beta * *c;
+            }
+        }
+    }
+}
+
+// ============================================================================
+// Kernel 4: 128x128x8 tiles, 8x8 outputs per thread, 128-bit global and shared
+// accesses, A transposed on its way into shared memory
+// (generated/my_sgemm_kernel_4.cu:1-88).  M, N multiples of BM, BN; K of BK.
+// The next k-slice is fetched into registers while the current one is consumed.
+// ============================================================================
+template <int BM, int BN, int BK, int TM, int TN>
+__global__ void __launch_bounds__((BM * BN) / (TM * TN))
+my_sgemm_kernel_4(int M, int N, int K, float alpha, float* A, float* B, float beta, float* C, int num_blocks_N) {
+    static_assert(BM == 128 && BN == 128 && BK == 8 && TM == 8 && TN == 8, "one 16-byte load per thread per operand");
+    __shared__ __align__(16) float As[2][BK][BM];
+    __shared__ __align__(16) float Bs[2][BK][BN];
+    const int row0 = (blockIdx.x / num_blocks_N) * BM;
+    const int col0 = (blockIdx.x % num_blocks_N) * BN;
+    const int ty = threadIdx.x / (BN / TN);
+    const int tx = threadIdx.x % (BN / TN);
+    const int a_row = threadIdx.x / (BK / 4), a_col = (threadIdx.x % (BK / 4)) * 4;
+    const int b_row = threadIdx.x / (BN / 4), b_col = (threadIdx.x % (BN / 4)) * 4;
+    const float* a_src = A + static_cast<size_t>(row0 + a_row) * K + a_col;
+    const float* b_src = B + static_cast<size_t>(b_row) * N + col0 + b_col;
+
+    float acc[TM][TN] = {};
+    float4 ra = *reinterpret_cast<const float4*>(a_src);
+    float4 rb = *reinterpret_cast<const float4*>(b_src);
+    int buf = 0;
+    for (int k0 = 0; k0 < K; k0 += BK) {
+        As[buf][a_col + 0][a_row] = ra.x;
+        As[buf][a_col + 1][a_row] = ra.y;
+        As[buf][a_col + 2][a_row] = ra.z;
+        As[buf][a_col + 3][a_row] = ra.w;
+        *reinterpret_cast<float4*>(&Bs[buf][b_row][b_col]) = rb;
+        __syncthreads();
+        if (k0 + BK < K) {
+            ra = *reinterpret_cast<const float4*>(a_src + k0 + BK);
+            rb = *reinterpret_cast<const float4*>(b_src + static_cast<size_t>(k0 + BK) * N);
+        }
+#pragma unroll
+        for (int k = 0; k < BK; ++k) {
+            float fa[TM], fb[TN];
+            // Two 16-byte reads per operand, 64 columns apart, keep each quarter-warp on distinct banks.
+            *reinterpret_cast<float4*>(&fa[0]) = *reinterpret_cast<const float4*>(&As[buf][k][ty * 4]);
+            *reinterpret_cast<float4*>(&fa[4]) = *reinterpret_cast<const float4*>(&As[buf][k][64 + ty * 4]);
+            *reinterpret_cast<float4*>(&fb[0]) = *reinterpret_cast<const float4*>(&Bs[buf][k][tx * 4]);
+            *reinterpret_cast<float4*>(&fb[4]) = *reinterpret_cast<const float4*>(&Bs[buf][k][64 + tx * 4]);
+#pragma unroll
+            for (int i = 0; i < TM; ++i)
+#pragma unroll
+                for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(fa[i], fb[j], acc[i][j]);
+        }
+        buf ^= 1;  // the other buffer was last read before the barrier above
+    }
+#pragma unroll
+    for (int i = 0; i < TM; ++i) {
+        const int r = row0 + (i < 4 ? ty * 4 + i : 64 + ty * 4 + (i - 4));
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            float4* c = reinterpret_cast<float4*>(C + static_cast<size_t>(r) * N + col0 + h * 64 + tx * 4);
+            float4 v = *c;
+            v.x = alpha * acc[i][h * 4 + 0] + beta * v.x;
+            v.y = alpha * acc[i][h * 4 + 1] + beta * v.y;
+            v.z = alpha * acc[i][h * 4 + 2] + beta * v.z;
+            v.w = alpha * acc[i][h * 4 + 3] + beta * v.w;
+            *c = v;
+        }
+    }
+}
+
+// ============================================================================
+// Kernel 5: the throughput kernel (generated/my_sgemm_kernel_5.cu:1-84 with
+// loadFromGmem_our / processFromSmem_our, evals/4090_sgemm/my_kernel_utils.cuh:13-89).
+//
+// CTA tile 128 x 128, k-slice 32, STAGES-deep ring in shared memory.
+//   Staging: a k-slice is 128 row copies of A (128 B each) and 32 row copies of B
+//     (512 B each) issued with cp.async.bulk, a quarter by each warp (one or two
+//     copies per lane); they complete on the stage's "full" mbarrier.  A rows land
+//     with a stride of 36 floats, which puts any 8 consecutive rows on 8 different
+//     16-byte bank groups.  Four warps and no separate producer warp keep the CTA at
+//     two warps per scheduler with two CTAs per SM, so a lane may use 255 registers.
+//   Compute: 2 x 2 arrangement of 64 x 64 warp tiles.  A lane owns
+//     rows  wm0 + (lane & 7) + 8 i  (i = 0..7) and columns  wn0 + 16 j + 4 (lane >> 3) .. +3
+//     (j = 0..3): 8 x 16 = 128 accumulators.  Per 4 k it reads 8 x 16 B of A (one per
+//     row, 4 consecutive k) and 4 x 4 x 16 B of B, all conflict-free, for 512 FMAs.
+//     With PACKED the FMAs are issued as fma.rn.f32x2 on column pairs, which halves
+//     the FMA issue slots and leaves room for the shared-memory reads.
+//   A "full"/"empty" mbarrier pair per stage hands slices back and forth; every
+//   wait is bounded.
+// Needs M % 128 == 0, N % 128 == 0, K % 32 == 0 and 16-byte aligned A, B, C.
+// ============================================================================
+namespace k5 {
+constexpr int BM = 128, BN = 128, BK = 32;
+constexpr int STAGES = 3;
+constexpr int A_STRIDE = BK + 4;                       // floats
+constexpr int A_STAGE = BM * A_STRIDE;                 // floats
+constexpr int B_STAGE = BK * BN;                       // floats
+constexpr int WARPS = 4;
+constexpr int THREADS = WARPS * 32;
+constexpr uint32_t STAGE_TX_BYTES = (BM * BK + BK * BN) * sizeof(float);
+constexpr size_t SMEM_BYTES = static_cast<size_t>(STAGES) * (A_STAGE + B_STAGE) * sizeof(float) + 2 * STAGES * 8 + 16;
+}  // namespace k5
+
+__device__ __forceinline__ void bulk_copy_g2s(void* dst_smem, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_u32(dst_smem)),
+                 "l"(src), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+
+__device__ __forceinline__ unsigned long long pack2(float lo, float hi) {
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(unsigned long long v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ void fma2(unsigned long long& acc, unsigned long long a, unsigned long long b) {
+    asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc) : "l"(a), "l"(b));
+}
+
+template <bool PACKED>
+__global__ void __launch_bounds__(k5::THREADS, 2)
+my_sgemm_kernel_5(int M, int N, int K, float alpha, float* A, float* B, float beta, float* C, int num_blocks_N) {
+    using namespace k5;
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    float* As = reinterpret_cast<float*>(smem_raw);
+    float* Bs = As + STAGES * A_STAGE;
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(Bs + STAGES * B_STAGE);
+    uint64_t* empty_bar = full_bar + STAGES;
+    volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(empty_bar + STAGES);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int row0 = (blockIdx.x / num_blocks_N) * BM;
+    const int col0 = (blockIdx.x % num_blocks_N) * BN;
+    const int k_slices = K / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full_bar[s], WARPS);
+            mbar_init(&empty_bar[s], WARPS);
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    __syncthreads();
+
+    // Each warp copies its quarter of a k-slice: 32 rows of A (lane = row) and 8 rows
+    // of B (lanes 0-7), and announces those bytes on the stage's "full" barrier first.
+    const float* a_src = A + static_cast<size_t>(row0 + warp * 32 + lane) * K;
+    const float* b_src = B + static_cast<size_t>(warp * 8 + (lane & 7)) * N + col0;
+    auto issue_slice = [&](int t) {
+        const int s = t % STAGES;
+        if (lane == 0) mbar_arrive_expect_tx(&full_bar[s], STAGE_TX_BYTES / WARPS);
+        __syncwarp();
+        bulk_copy_g2s(As + s * A_STAGE + (warp * 32 + lane) * A_STRIDE, a_src + t * BK, BK * sizeof(float),
+                      &full_bar[s]);
+        if (lane < 8)
+            bulk_copy_g2s(Bs + s * B_STAGE + (warp * 8 + lane) * BN, b_src + static_cast<size_t>(t) * BK * N,
+                          BN * sizeof(float), &full_bar[s]);
+    };
+    for (int t = 0; t < STAGES - 1 && t < k_slices; ++t) issue_slice(t);
+
+    const int tm = lane & 7;
+    const int tn = lane >> 3;
+    const int wm0 = (warp >> 1) * 64;
+    const int wn0 = (warp & 1) * 64;
+
+    unsigned long long acc2[PACKED ? 8 : 1][PACKED ? 8 : 1];
+    float acc[PACKED ? 1 : 8][PACKED ? 1 : 16];
+    if constexpr (PACKED) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc2[i][j] = 0ull;
+    } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+#pragma unroll
+            for (int j = 0; j < 16; ++j) acc[i][j] = 0.f;
+    }
+
+    bool ok = true;
+    for (int t = 0; t < k_slices; ++t) {
+        const int s = t % STAGES;
+        const uint32_t round = static_cast<uint32_t>(t / STAGES);
+        // Refill the stage that slice t-1 used with slice t+STAGES-1, once all four
+        // warps have released it.
+        const int refill = t + STAGES - 1;
+        if (refill < k_slices) {
+            if (t >= 1 && !mbar_wait_bounded(&empty_bar[(t - 1) % STAGES], static_cast<uint32_t>((t - 1) / STAGES) & 1u,
+                                             abort_flag)) {
+                ok = false;
+                break;
+            }
+            issue_slice(refill);
+        }
+        if (!mbar_wait_bounded(&full_bar[s], round & 1u, abort_flag)) {
+            ok = false;
+            break;
+        }
+        const float* a_base = As + s * A_STAGE + (wm0 + tm) * A_STRIDE;
+        const float* b_base = Bs + s * B_STAGE + wn0 + tn * 4;
+#pragma unroll 2
+        for (int kk = 0; kk < BK; kk += 4) {
+            float4 a[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) a[i] = *reinterpret_cast<const float4*>(a_base + i * 8 * A_STRIDE + kk);
+#pragma unroll
+            for (int k4 = 0; k4 < 4; ++k4) {
+                if constexpr (PACKED) {
+                    ulonglong2 b[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        b[j] = *reinterpret_cast<const ulonglong2*>(b_base + (kk + k4) * BN + j * 16);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const float av = k4 == 0 ? a[i].x : k4 == 1 ? a[i].y : k4 == 2 ? a[i].z : a[i].w;
+                        const unsigned long long a2 = pack2(av, av);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            fma2(acc2[i][2 * j + 0], a2, b[j].x);
+                            fma2(acc2[i][2 * j + 1], a2, b[j].y);
+                        }
+                    }
+                } else {
+                    float4 b[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) b[j] = *reinterpret_cast<const float4*>(b_base + (kk + k4) * BN + j * 16);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const float av = k4 == 0 ? a[i].x : k4 == 1 ? a[i].y : k4 == 2 ? a[i].z : a[i].w;
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            acc[i][4 * j + 0] = fmaf(av, b[j].x, acc[i][4 * j + 0]);
+                            acc[i][4 * j + 1] = fmaf(av, b[j].y, acc[i][4 * j + 1]);
+                            acc[i][4 * j + 2] = fmaf(av, b[j].z, acc[i][4 * j + 2]);
+                            acc[i][4 * j + 3] = fmaf(av, b[j].w, acc[i][4 * j + 3]);
+                        }
+                    }
+                }
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty_bar[s]);
+    }
+    if (!ok) {
+        if (lane == 0) {
+            *abort_flag = 1;
+            raise_device_status(DEV_SGEMM_PIPE_TIMEOUT);
+        }
+        return;
+    }
+
+    // C = alpha * acc + beta * C, 16 bytes at a time.
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        float* c_row = C + static_cast<size_t>(row0 + wm0 + tm + 8 * i) * N + col0 + wn0 + tn * 4;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            float4* c = reinterpret_cast<float4*>(c_row + j * 16);
+            float4 v = *c;
+            float r0, r1, r2, r3;
+            if constexpr (PACKED) {
+                unpack2(acc2[i][2 * j + 0], r0, r1);
+                unpack2(acc2[i][2 * j + 1], r2, r3);
+            } else {
+                r0 = acc[i][4 * j + 0]; r1 = acc[i][4 * j + 1]; r2 = acc[i][4 * j + 2]; r3 = acc[i][4 * j + 3];
+            }
+            v.x = alpha * r0 + beta * v.x;
+            v.y = alpha * r1 + beta * v.y;
+            v.z = alpha * r2 + beta * v.z;
+            v.w = alpha * r3 + beta * v.w;
+            *c = v;
+        }
+    }
+}
+
+namespace {
+
+inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Bounds-checked tiled kernel: any shape.
+int launch_generic(int M, int N, int K, float alpha, const float* A, const float* B, float beta, float* C,
+                   cudaStream_t s) {
+    constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
+    const int nbn = ceil_div(N, BN);
+    const long long blocks = static_cast<long long>(ceil_div(M, BM)) * nbn;
+    if (blocks > 0x7fffffffLL) return set_error(PRISM_B200_ERR_TOO_LARGE, "sgemm: too many tiles");
+    my_sgemm_kernel_3<BM, BN, BK, TM, TN>
+        <<<static_cast<unsigned>(blocks), (BM * BN) / (TM * TN), 0, s>>>(M, N, K, alpha, A, B, beta, C, nbn);
+    return PRISM_B200_OK;
+}
+
+bool g_k5_packed = true;  // fma.rn.f32x2 form of kernel 5; PRISM_B200_SGEMM_SCALAR=1 selects plain fmaf
+bool g_k5_env_read = false;
+
+}  // namespace
+}  // namespace prism_b200
+
+using namespace prism_b200;
+
+extern "C" int prism_b200_sgemm(int kernel_id, int M, int N, int K, float alpha, const float* A, const float* B,
+                                float beta, float* C, void* stream) {
+    if (kernel_id < 1 || kernel_id > 6)
+        return set_error(PRISM_B200_ERR_INVALID_ARGUMENT, "sgemm: unknown kernel id %d (1..6)", kernel_id);
+    if (M < 0 || N < 0 || K < 0) return set_error(PRISM_B200_ERR_INVALID_ARGUMENT, "sgemm: negative dimension");
+    if (M == 0 || N == 0) return PRISM_B200_OK;
+    if (!C || (K > 0 && (!A || !B))) return set_error(PRISM_B200_ERR_INVALID_ARGUMENT, "sgemm: null pointer");
+    if (static_cast<long long>(M) * N > 0x7fffffffLL * 256LL)
+        return set_error(PRISM_B200_ERR_TOO_LARGE, "sgemm: M*N too large");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (int rc = bind_status_word()) return rc;
+    const bool vec_ok = aligned16(A) && aligned16(B) && aligned16(C);
+    int rc = PRISM_B200_OK;
+
+    switch (kernel_id) {
+    case 1: {
+        const int block = 256;
+        const long long blocks = (static_cast<long long>(M) * N + block - 1) / block;
+        my_sgemm_kernel_1<<<static_cast<unsigned>(blocks), block, 0, s>>>(M, N, K, alpha, A, B, beta, C, block);
+        break;
+    }
+    case 2: {
+        const int tile = 32;
+        const long long blocks = static_cast<long long>(ceil_div(M, tile)) * ceil_div(N, tile);
+        my_sgemm_kernel_2<<<static_cast<unsigned>(blocks), tile * tile, 0, s>>>(M, N, K, alpha, A, B, beta, C, tile);
+        break;
+    }
+    case 3: {
+        constexpr int BS = 32;
+        if (M % BS == 0 && N % BS == 0 && K % BS == 0 && K > 0) {
+            const int nbn = N / BS;
+            sgemm_shared_mem_block<BS><<<(M / BS) * nbn, BS * BS, 0, s>>>(M, N, K, alpha, A, B, beta, C, nbn);
+        } else {
+            rc = launch_generic(M, N, K, alpha, A, B, beta, C, s);
+        }
+        break;
+    }
+    case 4: {
+        if (M % 128 == 0 && N % 128 == 0 && K % 8 == 0 && K > 0 && vec_ok) {
+            const int nbn = N / 128;
+            my_sgemm_kernel_4<128, 128, 8, 8, 8><<<(M / 128) * nbn, 256, 0, s>>>(
+                M, N, K, alpha, const_cast<float*>(A), const_cast<float*>(B), beta, C, nbn);
+        } else {
+            rc = launch_generic(M, N, K, alpha, A, B, beta, C, s);
+        }
+        break;
+    }
+    case 5: {
+        if (M % k5::BM == 0 && N % k5::BN == 0 && K % k5::BK == 0 && K > 0 && vec_ok) {
+            if (!g_k5_env_read) {
+                const char* e = getenv("PRISM_B200_SGEMM_SCALAR");
+                g_k5_packed = !(e && e[0] == '1');
+                g_k5_env_read = true;
+            }
+            const int nbn = N / k5::BN;
+            const unsigned blocks = static_cast<unsigned>((M / k5::BM) * nbn);
+            static bool attr_set[2][64] = {};
+            int dev = 0;
+            PRISM_CUDA_TRY(cudaGetDevice(&dev));
+            auto kern = g_k5_packed ? my_sgemm_kernel_5<true> : my_sgemm_kernel_5<false>;
+            if (dev < 0 || dev >= 64 || !attr_set[g_k5_packed][dev]) {
+                PRISM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                    static_cast<int>(k5::SMEM_BYTES)));
+                if (dev >= 0 && dev < 64) attr_set[g_k5_packed][dev] = true;
+            }
+            kern<<<blocks, k5::THREADS, k5::SMEM_BYTES, s>>>(M, N, K, alpha, const_cast<float*>(A),
+                                                            const_cast<float*>(B), beta, C, nbn);
+        } else {
+            rc = launch_generic(M, N, K, alpha, A, B, beta, C, s);
+        }
+        break;
+    }
+    case 6:
+        rc = launch_generic(M, N, K, alpha, A, B, beta, C, s);
+        break;
+    }
+    if (rc) return rc;
+    PRISM_CUDA_TRY(cudaGetLastError());
+    count_launch();
+    return PRISM_B200_OK;
+}

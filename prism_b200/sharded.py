@@ -1,0 +1,155 @@
+"""Multi-GPU forms of the two paths that shard: one process per GPU.
+
+* GEMM (fp32 and bf16): rows of M are independent given all of B.  Rank r owns
+  rows [r * M / g, (r + 1) * M / g) of A and of C; B is replicated.  There is no
+  collective on the data path.
+* scan: rank r owns the r-th contiguous chunk.  The only exchange is one
+  all-gather of one uint32 total per rank.  Two schedules are offered:
+    "reduce_then_scan"  (default) total of the chunk (4 B/element read), all-gather,
+                        then ONE scan pass whose first tile starts from the sum of the
+                        lower ranks' totals (8 B/element): 12 B/element per rank;
+    "scan_then_carry"   local scan (8 B/element), all-gather of the last elements,
+                        carry-add pass (8 B/element): 16 B/element per rank.
+  Both produce the scan of the concatenated array, bit for bit.
+
+The reference has no multi-GPU code; its scan harness works on one device
+(evals/4090_scan/main.cu:96-128).
+"""
+from __future__ import annotations
+
+from typing import Any
+
+import torch
+import torch.distributed as dist
+
+
+def chunk_bounds(n: int, world: int, rank: int, align: int = 4) -> tuple[int, int]:
+    """Contiguous chunk [lo, hi) of rank `rank`; interior boundaries are multiples of `align`
+    (16-byte alignment of every shard start for uint32 data)."""
+    if world <= 0 or not (0 <= rank < world):
+        raise ValueError(f"bad rank {rank} of {world}")
+    per = -(-n // world)            # ceil
+    per = -(-per // align) * align  # round up to the alignment
+    lo = min(n, rank * per)
+    hi = min(n, (rank + 1) * per)
+    return lo, hi
+
+
+def row_shard(M: int, world: int, rank: int, tile: int = 128) -> tuple[int, int]:
+    """Rows [lo, hi) of A and C owned by `rank`; M / world must be a multiple of the M tile."""
+    if M % world or (M // world) % tile:
+        raise ValueError(f"M={M} does not split into {world} shards of a multiple of {tile} rows")
+    per = M // world
+    return rank * per, (rank + 1) * per
+
+
+class _CudaOps:
+    """The real kernels (C ABI).  Tests on CPU pass a stand-in with the same four methods."""
+
+    def __init__(self):
+        import prism_b200 as pb
+        self._pb = pb
+
+    def workspace(self, n, device):
+        return self._pb.scan_workspace(n, device)
+
+    def reduce_u32(self, x, total):
+        self._pb.reduce_u32(x, total)
+
+    def scan_seeded_(self, x, workspace, totals, rank):
+        self._pb.scan_seeded_(x, workspace, totals, rank)
+
+    def scan_(self, x, workspace):
+        self._pb.launch_scan(x.numel(), x, workspace)
+
+    def scan_add_carry_(self, x, totals, rank):
+        self._pb.scan_add_carry_(x, totals, rank)
+
+
+class ShardedScan:
+    """In-place inclusive scan of an array cut into one contiguous chunk per rank."""
+
+    SCHEDULES = ("reduce_then_scan", "scan_then_carry")
+
+    def __init__(self, n_local: int, device, group: Any = None, schedule: str = "reduce_then_scan", ops: Any = None):
+        if schedule not in self.SCHEDULES:
+            raise ValueError(f"schedule must be one of {self.SCHEDULES}")
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.schedule = schedule
+        self.ops = ops if ops is not None else _CudaOps()
+        self.n_local = n_local
+        self.workspace = self.ops.workspace(n_local, device)
+        self.total = torch.zeros(1, dtype=torch.int32, device=device)
+        self.totals = torch.zeros(self.world, dtype=torch.int32, device=device)
+
+    def _exchange(self, total: torch.Tensor) -> None:
+        if self.world == 1:
+            self.totals.copy_(total)
+        else:
+            dist.all_gather_into_tensor(self.totals, total, group=self.group)
+
+    def __call__(self, x_local: torch.Tensor) -> torch.Tensor:
+        if x_local.numel() != self.n_local:
+            raise ValueError(f"shard has {x_local.numel()} elements, planned for {self.n_local}")
+        if self.schedule == "reduce_then_scan":
+            if self.world > 1:
+                self.ops.reduce_u32(x_local, self.total)
+                self._exchange(self.total)
+            self.ops.scan_seeded_(x_local, self.workspace, self.totals, self.rank)
+        else:
+            self.ops.scan_(x_local, self.workspace)
+            if self.world > 1:
+                # After a local inclusive scan the last element is the chunk total.
+                last = x_local[-1:] if self.n_local else self.total.zero_()
+                self._exchange(last.view(torch.int32) if last.dtype != torch.int32 else last)
+                self.ops.scan_add_carry_(x_local, self.totals, self.rank)
+        return x_local
+
+    def totals_int64(self) -> list[int]:
+        """Per-rank totals as non-negative Python ints (for the host-side overflow check)."""
+        return [int(v) & 0xFFFFFFFF for v in self.totals.cpu().tolist()]
+
+
+class RowShardedGemmBF16:
+    """C = A @ B.T with A and C cut by rows of M; each rank computes its own rows, no collective.
+
+    The rank's C shard is its own column-major (M / g) x N buffer, i.e. an (N, M / g)
+    row-major tensor, as the single-GPU kernel writes it.
+    """
+
+    def __init__(self, M: int, N: int, K: int, group: Any = None):
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.lo, self.hi = row_shard(M, self.world, self.rank)
+        self.M, self.N, self.K = M, N, K
+
+    @property
+    def rows(self) -> int:
+        return self.hi - self.lo
+
+    def __call__(self, A_local: torch.Tensor, B: torch.Tensor, C_local: torch.Tensor) -> torch.Tensor:
+        import prism_b200 as pb
+        pb.runmyh100(self.rows, self.N, self.K, A_local, B, C_local)
+        return C_local
+
+
+class RowShardedSgemm:
+    """C = alpha * A @ B + beta * C with A and C cut by rows of M; no collective."""
+
+    def __init__(self, M: int, N: int, K: int, group: Any = None, kernel: int = 5):
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.lo, self.hi = row_shard(M, self.world, self.rank)
+        self.M, self.N, self.K, self.kernel = M, N, K, kernel
+
+    @property
+    def rows(self) -> int:
+        return self.hi - self.lo
+
+    def __call__(self, alpha: float, A_local: torch.Tensor, B: torch.Tensor, beta: float,
+                 C_local: torch.Tensor) -> torch.Tensor:
+        import prism_b200 as pb
+        pb.run_my_kernel(self.kernel, self.rows, self.N, self.K, alpha, A_local, B, beta, C_local)
+        return C_local

@@ -1,0 +1,107 @@
+"""GPU parity of the bf16 GEMM through the C ABI: against fp64 NumPy on the
+bf16-rounded inputs, |D - D_ref| <= 1e-2 |D_ref| + 1e-2 rms(D_ref), in the
+reference's column-major C layout."""
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+sys.path.insert(0, str(ROOT))
+from oracle import cpu_oracle as O  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _dev(bits):
+    return torch.from_numpy(bits.view(np.int16)).to(DEV).view(torch.bfloat16)
+
+
+def _run(pb, A_bits, B_bits):
+    M, K = A_bits.shape
+    N = B_bits.shape[0]
+    c = torch.full((N, M), float("nan"), dtype=torch.bfloat16, device=DEV)  # every element must be written
+    pb.runmyh100(M, N, K, _dev(A_bits), _dev(B_bits), c)
+    torch.cuda.synchronize()
+    return c.view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+# Smallest tile, one of each tile width, several k-blocks (ring wrap), several tiles per CTA,
+# non-square, and sizes where M only divides the 128-wide tile.
+SHAPES = [(128, 128, 64), (256, 128, 64), (128, 128, 512), (256, 256, 1024), (384, 256, 320), (512, 1024, 256),
+          (1024, 512, 2048), (2048, 2048, 2048), (128, 4096, 128), (4096, 128, 192)]
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+def test_matches_fp64_oracle(pb, shape):
+    M, N, K = shape
+    A, B = O.gemm_bf16_inputs(M, N, K, seed=M * 7 + N * 3 + K)
+    out = _run(pb, A, B)
+    ok, worst = O.gemm_bf16_check(out, O.gemm_bf16_cpu(A, B))
+    assert ok, f"worst error / bound = {worst}"
+
+
+def test_layout_is_column_major_and_exact_on_small_integers(pb):
+    """Integer-valued inputs with small K: every product and sum is exact in fp32 and in bf16,
+    so the result must equal the oracle bit for bit, which also pins the C[n * M + m] layout."""
+    M, N, K = 256, 384, 64
+    rng = np.random.default_rng(1)
+    A = O.f32_to_bf16_bits(rng.integers(-2, 3, (M, K)).astype(np.float32))
+    B = O.f32_to_bf16_bits(rng.integers(-2, 3, (N, K)).astype(np.float32))
+    out = _run(pb, A, B)
+    ref = O.gemm_bf16_cpu(A, B)
+    assert np.array_equal(O.bf16_bits_to_f32(out).reshape(N, M), ref.astype(np.float32))
+
+
+def test_many_tiles_per_cta_4096(pb):
+    """4096^3: 512 tiles over 148 CTAs -> several tiles per CTA, both accumulators and every ring stage reused.
+    Checked on sampled rows in fp64 and against the full-size property C(A, B)^T == C(B, A)."""
+    S = 4096
+    A, B = O.gemm_bf16_inputs(S, S, S, seed=4096)
+    out = O.bf16_bits_to_f32(_run(pb, A, B)).reshape(S, S)          # [n, m]
+    swapped = O.bf16_bits_to_f32(_run(pb, B, A)).reshape(S, S)      # [m, n]
+    assert np.array_equal(out, swapped.T)
+    rows = [0, 1, 127, 128, 129, 2047, 2048, 4095]
+    a = O.bf16_bits_to_f32(A).astype(np.float64)
+    b = O.bf16_bits_to_f32(B).astype(np.float64)
+    ref = b[rows] @ a.T                                               # [n in rows, m]
+    rms = float(np.sqrt(np.mean(ref * ref)))
+    assert np.all(np.abs(out[rows] - ref) <= 1e-2 * np.abs(ref) + 1e-2 * rms)
+
+
+def test_agrees_with_cublas_like_the_reference_harness(pb):
+    """The reference harness accepts |kernel - cuBLAS| <= 0.1 (evals/h100_bench/main.cu:43-55); same check here."""
+    M, N, K = 1024, 1024, 1024
+    A, B = O.gemm_bf16_inputs(M, N, K, seed=2)
+    out = O.bf16_bits_to_f32(_run(pb, A, B)).reshape(N, M)
+    lib = (_dev(B).float() @ _dev(A).float().t()).cpu().numpy()
+    assert np.max(np.abs(out - lib)) <= 0.1
+
+
+def test_rejects_unsupported_shapes_and_alignment(pb):
+    a = torch.zeros(128 * 64 + 8, dtype=torch.bfloat16, device=DEV)
+    c = torch.zeros(128 * 128, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(pb.PrismB200Error) as e:
+        pb.runmyh100(100, 128, 64, a, a, c)
+    assert e.value.code == 2
+    with pytest.raises(pb.PrismB200Error) as e:
+        pb.runmyh100(128, 128, 32, a, a, c)
+    assert e.value.code == 2
+    with pytest.raises(pb.PrismB200Error) as e:
+        pb.runmyh100(128, 128, 64, a[1:], a, c)
+    assert e.value.code == 3
+    pb.clear_error()
+
+
+def test_new_buffer_same_shape_is_not_served_a_stale_map(pb):
+    """The reference caches its tensor maps on M alone (evals/h100_bench/utils.cuh:512-518)."""
+    M = N = K = 256
+    A1, B1 = O.gemm_bf16_inputs(M, N, K, seed=10)
+    A2, B2 = O.gemm_bf16_inputs(M, N, K, seed=11)
+    o1 = _run(pb, A1, B1)
+    o2 = _run(pb, A2, B2)
+    assert O.gemm_bf16_check(o1, O.gemm_bf16_cpu(A1, B1))[0]
+    assert O.gemm_bf16_check(o2, O.gemm_bf16_cpu(A2, B2))[0]

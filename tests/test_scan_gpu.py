@@ -1,0 +1,131 @@
+"""GPU parity of the scan: C ABI vs the CPU oracle, the golden fixture and the
+reference's own scan_kernel recompiled for sm_100.  Bit-exact everywhere."""
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+sys.path.insert(0, str(ROOT))
+from oracle import cpu_oracle as O  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _run(pb, x_np):
+    x = torch.from_numpy(x_np.view(np.int32).copy()).to(DEV)
+    ws = pb.scan_workspace(x.numel(), DEV)
+    ws.fill_(0xAB)  # the workspace may hold anything on entry
+    pb.launch_scan(x.numel(), x, ws)
+    torch.cuda.synchronize()
+    return x.cpu().numpy().view(np.uint32)
+
+
+# Sizes: empty, below one vector, ragged, the reference's correctness sizes
+# (evals/4090_scan/main.cu:97-103: 16384, 32768, 2^20, 2^24, 2^26) and config #2 (2^24, values < 16).
+@pytest.mark.parametrize("n", [0, 1, 3, 4, 5, 127, 128, 4095, 4096, 4097, 8191, 16384, 32768, 100003,
+                               1 << 20, (1 << 20) + 1, 1 << 24])
+def test_scan_matches_oracle(pb, n):
+    x = O.scan_inputs(n, seed=1000 + n % 97, high=16)
+    assert np.array_equal(_run(pb, x), O.scan_cpu(x))
+
+
+def test_scan_reference_harness_values(pb):
+    x = O.scan_inputs(1 << 22, seed=0xCA7CAFE, high=101)  # uniform 0..100, scan_harness.cuh:172
+    assert np.array_equal(_run(pb, x), O.scan_cpu(x))
+
+
+def test_scan_wraparound(pb):
+    x = O.scan_inputs((1 << 18) + 77, seed=5, high=0xFFFFFFFF)
+    assert np.array_equal(_run(pb, x), O.scan_cpu(x))
+
+
+def test_scan_golden_fixture(pb):
+    g = np.load(ROOT / "tests" / "golden" / "scan_ref_cpu.npz")
+    for key in ("small", "tile", "ragged", "wrap"):
+        assert np.array_equal(_run(pb, g[key + "_in"]), g[key + "_out"]), key
+
+
+def test_scan_uint32_dtype_and_workspace_reuse(pb):
+    n = (1 << 16) + 9
+    ws = pb.scan_workspace(n, DEV)
+    for seed in range(3):  # same workspace, back to back, no host re-arming
+        x_np = O.scan_inputs(n, seed=seed, high=1 << 20)
+        x = torch.from_numpy(x_np.view(np.int32).copy()).to(DEV).view(torch.uint32)
+        pb.launch_scan(n, x, ws)
+        assert np.array_equal(x.view(torch.int32).cpu().numpy().view(np.uint32), O.scan_cpu(x_np))
+
+
+def test_scan_2_26_largest_reference_correctness_size(pb):
+    n = 1 << 26
+    g = torch.Generator(device=DEV).manual_seed(26)
+    x = torch.randint(0, 101, (n,), dtype=torch.int32, device=DEV, generator=g)
+    x_np = x.cpu().numpy().view(np.uint32)
+    pb.scan_(x)
+    assert np.array_equal(x.cpu().numpy().view(np.uint32), O.scan_cpu(x_np))
+
+
+def test_scan_2_28_properties(pb):
+    """Benchmark size: values in {0,1}; checked by properties that need no CPU pass over
+    the array: last element = int64 total, differences reproduce the input, monotone."""
+    n = 1 << 28
+    g = torch.Generator(device=DEV).manual_seed(28)
+    x = torch.randint(0, 2, (n,), dtype=torch.int32, device=DEV, generator=g)
+    inp = x.clone()
+    total = int(inp.sum(dtype=torch.int64))
+    pb.scan_(x)
+    assert int(x[-1]) == total
+    assert int(x[0]) == int(inp[0])
+    assert torch.equal(x[1:] - x[:-1], inp[1:])
+    # and against a sample of oracle values: the prefix at a few tile boundaries
+    xs = x[: 1 << 22].cpu().numpy().view(np.uint32)
+    assert np.array_equal(xs, O.scan_cpu(inp[: 1 << 22].cpu().numpy().view(np.uint32)))
+
+
+@pytest.mark.parametrize("n", [16384, 32768, 1 << 20, 1 << 24])
+def test_scan_matches_reference_kernel(pb, ref_gpu, n):
+    """Side by side with the reference's generated scan_kernel (recompiled for sm_100)."""
+    x_np = O.scan_inputs(n, seed=n & 0xFFFF, high=16)
+    mine = _run(pb, x_np)
+    xr = torch.from_numpy(x_np.view(np.int32).copy()).to(DEV)
+    ws = torch.empty(ref_gpu.ref_scan_workspace_size(n), dtype=torch.uint8, device=DEV)
+    torch.cuda.synchronize()
+    assert ref_gpu.ref_scan(n, xr.data_ptr(), ws.data_ptr()) == 0
+    torch.cuda.synchronize()
+    assert np.array_equal(mine, xr.cpu().numpy().view(np.uint32))
+
+
+def test_sharded_pieces_compose(pb):
+    """reduce + seeded scan, and scan + carry add, over 3 uneven chunks on one GPU equal the full scan."""
+    full = O.scan_inputs(300007, seed=8, high=1 << 30)
+    cuts = [0, 100000, 100000, 233336, 300007]  # includes an empty chunk
+    expect = O.scan_cpu(full)
+    totals = torch.zeros(len(cuts) - 1, dtype=torch.int32, device=DEV)
+    chunks = []
+    for r in range(len(cuts) - 1):
+        c = torch.from_numpy(full[cuts[r]:cuts[r + 1]].view(np.int32).copy()).to(DEV)
+        pb.reduce_u32(c, totals[r:r + 1])
+        chunks.append(c)
+    torch.cuda.synchronize()
+    tot_np = totals.cpu().numpy().view(np.uint32)
+    for r in range(len(cuts) - 1):
+        assert int(tot_np[r]) == int(full[cuts[r]:cuts[r + 1]].sum(dtype=np.uint64)) & 0xFFFFFFFF
+    for r, c in enumerate(chunks):
+        a = c.clone()
+        pb.scan_seeded_(a, pb.scan_workspace(a.numel(), DEV), totals, r)
+        b = c.clone()
+        pb.scan_(b)
+        pb.scan_add_carry_(b, totals, r)
+        assert np.array_equal(a.cpu().numpy().view(np.uint32), expect[cuts[r]:cuts[r + 1]]), r
+        assert np.array_equal(b.cpu().numpy().view(np.uint32), expect[cuts[r]:cuts[r + 1]]), r
+
+
+def test_scan_rejects_misaligned(pb):
+    x = torch.zeros(1024, dtype=torch.int32, device=DEV)
+    with pytest.raises(pb.PrismB200Error) as e:
+        pb.launch_scan(1000, x[1:], pb.scan_workspace(1000, DEV))
+    assert e.value.code == 3
+    pb.clear_error()

@@ -1,0 +1,131 @@
+"""GPU parity of the SGEMM family through the C ABI: against fp64 NumPy (norm-wise
+relative error <= 1e-5), against the reference's kernels recompiled for sm_100,
+and against the GPU-generated fixture."""
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+sys.path.insert(0, str(ROOT))
+from oracle import cpu_oracle as O  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+KERNELS = [1, 2, 3, 4, 5, 6]
+
+
+def _run(pb, k, alpha, A, B, beta, C):
+    a, b, c = (torch.from_numpy(t).to(DEV) for t in (A, B, C))
+    pb.run_my_kernel(k, A.shape[0], B.shape[1], A.shape[1], alpha, a, b, beta, c)
+    torch.cuda.synchronize()
+    return c.cpu().numpy()
+
+
+@pytest.mark.parametrize("k", KERNELS)
+def test_config1_1024_alpha1_beta0(pb, k):
+    """M=N=K=1024, alpha=1, beta=0, C zero-initialised."""
+    A, B, C = O.sgemm_inputs(1024, 1024, 1024, seed=1, zero_c=True)
+    out = _run(pb, k, 1.0, A, B, 0.0, C)
+    assert O.sgemm_rel_error(out, O.sgemm_cpu(1.0, A, B, 0.0, C)) <= O.SGEMM_TOL
+
+
+@pytest.mark.parametrize("k", KERNELS)
+def test_config3_1024_alpha15_beta05(pb, k):
+    A, B, C = O.sgemm_inputs(1024, 1024, 1024, seed=3)
+    out = _run(pb, k, 1.5, A, B, 0.5, C)
+    assert O.sgemm_rel_error(out, O.sgemm_cpu(1.5, A, B, 0.5, C)) <= O.SGEMM_TOL
+
+
+@pytest.mark.parametrize("k", [4, 5])
+def test_config3_2048(pb, k):
+    A, B, C = O.sgemm_inputs(2048, 2048, 2048, seed=32)
+    out = _run(pb, k, 1.5, A, B, 0.5, C)
+    assert O.sgemm_rel_error(out, O.sgemm_cpu(1.5, A, B, 0.5, C)) <= O.SGEMM_TOL
+
+
+@pytest.mark.parametrize("shape", [(128, 128, 32), (128, 256, 64), (256, 128, 96), (384, 640, 160), (128, 128, 4096)])
+def test_kernel5_tile_edges(pb, shape):
+    M, N, K = shape
+    A, B, C = O.sgemm_inputs(M, N, K, seed=M + N + K)
+    out = _run(pb, 5, -0.75, A, B, 2.0, C)
+    assert O.sgemm_rel_error(out, O.sgemm_cpu(-0.75, A, B, 2.0, C)) <= O.SGEMM_TOL
+
+
+def test_kernel5_scalar_and_packed_fma_agree(pb, monkeypatch):
+    """fma.rn.f32x2 is two independent fp32 FMAs: both forms of kernel 5 must agree bit for bit.
+    (The scalar form is selected by an environment variable read at first use, so it is run in a child.)"""
+    import subprocess
+    code = (
+        "import sys, numpy as np, torch; sys.path.insert(0, %r)\n"
+        "import prism_b200 as pb\n"
+        "from oracle import cpu_oracle as O\n"
+        "A,B,C = O.sgemm_inputs(256, 384, 512, seed=11)\n"
+        "a,b,c = (torch.from_numpy(t).cuda() for t in (A,B,C))\n"
+        "pb.run_my_kernel(5, 256, 384, 512, 1.5, a, b, 0.5, c); torch.cuda.synchronize()\n"
+        "np.save(sys.argv[1], c.cpu().numpy())\n" % str(ROOT))
+    outs = []
+    for scalar in ("0", "1"):
+        path = f"/tmp/prism_b200_k5_{scalar}.npy"
+        env = dict(**__import__("os").environ, PRISM_B200_SGEMM_SCALAR=scalar)
+        subprocess.run([sys.executable, "-c", code, path], check=True, env=env, timeout=300)
+        outs.append(np.load(path))
+    assert np.array_equal(outs[0], outs[1])
+
+
+@pytest.mark.parametrize("k", KERNELS)
+@pytest.mark.parametrize("shape", [(1, 1, 1), (33, 65, 17), (100, 130, 50), (129, 127, 31), (64, 64, 0)])
+def test_ragged_shapes_every_kernel(pb, k, shape):
+    """Shapes no tile divides, and K = 0 (C = beta * C)."""
+    M, N, K = shape
+    A, B, C = O.sgemm_inputs(M, N, max(K, 1), seed=7)
+    A, B = A[:, :K].copy(), B[:K].copy()
+    out = _run(pb, k, 1.5, A, B, 0.5, C)
+    assert O.sgemm_rel_error(out, O.sgemm_cpu(1.5, A, B, 0.5, C)) <= O.SGEMM_TOL
+
+
+def test_linearity_at_4096(pb):
+    """Benchmark size, checked without an fp64 4096^3 product: rows sampled against fp64, plus
+    C(alpha=2, beta=0) == 2 * C(alpha=1, beta=0) exactly (scaling by 2 is exact in fp32)."""
+    S = 4096
+    A, B, C = O.sgemm_inputs(S, S, S, seed=4096, zero_c=True)
+    a, b = torch.from_numpy(A).to(DEV), torch.from_numpy(B).to(DEV)
+    c1 = torch.zeros(S, S, device=DEV)
+    c2 = torch.zeros(S, S, device=DEV)
+    pb.run_my_kernel(5, S, S, S, 1.0, a, b, 0.0, c1)
+    pb.run_my_kernel(5, S, S, S, 2.0, a, b, 0.0, c2)
+    torch.cuda.synchronize()
+    assert torch.equal(c2, 2.0 * c1)
+    rows = [0, 1, 127, 128, 2047, 4095]
+    ref = A[rows].astype(np.float64) @ B.astype(np.float64)
+    got = c1[rows].cpu().numpy()
+    assert O.sgemm_rel_error(got, ref) <= O.SGEMM_TOL
+
+
+@pytest.mark.parametrize("k", [1, 2, 3, 4, 5])
+def test_matches_reference_kernels(pb, ref_gpu, k):
+    """Side by side with the reference's generated kernel k (recompiled for sm_100, harness launch geometry)."""
+    M = N = K = 512
+    A, B, C = O.sgemm_inputs(M, N, K, seed=50 + k)
+    mine = _run(pb, k, 1.5, A, B, 0.5, C)
+    a, b, c = (torch.from_numpy(t).to(DEV) for t in (A, B, C))
+    torch.cuda.synchronize()
+    assert ref_gpu.ref_sgemm(k, M, N, K, 1.5, a.data_ptr(), b.data_ptr(), 0.5, c.data_ptr()) == 0
+    torch.cuda.synchronize()
+    theirs = c.cpu().numpy()
+    ref64 = O.sgemm_cpu(1.5, A, B, 0.5, C)
+    assert O.sgemm_rel_error(theirs, ref64) <= O.SGEMM_TOL      # the reference itself meets the bound
+    assert O.sgemm_rel_error(mine, ref64) <= O.SGEMM_TOL
+    assert O.sgemm_rel_error(mine, theirs.astype(np.float64)) <= 2 * O.SGEMM_TOL
+
+
+def test_golden_fixture_from_reference_kernels(pb):
+    path = ROOT / "tests" / "golden" / "sgemm_ref_gpu.npz"
+    if not path.exists():
+        pytest.skip("GPU-generated fixture not present")
+    g = np.load(path)
+    for k in (1, 2, 3, 4, 5):
+        out = _run(pb, k, float(g["alpha"]), g["A"], g["B"], float(g["beta"]), g["C"].copy())
+        assert O.sgemm_rel_error(out, g[f"out_k{k}"].astype(np.float64)) <= 2 * O.SGEMM_TOL, k

@@ -1,0 +1,553 @@
+#!/usr/bin/env python3
+"""Benchmark of the prism_b200 hot path on one node.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload gemm_bf16|sgemm|scan] [--no-extras]
+
+Prints ONE JSON line.  The headline workload is the bf16 GEMM D = A * B^T at
+M = N = K = 8192 (rows of M sharded over the GPUs, B replicated; total work
+fixed, so scaling is "strong"); `--workload` selects the FP32 SGEMM (4096^3,
+alpha = 1.5, beta = 0.5) or the uint32 scan (2^28 on one GPU, 2^30 sharded)
+instead.  With the default workload the line also carries the other two
+families under "extras" (one GPU: kernel timings, roofline fractions, the
+reference's own kernels recompiled for sm_100 timed beside ours).
+
+A "step" is one launch of the path through the C ABI on inputs resident in HBM;
+steps are timed with CUDA events on the launching stream, the job time is the
+maximum over ranks.  "e2e" repeats the measurement through the host-buffer
+operators (pinned host memory -> device -> kernel -> host inside the timed
+region).  `--impl reference` times the CPU path (NumPy, all host threads) on a
+bounded sample of the same workload; under torchrun only rank 0 does so.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+GEMM_S = 8192
+SGEMM_S = 4096
+SCAN_N1 = 1 << 28
+SCAN_NG = 1 << 30
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel,
+# from the ncu captures summarised under profiles/ (None = not captured).
+NCU_TRAFFIC_BYTES = {"gemm_bf16": None, "sgemm": None, "scan": None}
+
+
+def load_peaks() -> dict:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        d["source"] = "measured"
+        return d
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "sm_max_mhz": 1965.0,
+            "source": "fallback"}
+
+
+# --------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Samples nvidia-smi while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines: list[str] = []
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        def pump():
+            for line in self.proc.stdout:
+                self.lines.append(line.strip())
+        self.thread = threading.Thread(target=pump, daemon=True)
+        self.thread.start()
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, power, reasons = [], None, [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [t.strip() for t in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); smax = float(f[2]); power.append(float(f[3]))
+            except ValueError:
+                continue
+            for nm, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(nm)
+        sm.sort()
+        # the busiest half of the samples = the samples under load
+        load = sm[len(sm) // 2:] if sm else []
+        return {"sm_mhz": (load[len(load) // 2] if load else None), "sm_max_mhz": smax,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# --------------------------------------------------------------------------- helpers
+def dist_setup(n_gpus: int):
+    import torch
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    return world, rank, local
+
+
+def barrier(world):
+    import torch
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def max_over_ranks(value: float, world: int) -> float:
+    if world == 1:
+        return value
+    import torch
+    import torch.distributed as dist
+    t = torch.tensor([value], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def time_steps(step, steps: int, warmup: int, world: int, reset=None):
+    """Per-step CUDA-event timing on the current stream; returns (total_ms_max_over_ranks, per_step_ms list)."""
+    import torch
+    for _ in range(warmup):
+        if reset:
+            reset()
+        step()
+    barrier(world)
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    for i in range(steps):
+        if reset:
+            reset()          # outside the timed span of the step
+        starts[i].record()
+        step()
+        ends[i].record()
+    barrier(world)
+    per = [s.elapsed_time(e) for s, e in zip(starts, ends)]
+    return max_over_ranks(sum(per), world), per
+
+
+def ref_gpu_lib():
+    p = ROOT / "oracle" / "_ref" / "libprism_ref.so"
+    if not p.exists():
+        return None
+    lib = ctypes.CDLL(str(p))
+    lib.ref_sgemm.argtypes = [ctypes.c_int] * 4 + [ctypes.c_float, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_float,
+                                                   ctypes.c_void_p]
+    lib.ref_scan_workspace_size.argtypes = [ctypes.c_size_t]
+    lib.ref_scan_workspace_size.restype = ctypes.c_size_t
+    lib.ref_scan.argtypes = [ctypes.c_size_t, ctypes.c_void_p, ctypes.c_void_p]
+    return lib
+
+
+# --------------------------------------------------------------------------- workloads (ours)
+def run_gemm_bf16(args, world, rank, peaks):
+    import torch
+    import prism_b200 as pb
+    from prism_b200 import host, sharded
+    dev = torch.device("cuda", torch.cuda.current_device())
+    S = GEMM_S
+    plan = sharded.RowShardedGemmBF16(S, S, S)
+    rows = plan.rows
+    g = torch.Generator(device=dev).manual_seed(1234)           # B: same on every rank
+    B = (torch.randn((S, S), device=dev, generator=g) * 0.1).to(torch.bfloat16)
+    ga = torch.Generator(device=dev).manual_seed(5678 + rank)   # A: this rank's rows
+    A = (torch.randn((rows, S), device=dev, generator=ga) * 0.1).to(torch.bfloat16)
+    C = torch.empty((S, rows), dtype=torch.bfloat16, device=dev)
+
+    sampler = ClockSampler(torch.cuda.current_device())
+    sampler.start()
+    l0 = pb.launch_count()
+    total_ms, per = time_steps(lambda: plan(A, B, C), args.steps, args.warmup, world)
+    launches = (pb.launch_count() - l0) - args.warmup
+    clocks = sampler.stop()
+    ms = total_ms / args.steps
+    flops = 2.0 * S * S * S
+    value = flops / (ms * 1e-3) / 1e12
+
+    # spot check of this rank's result against fp64 on a few rows/columns (bf16-rounded inputs)
+    n_idx = [0, 1, 4095, S - 1]
+    ref = (B[n_idx].double() @ A.double().t()).cpu()
+    got = C[n_idx].double().cpu()
+    rms = float(ref.pow(2).mean().sqrt())
+    ok = bool(((got - ref).abs() <= 1e-2 * ref.abs() + 1e-2 * rms).all())
+
+    # end to end through the host-buffer operator
+    op = host.HostGemmBF16(rows, S, S, dev)
+    Ah = A.cpu().pin_memory(); Bh = B.cpu().pin_memory()
+    Ch = torch.empty((S, rows), dtype=torch.bfloat16).pin_memory()
+    e2e_steps = max(3, min(args.steps, 5))
+    e2e_total, _ = time_steps(lambda: op(Ah, Bh, Ch), e2e_steps, 1, world)
+    e2e_ms = e2e_total / e2e_steps
+    e2e = {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+           "h2d_bytes_per_step": op.h2d_bytes, "d2h_bytes_per_step": op.d2h_bytes}
+
+    kernel_ms = sum(per) / len(per)     # this rank's kernel: rows x S x S
+    achieved = 2.0 * rows * S * S / (kernel_ms * 1e-3) / 1e12
+    peak = peaks["bf16_tflops"]
+    roofline = {"bound": "tensor", "kernel": "cutlass_my_h100_match_no_tail<256> (tcgen05)", "achieved": achieved,
+                "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                "peak_source": f"{peaks['source']} cuBLAS bf16 burst", "frac_of_sustained": achieved / peaks["bf16_tflops_sustained"],
+                "frac_of_nominal_2250": achieved / 2250.0,
+                "traffic": NCU_TRAFFIC_BYTES["gemm_bf16"]}
+    line = {"metric": "bf16 GEMM TFLOP/s (D = A*B^T, M=N=K=8192, fp32 accumulate, bf16 out)", "value": value,
+            "unit": "TFLOP/s", "ms_per_step": ms, "scaling": "strong", "dtype": "bf16",
+            "config": {"workload": "gemm_bf16 8192x8192x8192, A and B K-major, C column-major, values 0.1*normal bf16",
+                       "M": S, "N": S, "K": S, "sharding": f"rows of M over {world} GPU(s), B replicated, no collective",
+                       "rows_per_gpu": rows, "l2": "inputs larger than L2 (A+B = %d MiB per GPU)" % ((rows + S) * S * 2 >> 20)},
+            "roofline": roofline, "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "spot_check_ok": ok}
+    return line
+
+
+def run_sgemm(args, world, rank, peaks, steps=None, warmup=None):
+    import torch
+    import prism_b200 as pb
+    from prism_b200 import host, sharded
+    steps = steps or args.steps
+    warmup = warmup or args.warmup
+    dev = torch.device("cuda", torch.cuda.current_device())
+    S = SGEMM_S
+    plan = sharded.RowShardedSgemm(S, S, S, kernel=5)
+    rows = plan.rows
+    g = torch.Generator(device=dev).manual_seed(4321)
+    B = torch.rand((S, S), device=dev, generator=g) * 2 - 1
+    ga = torch.Generator(device=dev).manual_seed(8765 + rank)
+    A = torch.rand((rows, S), device=dev, generator=ga) * 2 - 1
+    C0 = torch.rand((rows, S), device=dev, generator=ga) * 2 - 1
+    C = C0.clone()
+    sampler = ClockSampler(torch.cuda.current_device())
+    sampler.start()
+    l0 = pb.launch_count()
+    total_ms, per = time_steps(lambda: plan(1.5, A, B, 0.5, C), steps, warmup, world, reset=lambda: C.copy_(C0))
+    launches = (pb.launch_count() - l0) - warmup
+    clocks = sampler.stop()
+    ms = total_ms / steps
+    flops = 2.0 * S * S * S
+    ridx = [0, 1, rows // 2, rows - 1]
+    ref = 1.5 * (A[ridx].double() @ B.double()) + 0.5 * C0[ridx].double()
+    err = float((C[ridx].double() - ref).abs().max() / ref.abs().max())
+
+    op = host.HostSgemm(rows, S, S, dev)
+    Ah, Bh, Ch = A.cpu().pin_memory(), B.cpu().pin_memory(), C0.cpu().pin_memory()
+    e2e_steps = 3
+    e2e_total, _ = time_steps(lambda: op(1.5, Ah, Bh, 0.5, Ch), e2e_steps, 1, world)
+    e2e_ms = e2e_total / e2e_steps
+
+    kernel_ms = sum(per) / len(per)
+    achieved = 2.0 * rows * S * S / (kernel_ms * 1e-3) / 1e12
+    sm_max = peaks.get("sm_max_mhz", 1965.0)
+    peak_nominal = 148 * 128 * 2 * sm_max * 1e6 / 1e12
+    sm_load = clocks.get("sm_mhz") or sm_max
+    peak_at_clock = 148 * 128 * 2 * sm_load * 1e6 / 1e12
+    return {"metric": "FP32 SGEMM TFLOP/s (C = 1.5*A*B + 0.5*C, M=N=K=4096, pure FFMA)",
+            "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms, "scaling": "strong", "dtype": "f32",
+            "config": {"workload": "sgemm 4096x4096x4096 row-major, kernel 5, A/B/C uniform[-1,1)", "sharding":
+                       f"rows of M over {world} GPU(s), B replicated, no collective", "rows_per_gpu": rows,
+                       "l2": "C restored from a pristine copy before every step (untimed), which also displaces L2"},
+            "roofline": {"bound": "fp32_ffma", "kernel": "my_sgemm_kernel_5<packed>", "achieved": achieved,
+                         "peak": peak_nominal, "unit": "TFLOP/s", "frac": achieved / peak_nominal,
+                         "peak_source": "148 SMs x 128 FMA/clk x 2 x %.0f MHz (max SM clock)" % sm_max,
+                         "frac_at_observed_clock": achieved / peak_at_clock, "observed_sm_mhz": sm_load,
+                         "traffic": NCU_TRAFFIC_BYTES["sgemm"]},
+            "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": op.h2d_bytes, "d2h_bytes_per_step": op.d2h_bytes},
+            "gpu_launches": launches, "clocks": clocks, "rel_error_sampled_rows": err, "spot_check_ok": err <= 1e-5}
+
+
+def run_scan(args, world, rank, peaks, steps=None, warmup=None):
+    import torch
+    import prism_b200 as pb
+    from prism_b200 import host, sharded
+    steps = steps or args.steps
+    warmup = warmup or args.warmup
+    dev = torch.device("cuda", torch.cuda.current_device())
+    n_total = (1 << args.scan_log2n) if args.scan_log2n else (SCAN_N1 if world == 1 else SCAN_NG)
+    lo, hi = sharded.chunk_bounds(n_total, world, rank)
+    n = hi - lo
+    g = torch.Generator(device=dev).manual_seed(99 + rank)
+    src = torch.randint(0, 2, (n,), dtype=torch.int32, device=dev, generator=g)
+    x = torch.empty_like(src)
+    scan = sharded.ShardedScan(n, dev, schedule=args.scan_schedule)
+    sampler = ClockSampler(torch.cuda.current_device())
+    sampler.start()
+    l0 = pb.launch_count()
+    total_ms, per = time_steps(lambda: scan(x), steps, warmup, world, reset=lambda: x.copy_(src))
+    launches = (pb.launch_count() - l0) - warmup * (1 if world == 1 else 2)
+    clocks = sampler.stop()
+    ms = total_ms / steps
+    nbytes = 8.0 * n_total
+    # properties: differences reproduce the input; last element = carry + int64 total of the shard
+    carry = sum(scan.totals_int64()[:rank]) if world > 1 else 0
+    ok = bool(torch.equal(x[1:] - x[:-1], src[1:])) and (int(x[-1]) & 0xFFFFFFFF) == ((carry + int(src.sum(dtype=torch.int64))) & 0xFFFFFFFF)
+
+    e2e = None
+    if world == 1:
+        op = host.HostScan(n, dev)
+        xh = src.cpu().pin_memory()
+        e2e_total, _ = time_steps(lambda: op(xh), 3, 1, world)
+        e2e_ms = e2e_total / 3
+        e2e = {"value": nbytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_ms,
+               "h2d_bytes_per_step": op.h2d_bytes, "d2h_bytes_per_step": op.d2h_bytes}
+    kernel_ms = sum(per) / len(per)
+    achieved = 8.0 * n / (kernel_ms * 1e-3) / 1e9
+    peak = peaks["hbm_gbs"]
+    return {"metric": "uint32 inclusive scan GB/s (8 bytes per element)", "value": nbytes / (ms * 1e-3) / 1e9,
+            "unit": "GB/s", "ms_per_step": ms, "scaling": "strong" if world > 1 else "weak", "dtype": "u32",
+            "config": {"workload": f"scan n=2^{n_total.bit_length() - 1} int32 values in {{0,1}}, in place",
+                       "sharding": f"contiguous chunks over {world} GPU(s); " +
+                       ("single pass" if world == 1 else f"{args.scan_schedule}: one all-gather of per-shard totals"),
+                       "elements_per_gpu": n, "l2": "input restored from a pristine copy before every step (untimed); array larger than L2"},
+            "roofline": {"bound": "hbm", "kernel": "scan_kernel", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "peak_source": f"{peaks['source']} copy bandwidth",
+                         "frac_of_nominal_8000": achieved / 8000.0,
+                         "note": "8 B/element algorithmic; per-GPU rate of the whole step (all passes)",
+                         "traffic": NCU_TRAFFIC_BYTES["scan"]},
+            "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "spot_check_ok": ok}
+
+
+def reference_kernels_beside(peaks):
+    """The reference's own generated kernels, recompiled for sm_100, on the same inputs and GPU (one GPU)."""
+    import torch
+    lib = ref_gpu_lib()
+    if lib is None:
+        return {"unavailable": "oracle/_ref/libprism_ref.so not built"}
+    dev = torch.device("cuda", torch.cuda.current_device())
+    out = {}
+    S = SGEMM_S
+    A = torch.rand((S, S), device=dev) * 2 - 1
+    B = torch.rand((S, S), device=dev) * 2 - 1
+    C = torch.rand((S, S), device=dev) * 2 - 1
+    ms, _ = time_steps(lambda: lib.ref_sgemm(5, S, S, S, 1.5, A.data_ptr(), B.data_ptr(), 0.5, C.data_ptr()), 5, 2, 1)
+    out["sgemm_4096_my_sgemm_kernel_5_tflops"] = 2.0 * S ** 3 / (ms / 5 * 1e-3) / 1e12
+    del A, B, C
+    n = SCAN_N1
+    src = torch.randint(0, 2, (n,), dtype=torch.int32, device=dev)
+    x = torch.empty_like(src)
+    ws = torch.empty(lib.ref_scan_workspace_size(n), dtype=torch.uint8, device=dev)
+    ms, _ = time_steps(lambda: lib.ref_scan(n, x.data_ptr(), ws.data_ptr()), 5, 2, 1, reset=lambda: x.copy_(src))
+    out["scan_2^28_scan_kernel_gbs"] = 8.0 * n / (ms / 5 * 1e-3) / 1e9
+    out["bf16_gemm"] = "reference kernel is wgmma (sm_90a) only: does not assemble for sm_100"
+    return out
+
+
+# --------------------------------------------------------------------------- CPU arm
+def cpu_gemm_bf16(sample_rows: int, reps: int):
+    import numpy as np
+    from oracle import cpu_oracle as O
+    S = GEMM_S
+    rng = np.random.default_rng(0)
+    A = O.bf16_bits_to_f32(O.f32_to_bf16_bits((0.1 * rng.standard_normal((sample_rows, S))).astype(np.float32)))
+    B = O.bf16_bits_to_f32(O.f32_to_bf16_bits((0.1 * rng.standard_normal((S, S))).astype(np.float32)))
+    best = float("inf")
+    times = []
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        C = B @ A.T      # (N, rows): the reference's column-major C, fp32 accumulate (OpenBLAS sgemm)
+        dt = time.perf_counter() - t0
+        times.append(dt)
+        best = min(best, dt)
+    del C
+    flops = 2.0 * sample_rows * S * S
+    return flops, times
+
+
+def cpu_sgemm(sample_rows: int, reps: int):
+    import numpy as np
+    S = SGEMM_S
+    rng = np.random.default_rng(0)
+    A = rng.uniform(-1, 1, (sample_rows, S)).astype(np.float32)
+    B = rng.uniform(-1, 1, (S, S)).astype(np.float32)
+    C = rng.uniform(-1, 1, (sample_rows, S)).astype(np.float32)
+    times = []
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        C = np.float32(1.5) * (A @ B) + np.float32(0.5) * C
+        times.append(time.perf_counter() - t0)
+    return 2.0 * sample_rows * S * S, times
+
+
+def cpu_scan(n: int, reps: int):
+    import numpy as np
+    from oracle import cpu_oracle as O
+    x = O.scan_inputs(n, seed=0, high=2)
+    times = []
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        O.scan_cpu(x)
+        times.append(time.perf_counter() - t0)
+    return 8.0 * n, times
+
+
+def cpu_threads() -> int:
+    try:
+        from threadpoolctl import threadpool_info
+        n = [p.get("num_threads", 1) for p in threadpool_info() if p.get("user_api") == "blas"]
+        if n:
+            return max(n)
+    except Exception:
+        pass
+    return os.cpu_count() or 1
+
+
+def cpu_baseline(workload: str) -> dict:
+    import numpy as np  # noqa: F401  (loads BLAS so that the thread count can be read)
+    if workload == "gemm_bf16":
+        rows = 2048
+        work, times = cpu_gemm_bf16(rows, 3)
+        return {"value": work / min(times) / 1e12, "unit": "TFLOP/s", "cores": cpu_threads(), "kind": "port",
+                "sample": f"NumPy float32 matmul (BLAS, fp32 accumulate) on the bf16-rounded values, {rows} of the 8192 rows of M "
+                          f"against all of B (N = K = 8192), best of 3; os.cpu_count() = {os.cpu_count()}"}
+    if workload == "sgemm":
+        rows = 2048
+        work, times = cpu_sgemm(rows, 3)
+        return {"value": work / min(times) / 1e12, "unit": "TFLOP/s", "cores": cpu_threads(), "kind": "port",
+                "sample": f"NumPy float32 1.5*A@B+0.5*C, {rows} of the 4096 rows of M, best of 3; os.cpu_count() = {os.cpu_count()}"}
+    n = 1 << 26
+    work, times = cpu_scan(n, 3)
+    return {"value": work / min(times) / 1e9, "unit": "GB/s", "cores": 1, "kind": "port",
+            "sample": f"np.cumsum uint32 (single thread; the same loop as the reference's scan_cpu) on 2^26 of the 2^28 elements, best of 3"}
+
+
+def run_reference_arm(args):
+    """CPU implementation of the path on the host cores; each step is a bounded sample of the workload."""
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return None
+    steps, warmup = args.steps, args.warmup
+    if args.workload == "gemm_bf16":
+        rows = 1024
+        work, times = cpu_gemm_bf16(rows, steps + warmup)
+        unit, scale = "TFLOP/s", 1e12
+        metric = "bf16 GEMM TFLOP/s (D = A*B^T, M=N=K=8192, fp32 accumulate, bf16 out)"
+        sample = f"NumPy float32 matmul on bf16-rounded values; each step = {rows} of the 8192 rows of M against all of B"
+        cfg = {"workload": "gemm_bf16 8192x8192x8192, A and B K-major, C column-major, values 0.1*normal bf16"}
+        dtype, cores = "f32 on bf16-rounded inputs", cpu_threads()
+    elif args.workload == "sgemm":
+        rows = 1024
+        work, times = cpu_sgemm(rows, steps + warmup)
+        unit, scale = "TFLOP/s", 1e12
+        metric = "FP32 SGEMM TFLOP/s (C = 1.5*A*B + 0.5*C, M=N=K=4096, pure FFMA)"
+        sample = f"NumPy float32; each step = {rows} of the 4096 rows"
+        cfg = {"workload": "sgemm 4096x4096x4096 row-major"}
+        dtype, cores = "f32", cpu_threads()
+    else:
+        n = 1 << 25
+        work, times = cpu_scan(n, steps + warmup)
+        unit, scale = "GB/s", 1e9
+        metric = "uint32 inclusive scan GB/s (8 bytes per element)"
+        sample = "np.cumsum uint32, single thread; each step = 2^25 elements"
+        cfg = {"workload": "scan int32 values in {0,1}, in place"}
+        dtype, cores = "u32", 1
+    timed = times[warmup:]
+    ms = 1e3 * sum(timed) / len(timed)
+    value = work / (ms * 1e-3) / scale
+    return {"impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": args.gpus, "steps": steps,
+            "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": dtype, "data": "synthetic", "config": cfg,
+            "cpu_baseline": {"value": value, "unit": unit, "cores": cores, "kind": "port", "sample": sample +
+                             f"; os.cpu_count() = {os.cpu_count()}; the reference has no CPU GEMM and its bf16 kernel cannot "
+                             "run on sm_100, so the CPU path is NumPy as the benchmark definition prescribes"},
+            "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+
+
+# --------------------------------------------------------------------------- main
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--workload", choices=["gemm_bf16", "sgemm", "scan"], default="gemm_bf16")
+    ap.add_argument("--scan-schedule", choices=["reduce_then_scan", "scan_then_carry"], default="reduce_then_scan")
+    ap.add_argument("--scan-log2n", type=int, default=0, help="scan length 2^k (default: 28 on one GPU, 30 sharded)")
+    ap.add_argument("--no-extras", action="store_true", help="skip the other two kernel families and the CPU baseline")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    if args.impl == "reference":
+        line = run_reference_arm(args)
+        if line is not None:
+            print(json.dumps(line), flush=True)
+        return 0
+
+    import torch
+    if not torch.cuda.is_available():
+        print(json.dumps({"error": "no CUDA device: prism_b200 has no CPU path"}))
+        return 1
+    import prism_b200 as pb
+    pb.load(build_if_missing=False)   # the CUDA library must be there; there is nothing to fall back to
+    world, rank, local = dist_setup(args.gpus)
+    peaks = load_peaks()
+    runner = {"gemm_bf16": run_gemm_bf16, "sgemm": run_sgemm, "scan": run_scan}[args.workload]
+    line = runner(args, world, rank, peaks)
+    extras = {}
+    if not args.no_extras and args.workload == "gemm_bf16":
+        # the other two families at every N (sharded the same way), fewer steps
+        extras["sgemm"] = run_sgemm(args, world, rank, peaks, steps=min(args.steps, 5), warmup=3)
+        extras["scan"] = run_scan(args, world, rank, peaks, steps=min(args.steps, 10), warmup=3)
+        if world == 1:
+            extras["reference_kernels_sm100"] = reference_kernels_beside(peaks)
+    code, msg = pb.last_error()
+    if rank == 0:
+        out = {"metric": line.pop("metric"), "value": line.pop("value"), "unit": line.pop("unit"), "n_gpus": world,
+               "steps": args.steps, "warmup": args.warmup, "ms_per_step": line.pop("ms_per_step"), "higher_is_better": True,
+               "scaling": line.pop("scaling"), "vs_baseline": None, "dtype": line.pop("dtype"), "data": "synthetic",
+               "impl": "ours"}
+        out.update(line)
+        if world == 1 and not args.no_extras:
+            out["cpu_baseline"] = cpu_baseline(args.workload)
+            for k in ("sgemm", "scan"):
+                if k in extras:
+                    extras[k]["cpu_baseline"] = cpu_baseline(k)
+        if extras:
+            out["extras"] = extras
+        out["library_status"] = {"code": code, "message": msg}
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0 if code == 0 else 1
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -32,19 +32,19 @@ namespace prism_b200 {
 
 namespace {
 
-constexpr int kScanThreads = 256;
-constexpr int kScanWarps = kScanThreads / 32;
 constexpr uint32_t kStateInvalid = 0u;
 constexpr uint32_t kStateAggregate = 1u;
 constexpr uint32_t kStatePrefix = 2u;
 constexpr uint32_t kMaxPolls = 1u << 20;
 constexpr size_t kHeaderBytes = 128;  // [0] ticket, [1] abort flag; descriptors follow
 
-template <int VEC>
+template <int THREADS, int VEC>
 struct ScanCfg {
+    static constexpr int kThreads = THREADS;
+    static constexpr int kWarps = THREADS / 32;
     static constexpr int kItems = 4 * VEC;                       // elements per thread
     static constexpr int kWarpElems = 32 * kItems;               // contiguous elements per warp
-    static constexpr int kTile = kScanThreads * kItems;          // elements per CTA
+    static constexpr int kTile = THREADS * kItems;               // elements per CTA
 };
 
 __device__ __forceinline__ uint64_t ld_desc(const uint64_t* p) {
@@ -68,9 +68,23 @@ __device__ __forceinline__ uint32_t warp_sum(uint32_t v) {
     return v;
 }
 
-// Sum of the tiles before `tile`, found by walking the descriptors backwards 32
-// at a time until one that already carries an inclusive prefix.  Executed by
+__device__ __forceinline__ uint64_t poll_desc(const uint64_t* p, uint64_t first, const uint32_t* abort_flag) {
+    uint64_t d = first;
+    uint32_t polls = 0;
+    while (static_cast<uint32_t>(d) == kStateInvalid) {
+        if (++polls >= kMaxPolls) break;
+        if ((polls & 1023u) == 0u && ld_flag(abort_flag) != 0u) break;
+        d = ld_desc(p);
+    }
+    return d;
+}
+
+// Sum of the tiles before `tile`, found by walking the records backwards, 32 * NW
+// per probe, until one that already carries an inclusive prefix.  The rate at which
+// prefixes can propagate is (records per probe) x (tile bytes) per L2 round trip, so
+// wide probes and large tiles are what keep this off the critical path.  Executed by
 // one full warp.  *failed is set if a bounded poll ran out or an abort was seen.
+template <int NW>
 __device__ __forceinline__ uint32_t lookback(uint32_t tile, const uint64_t* desc,
                                              const uint32_t* abort_flag, bool* failed) {
     const int lane = threadIdx.x & 31;
@@ -79,37 +93,39 @@ __device__ __forceinline__ uint32_t lookback(uint32_t tile, const uint64_t* desc
     *failed = false;
     while (true) {
         // A slot before tile 0 behaves like a finished tile with prefix 0.
-        uint64_t d = kStatePrefix;
-        if (idx >= 0) {
-            uint32_t polls = 0;
-            while (true) {
-                d = ld_desc(desc + idx);
-                if (static_cast<uint32_t>(d) != kStateInvalid) break;
-                if (++polls >= kMaxPolls) break;
-                if ((polls & 1023u) == 0u && ld_flag(abort_flag) != 0u) break;
+        uint64_t d[NW];
+#pragma unroll
+        for (int w = 0; w < NW; ++w) {
+            const long long i = idx - 32 * w;
+            d[w] = i >= 0 ? ld_desc(desc + i) : static_cast<uint64_t>(kStatePrefix);
+        }
+#pragma unroll
+        for (int w = 0; w < NW; ++w) {
+            const long long i = idx - 32 * w;
+            if (i >= 0) d[w] = poll_desc(desc + i, d[w], abort_flag);
+            const uint32_t state = static_cast<uint32_t>(d[w]);
+            const uint32_t value = static_cast<uint32_t>(d[w] >> 32);
+            if (!__all_sync(0xffffffffu, state != kStateInvalid)) {
+                *failed = true;
+                return exclusive;
             }
+            const unsigned has_prefix = __ballot_sync(0xffffffffu, state == kStatePrefix);
+            if (has_prefix) {
+                const int first = __ffs(has_prefix) - 1;  // nearest predecessor with a prefix
+                exclusive += warp_sum(lane <= first ? value : 0u);
+                return exclusive;
+            }
+            exclusive += warp_sum(value);
         }
-        const uint32_t state = static_cast<uint32_t>(d);
-        const uint32_t value = static_cast<uint32_t>(d >> 32);
-        if (!__all_sync(0xffffffffu, state != kStateInvalid)) {
-            *failed = true;
-            return exclusive;
-        }
-        const unsigned has_prefix = __ballot_sync(0xffffffffu, state == kStatePrefix);
-        if (has_prefix) {
-            const int first = __ffs(has_prefix) - 1;  // nearest predecessor with a prefix
-            exclusive += warp_sum(lane <= first ? value : 0u);
-            return exclusive;
-        }
-        exclusive += warp_sum(value);
-        idx -= 32;
+        idx -= 32 * NW;
     }
 }
 
-template <int VEC, bool SEEDED>
+template <int THREADS, int VEC, int NW, bool SEEDED>
 __device__ __forceinline__ void scan_tile_body(uint32_t n, uint32_t* x, uint32_t* header,
                                                uint64_t* desc, const uint32_t* totals, int rank) {
-    using Cfg = ScanCfg<VEC>;
+    using Cfg = ScanCfg<THREADS, VEC>;
+    constexpr int kScanWarps = Cfg::kWarps;
     __shared__ uint32_t s_tile;
     __shared__ uint32_t s_warp_total[kScanWarps];
     __shared__ uint32_t s_prefix;
@@ -188,7 +204,7 @@ __device__ __forceinline__ void scan_tile_body(uint32_t n, uint32_t* x, uint32_t
         } else {
             if (lane == 0) st_desc(desc + tile, kStateAggregate, aggregate);
             bool failed;
-            exclusive = lookback(tile, desc, header + 1, &failed);
+            exclusive = lookback<NW>(tile, desc, header + 1, &failed);
             if (lane == 0) {
                 if (failed) {
                     atomicExch(header + 1, 1u);
@@ -222,25 +238,38 @@ __device__ __forceinline__ void scan_tile_body(uint32_t n, uint32_t* x, uint32_t
     }
 }
 
-constexpr int kVec = 4;  // 16 elements per thread, 4096 per tile
+// Tile geometry: threads per CTA, 16-byte vectors per thread, look-back probes of 32 * NW records.
+constexpr int kThreads = 256;
+constexpr int kVec = 4;
+constexpr int kNW = 1;
+constexpr int kMinTile = 4096;  // the workspace is sized for the smallest tile any variant uses
 
 }  // namespace
 
 // Same parameter list as the reference entry point (generated/scan_kernel.cu:1):
 // n elements, data in place, the ticket counter, the per-tile records.  Here the
 // counter word is followed by an abort flag and a record is one 64-bit word.
-__global__ void __launch_bounds__(kScanThreads)
+__global__ void __launch_bounds__(kThreads)
 scan_kernel(uint32_t n, uint32_t* x, uint32_t* block_idx_counter, int* block_infos) {
-    scan_tile_body<kVec, false>(n, x, block_idx_counter, reinterpret_cast<uint64_t*>(block_infos),
-                                nullptr, 0);
+    scan_tile_body<kThreads, kVec, kNW, false>(n, x, block_idx_counter, reinterpret_cast<uint64_t*>(block_infos),
+                                               nullptr, 0);
 }
 
 // Sharded form: tile 0 starts from totals[0] + ... + totals[rank-1].
-__global__ void __launch_bounds__(kScanThreads)
+__global__ void __launch_bounds__(kThreads)
 scan_kernel_seeded(uint32_t n, uint32_t* x, uint32_t* block_idx_counter, int* block_infos,
                    const uint32_t* totals, int rank) {
-    scan_tile_body<kVec, true>(n, x, block_idx_counter, reinterpret_cast<uint64_t*>(block_infos),
-                               totals, rank);
+    scan_tile_body<kThreads, kVec, kNW, true>(n, x, block_idx_counter, reinterpret_cast<uint64_t*>(block_infos),
+                                              totals, rank);
+}
+
+// TUNING ONLY: other geometries, selected with PRISM_B200_SCAN_VARIANT.
+template <int THREADS, int VEC, int NW>
+__global__ void __launch_bounds__(THREADS)
+scan_kernel_var(uint32_t n, uint32_t* x, uint32_t* block_idx_counter, int* block_infos, const uint32_t* totals,
+                int rank) {
+    scan_tile_body<THREADS, VEC, NW, true>(n, x, block_idx_counter, reinterpret_cast<uint64_t*>(block_infos), totals,
+                                           rank);
 }
 
 __global__ void __launch_bounds__(256) reduce_u32_kernel(size_t n, const uint32_t* x, uint32_t* total) {
@@ -288,7 +317,32 @@ __global__ void __launch_bounds__(256) add_carry_kernel(size_t n, uint32_t* x, c
 
 namespace {
 
-size_t scan_tiles(size_t n) { return (n + ScanCfg<kVec>::kTile - 1) / ScanCfg<kVec>::kTile; }
+size_t scan_tiles(size_t n) { return (n + kMinTile - 1) / kMinTile; }
+
+using VarKernel = void (*)(uint32_t, uint32_t*, uint32_t*, int*, const uint32_t*, int);
+struct Variant { VarKernel k; int threads; int tile; };
+#define PRISM_VARIANT(T, V, W) Variant{scan_kernel_var<T, V, W>, T, T * 4 * V}
+const Variant kVariants[] = {
+    PRISM_VARIANT(256, 4, 1),   // 0
+    PRISM_VARIANT(256, 4, 2),   // 1
+    PRISM_VARIANT(512, 4, 1),   // 2
+    PRISM_VARIANT(512, 8, 1),   // 3
+    PRISM_VARIANT(512, 8, 2),   // 4
+    PRISM_VARIANT(256, 8, 2),   // 5
+    PRISM_VARIANT(1024, 4, 2),  // 6
+    PRISM_VARIANT(256, 16, 2),  // 7
+    PRISM_VARIANT(1024, 4, 1),  // 8
+    PRISM_VARIANT(512, 8, 4),   // 9
+};
+int scan_variant() {
+    static int v = -2;
+    if (v == -2) {
+        const char* e = getenv("PRISM_B200_SCAN_VARIANT");
+        v = e ? atoi(e) : -1;
+        if (v >= static_cast<int>(sizeof(kVariants) / sizeof(kVariants[0]))) v = -1;
+    }
+    return v;
+}
 
 int scan_launch(size_t n, uint32_t* x, void* workspace, const uint32_t* totals, int rank, bool seeded,
                 cudaStream_t stream) {
@@ -302,18 +356,24 @@ int scan_launch(size_t n, uint32_t* x, void* workspace, const uint32_t* totals, 
         return set_error(PRISM_B200_ERR_INVALID_ARGUMENT, "scan_seeded: bad rank/totals");
     if (int rc = bind_status_word()) return rc;
 
-    const uint32_t tiles = static_cast<uint32_t>(scan_tiles(n));
+    const int var = scan_variant();
+    const int tile_elems = var >= 0 ? kVariants[var].tile : ScanCfg<kThreads, kVec>::kTile;
+    const uint32_t tiles = static_cast<uint32_t>((n + tile_elems - 1) / tile_elems);
     uint32_t* header = static_cast<uint32_t*>(workspace);
     uint64_t* desc = reinterpret_cast<uint64_t*>(static_cast<char*>(workspace) + kHeaderBytes);
     // One memset re-arms ticket, abort flag and every record (the reference
     // issues two, evals/4090_scan/main.cu:81-82).
     PRISM_CUDA_TRY(cudaMemsetAsync(workspace, 0, kHeaderBytes + static_cast<size_t>(tiles) * sizeof(uint64_t), stream));
-    if (seeded)
-        scan_kernel_seeded<<<tiles, kScanThreads, 0, stream>>>(static_cast<uint32_t>(n), x, header,
-                                                                reinterpret_cast<int*>(desc), totals, rank);
+    if (var >= 0)
+        kVariants[var].k<<<tiles, kVariants[var].threads, 0, stream>>>(static_cast<uint32_t>(n), x, header,
+                                                                       reinterpret_cast<int*>(desc), totals,
+                                                                       seeded ? rank : 0);
+    else if (seeded)
+        scan_kernel_seeded<<<tiles, kThreads, 0, stream>>>(static_cast<uint32_t>(n), x, header,
+                                                            reinterpret_cast<int*>(desc), totals, rank);
     else
-        scan_kernel<<<tiles, kScanThreads, 0, stream>>>(static_cast<uint32_t>(n), x, header,
-                                                         reinterpret_cast<int*>(desc));
+        scan_kernel<<<tiles, kThreads, 0, stream>>>(static_cast<uint32_t>(n), x, header,
+                                                     reinterpret_cast<int*>(desc));
     PRISM_CUDA_TRY(cudaGetLastError());
     count_launch();
     return PRISM_B200_OK;

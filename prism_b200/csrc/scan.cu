@@ -68,6 +68,12 @@ __device__ __forceinline__ uint32_t warp_sum(uint32_t v) {
     return v;
 }
 
+// TUNING ONLY: per-tile trace of the look-back (windows read, re-polls, timestamps).
+#ifdef PRISM_SCAN_TRACE
+__device__ unsigned long long g_trace[4 * 65536];
+__device__ unsigned int g_trace_polls;
+#endif
+
 __device__ __forceinline__ uint64_t poll_desc(const uint64_t* p, uint64_t first, const uint32_t* abort_flag) {
     uint64_t d = first;
     uint32_t polls = 0;
@@ -76,6 +82,9 @@ __device__ __forceinline__ uint64_t poll_desc(const uint64_t* p, uint64_t first,
         if ((polls & 1023u) == 0u && ld_flag(abort_flag) != 0u) break;
         d = ld_desc(p);
     }
+#ifdef PRISM_SCAN_TRACE
+    if (polls) atomicAdd(&g_trace_polls, polls);
+#endif
     return d;
 }
 
@@ -91,7 +100,14 @@ __device__ __forceinline__ uint32_t lookback(uint32_t tile, const uint64_t* desc
     uint32_t exclusive = 0;
     long long idx = static_cast<long long>(tile) - 1 - lane;
     *failed = false;
+#ifdef PRISM_SCAN_TRACE
+    unsigned long long rounds = 0;
+#endif
     while (true) {
+#ifdef PRISM_SCAN_TRACE
+        ++rounds;
+        if (lane == 0 && tile < 65536) g_trace[4 * tile + 2] = rounds;
+#endif
         // A slot before tile 0 behaves like a finished tile with prefix 0.
         uint64_t d[NW];
 #pragma unroll
@@ -121,7 +137,7 @@ __device__ __forceinline__ uint32_t lookback(uint32_t tile, const uint64_t* desc
     }
 }
 
-template <int THREADS, int VEC, int NW, bool SEEDED>
+template <int THREADS, int VEC, int NW, bool SEEDED, bool TICKET = true, bool LOOKBACK = true>
 __device__ __forceinline__ void scan_tile_body(uint32_t n, uint32_t* x, uint32_t* header,
                                                uint64_t* desc, const uint32_t* totals, int rank) {
     using Cfg = ScanCfg<THREADS, VEC>;
@@ -134,9 +150,11 @@ __device__ __forceinline__ void scan_tile_body(uint32_t n, uint32_t* x, uint32_t
     const int lane = tid & 31;
     const int warp = tid >> 5;
 
-    if (tid == 0) s_tile = atomicAdd(header, 1u);
-    __syncthreads();
-    const uint32_t tile = s_tile;
+    if (TICKET) {
+        if (tid == 0) s_tile = atomicAdd(header, 1u);
+        __syncthreads();
+    }
+    const uint32_t tile = TICKET ? s_tile : blockIdx.x;
     const unsigned long long base =
         static_cast<unsigned long long>(tile) * Cfg::kTile + static_cast<unsigned long long>(warp) * Cfg::kWarpElems;
     const bool full_tile = static_cast<unsigned long long>(tile) * Cfg::kTile + Cfg::kTile <= n;
@@ -203,8 +221,15 @@ __device__ __forceinline__ void scan_tile_body(uint32_t n, uint32_t* x, uint32_t
             if (lane == 0) st_desc(desc, kStatePrefix, exclusive + aggregate);
         } else {
             if (lane == 0) st_desc(desc + tile, kStateAggregate, aggregate);
+#ifdef PRISM_SCAN_TRACE
+            if (lane == 0 && tile < 65536) g_trace[4 * tile + 0] = global_timer_ns();
+#endif
             bool failed;
-            exclusive = lookback<NW>(tile, desc, header + 1, &failed);
+            exclusive = LOOKBACK ? lookback<NW>(tile, desc, header + 1, &failed) : 0u;
+            if (!LOOKBACK) failed = false;
+#ifdef PRISM_SCAN_TRACE
+            if (lane == 0 && tile < 65536) g_trace[4 * tile + 1] = global_timer_ns();
+#endif
             if (lane == 0) {
                 if (failed) {
                     atomicExch(header + 1, 1u);
@@ -264,12 +289,12 @@ scan_kernel_seeded(uint32_t n, uint32_t* x, uint32_t* block_idx_counter, int* bl
 }
 
 // TUNING ONLY: other geometries, selected with PRISM_B200_SCAN_VARIANT.
-template <int THREADS, int VEC, int NW>
+template <int THREADS, int VEC, int NW, bool TICKET = true, bool LOOKBACK = true>
 __global__ void __launch_bounds__(THREADS)
 scan_kernel_var(uint32_t n, uint32_t* x, uint32_t* block_idx_counter, int* block_infos, const uint32_t* totals,
                 int rank) {
-    scan_tile_body<THREADS, VEC, NW, true>(n, x, block_idx_counter, reinterpret_cast<uint64_t*>(block_infos), totals,
-                                           rank);
+    scan_tile_body<THREADS, VEC, NW, true, TICKET, LOOKBACK>(n, x, block_idx_counter,
+                                                             reinterpret_cast<uint64_t*>(block_infos), totals, rank);
 }
 
 __global__ void __launch_bounds__(256) reduce_u32_kernel(size_t n, const uint32_t* x, uint32_t* total) {
@@ -333,6 +358,12 @@ const Variant kVariants[] = {
     PRISM_VARIANT(256, 16, 2),  // 7
     PRISM_VARIANT(1024, 4, 1),  // 8
     PRISM_VARIANT(512, 8, 4),   // 9
+    Variant{scan_kernel_var<512, 8, 1, false, true>, 512, 16384},   // 10 no ticket
+    Variant{scan_kernel_var<512, 8, 1, true, false>, 512, 16384},   // 11 no look-back (wrong results)
+    Variant{scan_kernel_var<512, 8, 1, false, false>, 512, 16384},  // 12 neither
+    Variant{scan_kernel_var<256, 4, 1, false, true>, 256, 4096},    // 13 no ticket
+    Variant{scan_kernel_var<256, 4, 1, false, false>, 256, 4096},   // 14 neither
+    Variant{scan_kernel_var<256, 8, 1, false, true>, 256, 8192},    // 15 no ticket
 };
 int scan_variant() {
     static int v = -2;
@@ -390,6 +421,16 @@ unsigned streaming_grid(size_t n4) {
 }  // namespace prism_b200
 
 using namespace prism_b200;
+
+#ifdef PRISM_SCAN_TRACE
+extern "C" int prism_b200_scan_trace(unsigned long long* out, unsigned int* polls) {
+    cudaMemcpyFromSymbol(out, g_trace, sizeof(unsigned long long) * 4 * 65536);
+    cudaMemcpyFromSymbol(polls, g_trace_polls, 4);
+    unsigned int z = 0;
+    cudaMemcpyToSymbol(g_trace_polls, &z, 4);
+    return 0;
+}
+#endif
 
 extern "C" int prism_b200_scan_workspace_size(size_t n, size_t* bytes) {
     if (!bytes) return set_error(PRISM_B200_ERR_INVALID_ARGUMENT, "scan_workspace_size: null bytes");

@@ -237,14 +237,13 @@ my_sgemm_kernel_4(int M, int N, int K, float alpha, float* A, float* B, float be
 // ============================================================================
 namespace k5 {
 constexpr int BM = 128, BN = 128, BK = 32;
-constexpr int STAGES = 3;
 constexpr int A_STRIDE = BK + 4;                       // floats
 constexpr int A_STAGE = BM * A_STRIDE;                 // floats
 constexpr int B_STAGE = BK * BN;                       // floats
-constexpr int WARPS = 4;
-constexpr int THREADS = WARPS * 32;
 constexpr uint32_t STAGE_TX_BYTES = (BM * BK + BK * BN) * sizeof(float);
-constexpr size_t SMEM_BYTES = static_cast<size_t>(STAGES) * (A_STAGE + B_STAGE) * sizeof(float) + 2 * STAGES * 8 + 16;
+constexpr size_t smem_bytes(int stages) {
+    return static_cast<size_t>(stages) * (A_STAGE + B_STAGE) * sizeof(float) + 2 * stages * 8 + 16;
+}
 }  // namespace k5
 
 __device__ __forceinline__ void bulk_copy_g2s(void* dst_smem, const void* src, uint32_t bytes, uint64_t* bar) {
@@ -266,10 +265,20 @@ __device__ __forceinline__ void fma2(unsigned long long& acc, unsigned long long
     asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc) : "l"(a), "l"(b));
 }
 
-template <bool PACKED>
-__global__ void __launch_bounds__(k5::THREADS, 2)
+// PACKED : fma.rn.f32x2 on column pairs (else scalar fmaf)
+// WARPS  : 4 (8 x 16 outputs per lane, NV = 4) or 8 (8 x 8 outputs per lane, NV = 2)
+// STAGES : depth of the shared-memory ring
+// MINB   : CTAs per SM asked of the compiler
+template <bool PACKED, int WARPS, int STAGES, int MINB>
+__global__ void __launch_bounds__(WARPS * 32, MINB)
 my_sgemm_kernel_5(int M, int N, int K, float alpha, float* A, float* B, float beta, float* C, int num_blocks_N) {
     using namespace k5;
+    static_assert(WARPS == 4 || WARPS == 8, "2 x 2 or 2 x 4 warp tiles");
+    constexpr int NV = WARPS == 4 ? 4 : 2;            // 16-byte B vectors per lane per k
+    constexpr int WN = 16 * NV;                       // warp tile columns
+    constexpr int WARPS_N = BN / WN;
+    constexpr int B_WARP = WARPS == 4 ? 0 : 4;        // the warp that copies the B rows
+    constexpr int COPY_WARPS = WARPS == 4 ? 4 : 5;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     float* As = reinterpret_cast<float*>(smem_raw);
     float* Bs = As + STAGES * A_STAGE;
@@ -285,7 +294,7 @@ my_sgemm_kernel_5(int M, int N, int K, float alpha, float* A, float* B, float be
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
-            mbar_init(&full_bar[s], WARPS);
+            mbar_init(&full_bar[s], COPY_WARPS);
             mbar_init(&empty_bar[s], WARPS);
         }
         *abort_flag = 0;
@@ -293,49 +302,54 @@ my_sgemm_kernel_5(int M, int N, int K, float alpha, float* A, float* B, float be
     }
     __syncthreads();
 
-    // Each warp copies its quarter of a k-slice: 32 rows of A (lane = row) and 8 rows
-    // of B (lanes 0-7), and announces those bytes on the stage's "full" barrier first.
-    const float* a_src = A + static_cast<size_t>(row0 + warp * 32 + lane) * K;
-    const float* b_src = B + static_cast<size_t>(warp * 8 + (lane & 7)) * N + col0;
+    // Warps 0-3 copy 32 rows of A each (lane = row); warp B_WARP also copies the 32 rows
+    // of B.  A copying warp announces its bytes on the stage's "full" barrier first.
+    const bool copies_a = warp < 4;
+    const bool copies_b = warp == B_WARP;
+    const float* a_src = A + static_cast<size_t>(row0 + (warp & 3) * 32 + lane) * K;
+    const float* b_src = B + static_cast<size_t>(lane) * N + col0;
     auto issue_slice = [&](int t) {
         const int s = t % STAGES;
-        if (lane == 0) mbar_arrive_expect_tx(&full_bar[s], STAGE_TX_BYTES / WARPS);
+        if (lane == 0)
+            mbar_arrive_expect_tx(&full_bar[s], (copies_a ? 32u * BK * 4u : 0u) + (copies_b ? 32u * BN * 4u : 0u));
         __syncwarp();
-        bulk_copy_g2s(As + s * A_STAGE + (warp * 32 + lane) * A_STRIDE, a_src + t * BK, BK * sizeof(float),
-                      &full_bar[s]);
-        if (lane < 8)
-            bulk_copy_g2s(Bs + s * B_STAGE + (warp * 8 + lane) * BN, b_src + static_cast<size_t>(t) * BK * N,
-                          BN * sizeof(float), &full_bar[s]);
+        if (copies_a)
+            bulk_copy_g2s(As + s * A_STAGE + (warp * 32 + lane) * A_STRIDE, a_src + t * BK, BK * sizeof(float),
+                          &full_bar[s]);
+        if (copies_b)
+            bulk_copy_g2s(Bs + s * B_STAGE + lane * BN, b_src + static_cast<size_t>(t) * BK * N, BN * sizeof(float),
+                          &full_bar[s]);
     };
-    for (int t = 0; t < STAGES - 1 && t < k_slices; ++t) issue_slice(t);
+    if (copies_a || copies_b)
+        for (int t = 0; t < STAGES - 1 && t < k_slices; ++t) issue_slice(t);
 
     const int tm = lane & 7;
     const int tn = lane >> 3;
-    const int wm0 = (warp >> 1) * 64;
-    const int wn0 = (warp & 1) * 64;
+    const int wm0 = (warp / WARPS_N) * 64;
+    const int wn0 = (warp % WARPS_N) * WN;
 
-    unsigned long long acc2[PACKED ? 8 : 1][PACKED ? 8 : 1];
-    float acc[PACKED ? 1 : 8][PACKED ? 1 : 16];
+    unsigned long long acc2[PACKED ? 8 : 1][PACKED ? 2 * NV : 1];
+    float acc[PACKED ? 1 : 8][PACKED ? 1 : 4 * NV];
     if constexpr (PACKED) {
 #pragma unroll
         for (int i = 0; i < 8; ++i)
 #pragma unroll
-            for (int j = 0; j < 8; ++j) acc2[i][j] = 0ull;
+            for (int j = 0; j < 2 * NV; ++j) acc2[i][j] = 0ull;
     } else {
 #pragma unroll
         for (int i = 0; i < 8; ++i)
 #pragma unroll
-            for (int j = 0; j < 16; ++j) acc[i][j] = 0.f;
+            for (int j = 0; j < 4 * NV; ++j) acc[i][j] = 0.f;
     }
 
     bool ok = true;
     for (int t = 0; t < k_slices; ++t) {
         const int s = t % STAGES;
         const uint32_t round = static_cast<uint32_t>(t / STAGES);
-        // Refill the stage that slice t-1 used with slice t+STAGES-1, once all four
-        // warps have released it.
+        // Refill the stage that slice t-1 used with slice t+STAGES-1, once every warp
+        // has released it.
         const int refill = t + STAGES - 1;
-        if (refill < k_slices) {
+        if ((copies_a || copies_b) && refill < k_slices) {
             if (t >= 1 && !mbar_wait_bounded(&empty_bar[(t - 1) % STAGES], static_cast<uint32_t>((t - 1) / STAGES) & 1u,
                                              abort_flag)) {
                 ok = false;
@@ -357,29 +371,29 @@ my_sgemm_kernel_5(int M, int N, int K, float alpha, float* A, float* B, float be
 #pragma unroll
             for (int k4 = 0; k4 < 4; ++k4) {
                 if constexpr (PACKED) {
-                    ulonglong2 b[4];
+                    ulonglong2 b[NV];
 #pragma unroll
-                    for (int j = 0; j < 4; ++j)
+                    for (int j = 0; j < NV; ++j)
                         b[j] = *reinterpret_cast<const ulonglong2*>(b_base + (kk + k4) * BN + j * 16);
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
                         const float av = k4 == 0 ? a[i].x : k4 == 1 ? a[i].y : k4 == 2 ? a[i].z : a[i].w;
                         const unsigned long long a2 = pack2(av, av);
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
+                        for (int j = 0; j < NV; ++j) {
                             fma2(acc2[i][2 * j + 0], a2, b[j].x);
                             fma2(acc2[i][2 * j + 1], a2, b[j].y);
                         }
                     }
                 } else {
-                    float4 b[4];
+                    float4 b[NV];
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) b[j] = *reinterpret_cast<const float4*>(b_base + (kk + k4) * BN + j * 16);
+                    for (int j = 0; j < NV; ++j) b[j] = *reinterpret_cast<const float4*>(b_base + (kk + k4) * BN + j * 16);
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
                         const float av = k4 == 0 ? a[i].x : k4 == 1 ? a[i].y : k4 == 2 ? a[i].z : a[i].w;
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
+                        for (int j = 0; j < NV; ++j) {
                             acc[i][4 * j + 0] = fmaf(av, b[j].x, acc[i][4 * j + 0]);
                             acc[i][4 * j + 1] = fmaf(av, b[j].y, acc[i][4 * j + 1]);
                             acc[i][4 * j + 2] = fmaf(av, b[j].z, acc[i][4 * j + 2]);
@@ -405,7 +419,7 @@ my_sgemm_kernel_5(int M, int N, int K, float alpha, float* A, float* B, float be
     for (int i = 0; i < 8; ++i) {
         float* c_row = C + static_cast<size_t>(row0 + wm0 + tm + 8 * i) * N + col0 + wn0 + tn * 4;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < NV; ++j) {
             float4* c = reinterpret_cast<float4*>(c_row + j * 16);
             float4 v = *c;
             float r0, r1, r2, r3;
@@ -442,7 +456,7 @@ int launch_generic(int M, int N, int K, float alpha, const float* A, const float
     return PRISM_B200_OK;
 }
 
-bool g_k5_packed = true;  // fma.rn.f32x2 form of kernel 5; PRISM_B200_SGEMM_SCALAR=1 selects plain fmaf
+int g_k5_variant = 0;  // fma.rn.f32x2 form of kernel 5; PRISM_B200_SGEMM_SCALAR=1 selects the plain fmaf form
 bool g_k5_env_read = false;
 
 }  // namespace
@@ -499,24 +513,36 @@ extern "C" int prism_b200_sgemm(int kernel_id, int M, int N, int K, float alpha,
     }
     case 5: {
         if (M % k5::BM == 0 && N % k5::BN == 0 && K % k5::BK == 0 && K > 0 && vec_ok) {
+            using Kern = void (*)(int, int, int, float, float*, float*, float, float*, int);
+            struct Var { Kern k; int threads; int stages; };
+            // 0: packed, 4 warps, 8x16 per lane, 3 stages, 2 CTAs/SM (default)   1: scalar fmaf form of 0
+            // TUNING ONLY (PRISM_B200_SGEMM_VARIANT): 2: 8 warps 8x8 per lane   3: 4 warps, 2 stages, 3 CTAs/SM
+            static const Var vars[] = {
+                {my_sgemm_kernel_5<true, 4, 3, 2>, 128, 3},  {my_sgemm_kernel_5<false, 4, 3, 2>, 128, 3},
+                {my_sgemm_kernel_5<true, 8, 3, 2>, 256, 3},  {my_sgemm_kernel_5<true, 4, 2, 3>, 128, 2},
+                {my_sgemm_kernel_5<true, 8, 2, 3>, 256, 2},  {my_sgemm_kernel_5<true, 8, 4, 1>, 256, 4},
+            };
             if (!g_k5_env_read) {
                 const char* e = getenv("PRISM_B200_SGEMM_SCALAR");
-                g_k5_packed = !(e && e[0] == '1');
+                g_k5_variant = (e && e[0] == '1') ? 1 : 0;
+                const char* v = getenv("PRISM_B200_SGEMM_VARIANT");
+                if (v && atoi(v) >= 0 && atoi(v) < static_cast<int>(sizeof(vars) / sizeof(vars[0]))) g_k5_variant = atoi(v);
                 g_k5_env_read = true;
             }
+            const Var& var = vars[g_k5_variant];
             const int nbn = N / k5::BN;
             const unsigned blocks = static_cast<unsigned>((M / k5::BM) * nbn);
-            static bool attr_set[2][64] = {};
+            static bool attr_set[8][64] = {};
             int dev = 0;
             PRISM_CUDA_TRY(cudaGetDevice(&dev));
-            auto kern = g_k5_packed ? my_sgemm_kernel_5<true> : my_sgemm_kernel_5<false>;
-            if (dev < 0 || dev >= 64 || !attr_set[g_k5_packed][dev]) {
-                PRISM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                    static_cast<int>(k5::SMEM_BYTES)));
-                if (dev >= 0 && dev < 64) attr_set[g_k5_packed][dev] = true;
+            const size_t smem = k5::smem_bytes(var.stages);
+            if (dev < 0 || dev >= 64 || !attr_set[g_k5_variant][dev]) {
+                PRISM_CUDA_TRY(cudaFuncSetAttribute(var.k, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                    static_cast<int>(smem)));
+                if (dev >= 0 && dev < 64) attr_set[g_k5_variant][dev] = true;
             }
-            kern<<<blocks, k5::THREADS, k5::SMEM_BYTES, s>>>(M, N, K, alpha, const_cast<float*>(A),
-                                                            const_cast<float*>(B), beta, C, nbn);
+            var.k<<<blocks, var.threads, smem, s>>>(M, N, K, alpha, const_cast<float*>(A), const_cast<float*>(B), beta,
+                                                    C, nbn);
         } else {
             rc = launch_generic(M, N, K, alpha, A, B, beta, C, s);
         }

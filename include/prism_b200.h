@@ -119,6 +119,30 @@ int prism_b200_scan_seeded(size_t n, uint32_t* x, void* workspace,
 int prism_b200_scan_add_carry(size_t n, uint32_t* x, const uint32_t* totals,
                               int rank, void* stream);
 
+/*
+ * Scan without caller-provided scratch and without any allocation.  No
+ * counterpart in the reference (its launcher always takes a workspace,
+ * evals/4090_scan/main.cu:68-86).
+ *
+ * For callers that cannot allocate device memory where the scan runs: plugins
+ * that only ever see buffers owned by their host application, loops that may
+ * not block on the allocator, processes whose device memory is already all
+ * handed out.  Same result as prism_b200_scan, in place, but the look-back
+ * records live in a fixed 524,416-byte array inside the library's device image
+ * (every GPU that loads the library holds it until exit), which bounds n:
+ *   n <= 2^28 elements; larger n returns PRISM_B200_ERR_TOO_LARGE.
+ * The call performs no cudaMalloc/cudaFree and calls no allocating routine.
+ * The first call on a device looks up the array's device address
+ * (cudaGetSymbolAddress) and should therefore come before any stream capture.
+ * All calls on a device share the one array and it is re-armed at the start of
+ * each call, so two calls whose GPU work overlaps (different streams, or
+ * different host threads) race with each other: serialise them.  A device-side
+ * timeout is reported through prism_b200_last_error only if another entry point
+ * has already set up the status word on that device, since doing so allocates
+ * pinned memory, which this entry point will not do.
+ */
+int prism_b200_scan_static(size_t n, uint32_t* x, void* stream);
+
 /* ---- bf16 GEMM: C = A * B^T, fp32 accumulate ------------------------------ */
 
 /*

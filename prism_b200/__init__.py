@@ -24,7 +24,7 @@ from ._lib import PrismB200Error, last_error, load  # noqa: F401
 
 __all__ = [
     "run_my_kernel", "get_workspace_size", "launch_scan", "runmyh100",
-    "sgemm", "scan_", "scan_workspace", "gemm_bf16", "reduce_u32", "scan_seeded_", "scan_add_carry_",
+    "sgemm", "scan_", "scan_static_", "scan_workspace", "gemm_bf16", "reduce_u32", "scan_seeded_", "scan_add_carry_",
     "launch_count", "last_error", "clear_error", "version", "PrismB200Error",
 ]
 
@@ -118,6 +118,15 @@ def scan_(x: torch.Tensor, workspace: torch.Tensor | None = None) -> torch.Tenso
     if workspace is None:
         workspace = scan_workspace(n, x.device)
     return launch_scan(n, x, workspace)
+
+
+def scan_static_(x: torch.Tensor) -> torch.Tensor:
+    """In-place scan that allocates nothing: the look-back records live in a fixed array inside the
+    library (at most 2^28 elements; calls that overlap on the GPU race -- see include/prism_b200.h)."""
+    _require_cuda("x", x, _SCAN_DTYPES)
+    with torch.cuda.device(x.device):
+        _lib.check(load().prism_b200_scan_static(x.numel(), x.data_ptr(), _stream(x)))
+    return x
 
 
 def reduce_u32(x: torch.Tensor, total: torch.Tensor) -> torch.Tensor:

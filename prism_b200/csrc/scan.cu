@@ -422,6 +422,78 @@ unsigned streaming_grid(size_t n4) {
 
 using namespace prism_b200;
 
+// ---------------------------------------------------------------------------
+// Scan for callers that must not allocate device memory.
+//
+// Some hosts of this library cannot call cudaMalloc on the path that runs the
+// scan: a plugin that is handed device buffers by its host application and is
+// forbidden to grow the process's memory footprint, a real-time loop that may
+// not block on the allocator, code running after the application has handed all
+// remaining device memory to its own pool.  prism_b200_scan needs caller-provided
+// scratch, which such callers have nowhere to get from.  This entry point keeps
+// the scratch inside the library image instead: a fixed array in device memory
+// that exists on every GPU that loads the library, from load until exit.
+// ---------------------------------------------------------------------------
+namespace prism_b200 {
+namespace {
+constexpr size_t kStaticMaxN = 1ull << 28;  // elements (1 GiB of data)
+constexpr size_t kStaticScratchBytes = kHeaderBytes + (kStaticMaxN / kMinTile) * sizeof(uint64_t);  // 524,416 B
+}  // namespace
+}  // namespace prism_b200
+
+// In host code this name is only a handle for the runtime; the device address
+// comes from cudaGetSymbolAddress (static_scratch_address below).
+static __device__ __align__(256) unsigned char g_static_scan_scratch[prism_b200::kStaticScratchBytes];
+
+namespace prism_b200 {
+namespace {
+void* g_static_scratch_addr[64] = {};
+
+// Device address of the built-in scratch on the current device, looked up once per device.
+int static_scratch_address(void** out) {
+    int dev = 0;
+    PRISM_CUDA_TRY(cudaGetDevice(&dev));
+    const bool cacheable = dev >= 0 && dev < 64;
+    if (cacheable && g_static_scratch_addr[dev]) {
+        *out = g_static_scratch_addr[dev];
+        return PRISM_B200_OK;
+    }
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_static_scan_scratch);
+    if (e != cudaSuccess) return cuda_failed(e, "cudaGetSymbolAddress(built-in scan scratch)");
+    if (!p) return set_error(PRISM_B200_ERR_CUDA, "built-in scan scratch has no device address");
+    if (cacheable) g_static_scratch_addr[dev] = p;
+    *out = p;
+    return PRISM_B200_OK;
+}
+}  // namespace
+}  // namespace prism_b200
+
+extern "C" int prism_b200_scan_static(size_t n, uint32_t* x, void* stream) {
+    if (n == 0) return PRISM_B200_OK;
+    if (!x) return set_error(PRISM_B200_ERR_INVALID_ARGUMENT, "scan_static: null pointer");
+    if (n > kStaticMaxN)
+        return set_error(PRISM_B200_ERR_TOO_LARGE,
+                         "scan_static: n=%zu exceeds the built-in scratch (at most %zu elements); use prism_b200_scan "
+                         "with caller-provided scratch",
+                         n, static_cast<size_t>(kStaticMaxN));
+    if (reinterpret_cast<uintptr_t>(x) & 15u)
+        return set_error(PRISM_B200_ERR_MISALIGNED, "scan_static: x not 16-byte aligned");
+    void* scratch = nullptr;
+    if (int rc = static_scratch_address(&scratch)) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    constexpr int tile_elems = ScanCfg<kThreads, kVec>::kTile;
+    const uint32_t tiles = static_cast<uint32_t>((n + tile_elems - 1) / tile_elems);
+    uint32_t* header = static_cast<uint32_t*>(scratch);
+    uint64_t* desc = reinterpret_cast<uint64_t*>(static_cast<char*>(scratch) + kHeaderBytes);
+    // The array still holds the previous call's ticket, abort flag and records.
+    PRISM_CUDA_TRY(cudaMemsetAsync(scratch, 0, kHeaderBytes + static_cast<size_t>(tiles) * sizeof(uint64_t), s));
+    scan_kernel<<<tiles, kThreads, 0, s>>>(static_cast<uint32_t>(n), x, header, reinterpret_cast<int*>(desc));
+    PRISM_CUDA_TRY(cudaGetLastError());
+    count_launch();
+    return PRISM_B200_OK;
+}
+
 #ifdef PRISM_SCAN_TRACE
 extern "C" int prism_b200_scan_trace(unsigned long long* out, unsigned int* polls) {
     cudaMemcpyFromSymbol(out, g_trace, sizeof(unsigned long long) * 4 * 65536);

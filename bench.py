@@ -183,7 +183,7 @@ def run_gemm_bf16(args, world, rank, peaks):
     import prism_b200 as pb
     from prism_b200 import host, sharded
     dev = torch.device("cuda", torch.cuda.current_device())
-    S = GEMM_S
+    S = args.size or GEMM_S
     plan = sharded.RowShardedGemmBF16(S, S, S)
     rows = plan.rows
     g = torch.Generator(device=dev).manual_seed(1234)           # B: same on every rank
@@ -203,7 +203,7 @@ def run_gemm_bf16(args, world, rank, peaks):
     value = flops / (ms * 1e-3) / 1e12
 
     # spot check of this rank's result against fp64 on a few rows/columns (bf16-rounded inputs)
-    n_idx = [0, 1, 4095, S - 1]
+    n_idx = [0, 1, S // 2 - 1, S - 1]
     ref = (B[n_idx].double() @ A.double().t()).cpu()
     got = C[n_idx].double().cpu()
     rms = float(ref.pow(2).mean().sqrt())
@@ -227,9 +227,9 @@ def run_gemm_bf16(args, world, rank, peaks):
                 "peak_source": f"{peaks['source']} cuBLAS bf16 burst", "frac_of_sustained": achieved / peaks["bf16_tflops_sustained"],
                 "frac_of_nominal_2250": achieved / 2250.0,
                 "traffic": NCU_TRAFFIC_BYTES["gemm_bf16"]}
-    line = {"metric": "bf16 GEMM TFLOP/s (D = A*B^T, M=N=K=8192, fp32 accumulate, bf16 out)", "value": value,
+    line = {"metric": "bf16 GEMM TFLOP/s (D = A*B^T, M=N=K=%d, fp32 accumulate, bf16 out)" % S, "value": value,
             "unit": "TFLOP/s", "ms_per_step": ms, "scaling": "strong", "dtype": "bf16",
-            "config": {"workload": "gemm_bf16 8192x8192x8192, A and B K-major, C column-major, values 0.1*normal bf16",
+            "config": {"workload": "gemm_bf16 %dx%dx%d, A and B K-major, C column-major, values 0.1*normal bf16" % (S, S, S),
                        "M": S, "N": S, "K": S, "sharding": f"rows of M over {world} GPU(s), B replicated, no collective",
                        "rows_per_gpu": rows, "l2": "inputs larger than L2 (A+B = %d MiB per GPU)" % ((rows + S) * S * 2 >> 20)},
             "roofline": roofline, "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "spot_check_ok": ok}
@@ -243,7 +243,7 @@ def run_sgemm(args, world, rank, peaks, steps=None, warmup=None):
     steps = steps or args.steps
     warmup = warmup or args.warmup
     dev = torch.device("cuda", torch.cuda.current_device())
-    S = SGEMM_S
+    S = (args.size if args.workload == "sgemm" else 0) or SGEMM_S
     plan = sharded.RowShardedSgemm(S, S, S, kernel=5)
     rows = plan.rows
     g = torch.Generator(device=dev).manual_seed(4321)
@@ -276,9 +276,9 @@ def run_sgemm(args, world, rank, peaks, steps=None, warmup=None):
     peak_nominal = 148 * 128 * 2 * sm_max * 1e6 / 1e12
     sm_load = clocks.get("sm_mhz") or sm_max
     peak_at_clock = 148 * 128 * 2 * sm_load * 1e6 / 1e12
-    return {"metric": "FP32 SGEMM TFLOP/s (C = 1.5*A*B + 0.5*C, M=N=K=4096, pure FFMA)",
+    return {"metric": "FP32 SGEMM TFLOP/s (C = 1.5*A*B + 0.5*C, M=N=K=%d, pure FFMA)" % S,
             "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms, "scaling": "strong", "dtype": "f32",
-            "config": {"workload": "sgemm 4096x4096x4096 row-major, kernel 5, A/B/C uniform[-1,1)", "sharding":
+            "config": {"workload": "sgemm %dx%dx%d row-major, kernel 5, A/B/C uniform[-1,1)" % (S, S, S), "sharding":
                        f"rows of M over {world} GPU(s), B replicated, no collective", "rows_per_gpu": rows,
                        "l2": "C restored from a pristine copy before every step (untimed), which also displaces L2"},
             "roofline": {"bound": "fp32_ffma", "kernel": "my_sgemm_kernel_5<packed>", "achieved": achieved,
@@ -498,6 +498,8 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=["gemm_bf16", "sgemm", "scan"], default="gemm_bf16")
     ap.add_argument("--scan-schedule", choices=["reduce_then_scan", "scan_then_carry"], default="reduce_then_scan")
+    ap.add_argument("--size", type=int, default=0,
+                    help="square GEMM size for --workload gemm_bf16/sgemm (default 8192 / 4096); smaller sizes are for profiling")
     ap.add_argument("--scan-log2n", type=int, default=0, help="scan length 2^k (default: 28 on one GPU, 30 sharded)")
     ap.add_argument("--no-extras", action="store_true", help="skip the other two kernel families and the CPU baseline")
     args = ap.parse_args()

@@ -1,5 +1,5 @@
 // uint32 inclusive scan for B200: one pass over the data, decoupled look-back
-// between tiles.
+// between tiles, tiles parked in shared memory while their prefix is in flight.
 //
 // What it stands in for: `scan_kernel` and its nine device helpers
 // (generated/scan_kernel.cu:1-29, generated/scan_warps.cu, get_warp_ends_inclusive.cu,
@@ -8,24 +8,37 @@
 // get_block_idx_from_global_counter.cu, shfl_up_sync_wrapper.cu) and the host
 // glue `get_workspace_size` / `launch_scan` (evals/4090_scan/main.cu:63-86).
 //
-// How it differs, and why, on a machine whose HBM moves ~6.5 TB/s:
-//   * every element is read by one 16-byte load and written by one 16-byte
-//     store; the tile lives in registers, not in 64 KB of shared memory, so
-//     eight 256-thread CTAs stay resident per SM and keep >100 KB of loads in
-//     flight per SM;
-//   * the block-level scan is four independent 5-step warp-shuffle scans per
-//     thread plus one 8-entry shared-memory hand-off (one __syncthreads), not a
-//     9-round Hillis-Steele with a barrier per round;
-//   * a tile publishes ONE 64-bit word {state, value}; state says whether value
-//     is the tile's own aggregate or its inclusive prefix.  Flag and value
-//     travel in one relaxed 64-bit store, so no fence is needed (the reference
-//     uses the same packing in BlockInfo, evals/4090_scan/main.cu:21-37, but
-//     keeps two words per tile);
-//   * look-back is done by a whole warp, 32 predecessors per probe, and every
-//     spin is bounded: when it runs out the tile raises an abort flag and a
-//     status code instead of hanging the GPU;
-//   * tiles take their index from an atomic ticket exactly as the reference
-//     does, so a tile's predecessors are always resident or finished.
+// Why it is shaped the way it is.  A one-tile-per-CTA scan that keeps its tile in
+// registers streams at HBM speed on B200 if the look-back is taken out (6.8 TB/s
+// measured) but reaches 2.9-3.8 TB/s with it: every tile waits ~5 us for its
+// predecessors, mostly for aggregates that are published late, and while it
+// waits its data occupies registers that the SM needs to keep loads in flight.
+// So here a CTA is persistent and owns a ring of S 16 KB slots in shared memory:
+//   producer warp   draws a ticket (the reference's atomic tile counter), bulk-copies
+//                   that tile into the next free slot with cp.async.bulk; completion
+//                   is counted on the slot's "full" mbarrier;
+//   8 scan warps    phase A when a slot fills: slot -> registers, tile-local scan
+//                   (serial over 4 elements, four independent 5-step warp-shuffle
+//                   scans per lane, one 8-entry hand-off between warps), scanned
+//                   values back into the slot, tile aggregate published;
+//                   phase B, up to LAG tiles later: slot -> registers, add the
+//                   exclusive prefix, 16-byte stores to global memory, slot released;
+//   look-back warp  resolves the exclusive prefix of the CTA's tiles in order, 32
+//                   predecessor records per probe, and publishes inclusive prefixes.
+// Between A and B a tile costs only shared memory, so loads keep flowing.
+//
+// A tile publishes ONE 64-bit record {state, value}; state says whether value is
+// the tile's own aggregate or its inclusive prefix.  Flag and value travel in one
+// relaxed 64-bit store, so they cannot tear and no fence is needed (the reference
+// packs the same way in BlockInfo, evals/4090_scan/main.cu:21-37, but keeps two
+// words per tile).
+//
+// No-deadlock argument, as in the reference: a tile only ever waits for tiles with
+// smaller tickets; a ticket is drawn only when a slot is free, so the load of a
+// ticketed tile never waits on anything, and the CTA holding the smallest unresolved
+// ticket can always finish it.  CTAs need not be co-resident.  Every wait is bounded
+// all the same: one that runs out raises an abort flag and a status code, all roles
+// unwind and the kernel returns.
 #include "common.cuh"
 
 namespace prism_b200 {
@@ -36,16 +49,20 @@ constexpr uint32_t kStateInvalid = 0u;
 constexpr uint32_t kStateAggregate = 1u;
 constexpr uint32_t kStatePrefix = 2u;
 constexpr uint32_t kMaxPolls = 1u << 20;
-constexpr size_t kHeaderBytes = 128;  // [0] ticket, [1] abort flag; descriptors follow
+constexpr size_t kHeaderBytes = 128;  // [0] ticket, [1] abort flag; the records follow
 
-template <int THREADS, int VEC>
-struct ScanCfg {
-    static constexpr int kThreads = THREADS;
-    static constexpr int kWarps = THREADS / 32;
-    static constexpr int kItems = 4 * VEC;                       // elements per thread
-    static constexpr int kWarpElems = 32 * kItems;               // contiguous elements per warp
-    static constexpr int kTile = THREADS * kItems;               // elements per CTA
-};
+constexpr int kScanThreads = 256;               // 8 scan warps
+constexpr int kThreads = kScanThreads + 64;     // + producer warp + look-back warp
+constexpr int kVecs = 4;                        // 16-byte vectors per lane
+constexpr int kTile = kScanThreads * 4 * kVecs; // 4096 elements = 16 KB
+constexpr int kWarpElems = 128 * kVecs;         // contiguous elements per scan warp
+constexpr int kSlots = 4;                       // ring depth: 3 CTAs of 64 KB per SM
+constexpr int kLag = 3;                         // tiles parked between phase A and phase B
+constexpr uint32_t kSentinel = 0xFFFFFFFFu;
+static_assert(kLag >= 1 && kLag <= kSlots - 1, "one slot must always be free for the producer");
+
+constexpr size_t kSlotBytes = static_cast<size_t>(kTile) * 4;
+constexpr size_t kSmemBytes = kSlots * kSlotBytes + 4 * kSlots * 8 /* barriers */ + 3 * kSlots * 4 + 2 * 8 * 4 + 32;
 
 __device__ __forceinline__ uint64_t ld_desc(const uint64_t* p) {
     uint64_t v;
@@ -68,233 +85,315 @@ __device__ __forceinline__ uint32_t warp_sum(uint32_t v) {
     return v;
 }
 
-// TUNING ONLY: per-tile trace of the look-back (windows read, re-polls, timestamps).
-#ifdef PRISM_SCAN_TRACE
-__device__ unsigned long long g_trace[4 * 65536];
-__device__ unsigned int g_trace_polls;
-#endif
-
-__device__ __forceinline__ uint64_t poll_desc(const uint64_t* p, uint64_t first, const uint32_t* abort_flag) {
-    uint64_t d = first;
-    uint32_t polls = 0;
-    while (static_cast<uint32_t>(d) == kStateInvalid) {
-        if (++polls >= kMaxPolls) break;
-        if ((polls & 1023u) == 0u && ld_flag(abort_flag) != 0u) break;
-        d = ld_desc(p);
-    }
-#ifdef PRISM_SCAN_TRACE
-    if (polls) atomicAdd(&g_trace_polls, polls);
-#endif
-    return d;
+__device__ __forceinline__ void bulk_load_tile(void* dst_smem, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_u32(dst_smem)),
+                 "l"(src), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
 }
 
-// Sum of the tiles before `tile`, found by walking the records backwards, 32 * NW
-// per probe, until one that already carries an inclusive prefix.  The rate at which
-// prefixes can propagate is (records per probe) x (tile bytes) per L2 round trip, so
-// wide probes and large tiles are what keep this off the critical path.  Executed by
-// one full warp.  *failed is set if a bounded poll ran out or an abort was seen.
-template <int NW>
-__device__ __forceinline__ uint32_t lookback(uint32_t tile, const uint64_t* desc,
-                                             const uint32_t* abort_flag, bool* failed) {
+// Sum of the tiles before `tile`, found by walking the records backwards 32 at a
+// time until one that already carries an inclusive prefix (the job of the reference's
+// lookback_to_prev_blocks, generated/lookback_to_prev_blocks.cu:8-25, done by a warp
+// instead of a thread and with bounded spins).  *failed is set if a poll ran out or
+// an abort was seen.
+__device__ __forceinline__ uint32_t lookback(uint32_t tile, const uint64_t* desc, const uint32_t* abort_flag,
+                                             bool* failed) {
     const int lane = threadIdx.x & 31;
     uint32_t exclusive = 0;
     long long idx = static_cast<long long>(tile) - 1 - lane;
     *failed = false;
-#ifdef PRISM_SCAN_TRACE
-    unsigned long long rounds = 0;
-#endif
     while (true) {
-#ifdef PRISM_SCAN_TRACE
-        ++rounds;
-        if (lane == 0 && tile < 65536) g_trace[4 * tile + 2] = rounds;
-#endif
         // A slot before tile 0 behaves like a finished tile with prefix 0.
-        uint64_t d[NW];
-#pragma unroll
-        for (int w = 0; w < NW; ++w) {
-            const long long i = idx - 32 * w;
-            d[w] = i >= 0 ? ld_desc(desc + i) : static_cast<uint64_t>(kStatePrefix);
-        }
-#pragma unroll
-        for (int w = 0; w < NW; ++w) {
-            const long long i = idx - 32 * w;
-            if (i >= 0) d[w] = poll_desc(desc + i, d[w], abort_flag);
-            const uint32_t state = static_cast<uint32_t>(d[w]);
-            const uint32_t value = static_cast<uint32_t>(d[w] >> 32);
-            if (!__all_sync(0xffffffffu, state != kStateInvalid)) {
-                *failed = true;
-                return exclusive;
+        uint64_t d = kStatePrefix;
+        if (idx >= 0) {
+            uint32_t polls = 0;
+            d = ld_desc(desc + idx);
+            while (static_cast<uint32_t>(d) == kStateInvalid) {
+                if (++polls >= kMaxPolls) break;
+                if ((polls & 1023u) == 0u && ld_flag(abort_flag) != 0u) break;
+                d = ld_desc(desc + idx);
             }
-            const unsigned has_prefix = __ballot_sync(0xffffffffu, state == kStatePrefix);
-            if (has_prefix) {
-                const int first = __ffs(has_prefix) - 1;  // nearest predecessor with a prefix
-                exclusive += warp_sum(lane <= first ? value : 0u);
-                return exclusive;
-            }
-            exclusive += warp_sum(value);
         }
-        idx -= 32 * NW;
+        const uint32_t state = static_cast<uint32_t>(d);
+        const uint32_t value = static_cast<uint32_t>(d >> 32);
+        if (!__all_sync(0xffffffffu, state != kStateInvalid)) {
+            *failed = true;
+            return exclusive;
+        }
+        const unsigned has_prefix = __ballot_sync(0xffffffffu, state == kStatePrefix);
+        if (has_prefix) {
+            const int first = __ffs(has_prefix) - 1;  // nearest predecessor with a prefix
+            exclusive += warp_sum(lane <= first ? value : 0u);
+            return exclusive;
+        }
+        exclusive += warp_sum(value);
+        idx -= 32;
     }
 }
 
-template <int THREADS, int VEC, int NW, bool SEEDED, bool TICKET = true, bool LOOKBACK = true>
-__device__ __forceinline__ void scan_tile_body(uint32_t n, uint32_t* x, uint32_t* header,
-                                               uint64_t* desc, const uint32_t* totals, int rank) {
-    using Cfg = ScanCfg<THREADS, VEC>;
-    constexpr int kScanWarps = Cfg::kWarps;
-    __shared__ uint32_t s_tile;
-    __shared__ uint32_t s_warp_total[kScanWarps];
-    __shared__ uint32_t s_prefix;
+template <bool SEEDED>
+__device__ __forceinline__ void scan_body(uint32_t n, uint32_t* x, uint32_t* header, uint64_t* desc,
+                                          const uint32_t* totals, int rank) {
+    constexpr int S = kSlots;
+    extern __shared__ __align__(128) unsigned char p_smem[];
+    uint32_t* slots = reinterpret_cast<uint32_t*>(p_smem);
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(p_smem + S * kSlotBytes);  // tile landed in the slot
+    uint64_t* agg_bar = full_bar + S;                                           // phase A done, aggregate known
+    uint64_t* pre_bar = agg_bar + S;                                            // exclusive prefix known
+    uint64_t* empty_bar = pre_bar + S;                                          // phase B done, slot reusable
+    uint32_t* s_tile = reinterpret_cast<uint32_t*>(empty_bar + S);
+    uint32_t* s_agg = s_tile + S;
+    uint32_t* s_excl = s_agg + S;
+    uint32_t* s_warp_total = s_excl + S;  // [2][8]
+    volatile uint32_t* abort_flag = s_warp_total + 16;
+    volatile uint32_t* s_ctrl = s_warp_total + 17;  // [2]: outcome of thread 0's bounded wait, double-buffered
 
     const int tid = threadIdx.x;
     const int lane = tid & 31;
     const int warp = tid >> 5;
+    const uint32_t tiles = static_cast<uint32_t>((static_cast<unsigned long long>(n) + kTile - 1) / kTile);
 
-    if (TICKET) {
-        if (tid == 0) s_tile = atomicAdd(header, 1u);
-        __syncthreads();
-    }
-    const uint32_t tile = TICKET ? s_tile : blockIdx.x;
-    const unsigned long long base =
-        static_cast<unsigned long long>(tile) * Cfg::kTile + static_cast<unsigned long long>(warp) * Cfg::kWarpElems;
-    const bool full_tile = static_cast<unsigned long long>(tile) * Cfg::kTile + Cfg::kTile <= n;
-
-    uint4 v[VEC];
-    if (full_tile) {
-#pragma unroll
-        for (int j = 0; j < VEC; ++j)
-            v[j] = __ldcg(reinterpret_cast<const uint4*>(x + base + j * 128 + lane * 4));
-    } else {
-#pragma unroll
-        for (int j = 0; j < VEC; ++j) {
-            const unsigned long long e = base + j * 128 + lane * 4;
-            v[j].x = (e + 0 < n) ? x[e + 0] : 0u;
-            v[j].y = (e + 1 < n) ? x[e + 1] : 0u;
-            v[j].z = (e + 2 < n) ? x[e + 2] : 0u;
-            v[j].w = (e + 3 < n) ? x[e + 3] : 0u;
+    if (tid == 0) {
+        for (int s = 0; s < S; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&agg_bar[s], 1);
+            mbar_init(&pre_bar[s], 1);
+            mbar_init(&empty_bar[s], kScanThreads / 32);
         }
+        *abort_flag = 0;
+        fence_barrier_init();
     }
-
-    // Inside each 16-byte group, then across the 32 lanes of each of the VEC chunks.
-    uint32_t sum[VEC], inc[VEC];
-#pragma unroll
-    for (int j = 0; j < VEC; ++j) {
-        v[j].y += v[j].x;
-        v[j].z += v[j].y;
-        v[j].w += v[j].z;
-        sum[j] = v[j].w;
-        inc[j] = sum[j];
-    }
-#pragma unroll
-    for (int d = 1; d < 32; d <<= 1) {
-#pragma unroll
-        for (int j = 0; j < VEC; ++j) {
-            const uint32_t up = __shfl_up_sync(0xffffffffu, inc[j], d);
-            if (lane >= d) inc[j] += up;
-        }
-    }
-    // Offset of each chunk inside the warp, and the warp's total.
-    uint32_t chunk_off = 0;
-    uint32_t excl[VEC];
-#pragma unroll
-    for (int j = 0; j < VEC; ++j) {
-        excl[j] = chunk_off + inc[j] - sum[j];
-        chunk_off += __shfl_sync(0xffffffffu, inc[j], 31);
-    }
-    if (lane == 0) s_warp_total[warp] = chunk_off;
     __syncthreads();
 
-    uint32_t warp_off = 0, aggregate = 0;
-#pragma unroll
-    for (int w = 0; w < kScanWarps; ++w) {
-        const uint32_t t = s_warp_total[w];
-        if (w < warp) warp_off += t;
-        aggregate += t;
+    if (warp == kScanThreads / 32) {
+        // ------------------------------ producer ------------------------------
+        if (lane == 0) {
+            for (uint32_t i = 0;; ++i) {
+                const int s = i % S;
+                if (!mbar_wait_bounded(&empty_bar[s], ((i / S) & 1u) ^ 1u, abort_flag)) {
+                    *abort_flag = 1;
+                    atomicExch(header + 1, 1u);
+                    raise_device_status(DEV_SCAN_LOOKBACK_TIMEOUT);
+                    break;
+                }
+                // The ticket of the reference (generated/get_block_idx_from_global_counter.cu:1-13),
+                // drawn only now that the tile has somewhere to go.
+                const uint32_t t = atomicAdd(header, 1u);
+                if (t >= tiles) {
+                    s_tile[s] = kSentinel;
+                    mbar_arrive(&full_bar[s]);
+                    break;
+                }
+                s_tile[s] = t;
+                const unsigned long long base = static_cast<unsigned long long>(t) * kTile;
+                const unsigned long long left = n - base;
+                const uint32_t cnt = left < kTile ? static_cast<uint32_t>(left) : kTile;
+                const uint32_t bytes = (cnt * 4u) & ~15u;  // whole 16-byte vectors; a ragged end is read by its owner
+                if (bytes) {
+                    mbar_arrive_expect_tx(&full_bar[s], bytes);
+                    bulk_load_tile(slots + s * kTile, x + base, bytes, &full_bar[s]);
+                } else {
+                    mbar_arrive(&full_bar[s]);
+                }
+            }
+        }
+        return;
     }
 
-    if (warp == 0) {
-        uint32_t exclusive = 0;
-        if (tile == 0) {
-            if (SEEDED) {
-                for (int r = 0; r < rank; ++r) exclusive += totals[r];
-            }
-            if (lane == 0) st_desc(desc, kStatePrefix, exclusive + aggregate);
-        } else {
-            if (lane == 0) st_desc(desc + tile, kStateAggregate, aggregate);
-#ifdef PRISM_SCAN_TRACE
-            if (lane == 0 && tile < 65536) g_trace[4 * tile + 0] = global_timer_ns();
-#endif
-            bool failed;
-            exclusive = LOOKBACK ? lookback<NW>(tile, desc, header + 1, &failed) : 0u;
-            if (!LOOKBACK) failed = false;
-#ifdef PRISM_SCAN_TRACE
-            if (lane == 0 && tile < 65536) g_trace[4 * tile + 1] = global_timer_ns();
-#endif
-            if (lane == 0) {
-                if (failed) {
+    if (warp == kScanThreads / 32 + 1) {
+        // ------------------------------ look-back ------------------------------
+        for (uint32_t k = 0;; ++k) {
+            const int s = k % S;
+            const bool ready = mbar_wait_bounded(&agg_bar[s], (k / S) & 1u, abort_flag);
+            if (!__all_sync(0xffffffffu, ready)) {
+                if (lane == 0) {
+                    *abort_flag = 1;
                     atomicExch(header + 1, 1u);
                     raise_device_status(DEV_SCAN_LOOKBACK_TIMEOUT);
                 }
-                st_desc(desc + tile, kStatePrefix, exclusive + aggregate);
+                break;
             }
+            const uint32_t t = s_tile[s];
+            if (t == kSentinel) break;
+            const uint32_t agg = s_agg[s];
+            uint32_t exclusive = 0;
+            bool failed = false;
+            if (t == 0) {
+                if (SEEDED)
+                    for (int r = 0; r < rank; ++r) exclusive += totals[r];
+            } else {
+                exclusive = lookback(t, desc, header + 1, &failed);
+            }
+            if (lane == 0) {
+                if (failed) {
+                    *abort_flag = 1;
+                    atomicExch(header + 1, 1u);
+                    raise_device_status(DEV_SCAN_LOOKBACK_TIMEOUT);
+                }
+                st_desc(desc + t, kStatePrefix, exclusive + agg);  // as write_block_prefix.cu:8-10
+                s_excl[s] = exclusive;
+                mbar_arrive(&pre_bar[s]);
+            }
+            __syncwarp();
+            if (failed) break;
         }
-        if (lane == 0) s_prefix = exclusive;
+        return;
     }
-    __syncthreads();
-    const uint32_t add = s_prefix + warp_off;
 
-    if (full_tile) {
-#pragma unroll
-        for (int j = 0; j < VEC; ++j) {
-            const uint32_t a = add + excl[j];
-            v[j].x += a; v[j].y += a; v[j].z += a; v[j].w += a;
-            __stcg(reinterpret_cast<uint4*>(x + base + j * 128 + lane * 4), v[j]);
+    // ------------------------------ scan warps ------------------------------
+    // Lane l of warp w owns the 16-byte vectors at tile-local elements
+    // w * 512 + q * 128 + l * 4 (q = 0..3), in phase A and again in phase B.
+    const int vec0 = warp * kWarpElems + lane * 4;
+    uint32_t i = 0, j = 0;  // ring items taken through phase A / phase B so far
+    bool drained = false;
+    // Only thread 0 performs the bounded wait; the outcome reaches the other 255 scan
+    // threads through a named barrier, so that all of them always take the same branch
+    // (a thread that gave up on its own would leave the others stuck at the next barrier).
+    uint32_t waits = 0;
+    auto wait_uniform = [&](uint64_t* bar, uint32_t parity) -> bool {
+        volatile uint32_t* c = s_ctrl + (waits++ & 1u);
+        if (tid == 0) {
+            const bool got = mbar_wait_bounded(bar, parity, abort_flag);
+            if (!got) {
+                *abort_flag = 1;
+                atomicExch(header + 1, 1u);
+                raise_device_status(DEV_SCAN_LOOKBACK_TIMEOUT);
+            }
+            *c = got ? 1u : 0u;
         }
-    } else {
+        asm volatile("bar.sync 1, %0;" ::"n"(kScanThreads) : "memory");
+        const bool got = *c != 0u;
+        if (got) (void)mbar_try_wait(bar, parity);  // this thread's own acquire of the completed phase
+        return got;
+    };
+
+    while (true) {
+        if (!drained && i - j < static_cast<uint32_t>(kLag)) {
+            // ---------------- phase A on ring item i ----------------
+            const int s = i % S;
+            if (!wait_uniform(&full_bar[s], (i / S) & 1u)) break;
+            const uint32_t t = s_tile[s];
+            if (t == kSentinel) {
+                drained = true;
+                if (tid == 0) mbar_arrive(&agg_bar[s]);  // hands the end mark on to the look-back warp
+                continue;
+            }
+            uint32_t* slot = slots + s * kTile;
+            const unsigned long long base = static_cast<unsigned long long>(t) * kTile;
+            const unsigned long long left = n - base;
+            const uint32_t cnt = left < kTile ? static_cast<uint32_t>(left) : kTile;
+            uint4 v[kVecs];
 #pragma unroll
-        for (int j = 0; j < VEC; ++j) {
-            const uint32_t a = add + excl[j];
-            const unsigned long long e = base + j * 128 + lane * 4;
-            if (e + 0 < n) x[e + 0] = v[j].x + a;
-            if (e + 1 < n) x[e + 1] = v[j].y + a;
-            if (e + 2 < n) x[e + 2] = v[j].z + a;
-            if (e + 3 < n) x[e + 3] = v[j].w + a;
+            for (int q = 0; q < kVecs; ++q) {
+                const uint32_t e = vec0 + q * 128;
+                if (e + 4 <= (cnt & ~3u)) {
+                    v[q] = *reinterpret_cast<const uint4*>(slot + e);
+                } else {  // the ragged end of the last tile: straight from global memory, zero beyond n
+                    v[q].x = (e + 0 < cnt) ? x[base + e + 0] : 0u;
+                    v[q].y = (e + 1 < cnt) ? x[base + e + 1] : 0u;
+                    v[q].z = (e + 2 < cnt) ? x[base + e + 2] : 0u;
+                    v[q].w = (e + 3 < cnt) ? x[base + e + 3] : 0u;
+                }
+            }
+            // Inside each 16-byte group, then across the 32 lanes of each of the four chunks
+            // (the work of scan_warps.cu / naive_scan_warp_ends.cu in the reference).
+            uint32_t sum[kVecs], inc[kVecs];
+#pragma unroll
+            for (int q = 0; q < kVecs; ++q) {
+                v[q].y += v[q].x;
+                v[q].z += v[q].y;
+                v[q].w += v[q].z;
+                sum[q] = v[q].w;
+                inc[q] = sum[q];
+            }
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+#pragma unroll
+                for (int q = 0; q < kVecs; ++q) {
+                    const uint32_t up = __shfl_up_sync(0xffffffffu, inc[q], d);
+                    if (lane >= d) inc[q] += up;
+                }
+            }
+            uint32_t chunk_off = 0, excl[kVecs];
+#pragma unroll
+            for (int q = 0; q < kVecs; ++q) {
+                excl[q] = chunk_off + inc[q] - sum[q];
+                chunk_off += __shfl_sync(0xffffffffu, inc[q], 31);
+            }
+            uint32_t* wt = s_warp_total + (i & 1u) * 8;
+            if (lane == 0) wt[warp] = chunk_off;
+            asm volatile("bar.sync 1, %0;" ::"n"(kScanThreads) : "memory");
+            uint32_t warp_off = 0, aggregate = 0;
+#pragma unroll
+            for (int w = 0; w < kScanThreads / 32; ++w) {
+                const uint32_t tot = wt[w];
+                if (w < warp) warp_off += tot;
+                aggregate += tot;
+            }
+            if (tid == 0) {
+                if (t != 0) st_desc(desc + t, kStateAggregate, aggregate);  // as write_block_aggregate.cu:8-10
+                s_agg[s] = aggregate;
+                mbar_arrive(&agg_bar[s]);
+            }
+            // Tile-local inclusive scan back into the slot; the same lane reads it again in phase B.
+#pragma unroll
+            for (int q = 0; q < kVecs; ++q) {
+                const uint32_t a = warp_off + excl[q];
+                v[q].x += a; v[q].y += a; v[q].z += a; v[q].w += a;
+                *reinterpret_cast<uint4*>(slot + vec0 + q * 128) = v[q];
+            }
+            ++i;
+        } else if (j < i) {
+            // ---------------- phase B on ring item j (update_with_new_data_and_writeback.cu) ----------------
+            const int s = j % S;
+            if (!wait_uniform(&pre_bar[s], (j / S) & 1u)) break;
+            const uint32_t t = s_tile[s];
+            const uint32_t add = s_excl[s];
+            const uint32_t* slot = slots + s * kTile;
+            const unsigned long long base = static_cast<unsigned long long>(t) * kTile;
+            const unsigned long long left = n - base;
+            const uint32_t cnt = left < kTile ? static_cast<uint32_t>(left) : kTile;
+#pragma unroll
+            for (int q = 0; q < kVecs; ++q) {
+                const uint32_t e = vec0 + q * 128;
+                uint4 v = *reinterpret_cast<const uint4*>(slot + e);
+                v.x += add; v.y += add; v.z += add; v.w += add;
+                if (e + 4 <= cnt) {
+                    __stcg(reinterpret_cast<uint4*>(x + base + e), v);
+                } else {
+                    if (e + 0 < cnt) x[base + e + 0] = v.x;
+                    if (e + 1 < cnt) x[base + e + 1] = v.y;
+                    if (e + 2 < cnt) x[base + e + 2] = v.z;
+                    if (e + 3 < cnt) x[base + e + 3] = v.w;
+                }
+            }
+            // The slot was written with ordinary stores; the next write comes from the bulk-copy engine.
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty_bar[s]);
+            ++j;
+        } else {
+            break;  // drained and every tile written
         }
     }
 }
-
-// Tile geometry: threads per CTA, 16-byte vectors per thread, look-back probes of 32 * NW records.
-constexpr int kThreads = 256;
-constexpr int kVec = 4;
-constexpr int kNW = 1;
-constexpr int kMinTile = 4096;  // the workspace is sized for the smallest tile any variant uses
 
 }  // namespace
 
 // Same parameter list as the reference entry point (generated/scan_kernel.cu:1):
 // n elements, data in place, the ticket counter, the per-tile records.  Here the
 // counter word is followed by an abort flag and a record is one 64-bit word.
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 3)
 scan_kernel(uint32_t n, uint32_t* x, uint32_t* block_idx_counter, int* block_infos) {
-    scan_tile_body<kThreads, kVec, kNW, false>(n, x, block_idx_counter, reinterpret_cast<uint64_t*>(block_infos),
-                                               nullptr, 0);
+    scan_body<false>(n, x, block_idx_counter, reinterpret_cast<uint64_t*>(block_infos), nullptr, 0);
 }
 
 // Sharded form: tile 0 starts from totals[0] + ... + totals[rank-1].
-__global__ void __launch_bounds__(kThreads)
-scan_kernel_seeded(uint32_t n, uint32_t* x, uint32_t* block_idx_counter, int* block_infos,
-                   const uint32_t* totals, int rank) {
-    scan_tile_body<kThreads, kVec, kNW, true>(n, x, block_idx_counter, reinterpret_cast<uint64_t*>(block_infos),
-                                              totals, rank);
-}
-
-// TUNING ONLY: other geometries, selected with PRISM_B200_SCAN_VARIANT.
-template <int THREADS, int VEC, int NW, bool TICKET = true, bool LOOKBACK = true>
-__global__ void __launch_bounds__(THREADS)
-scan_kernel_var(uint32_t n, uint32_t* x, uint32_t* block_idx_counter, int* block_infos, const uint32_t* totals,
-                int rank) {
-    scan_tile_body<THREADS, VEC, NW, true, TICKET, LOOKBACK>(n, x, block_idx_counter,
-                                                             reinterpret_cast<uint64_t*>(block_infos), totals, rank);
+__global__ void __launch_bounds__(kThreads, 3)
+scan_kernel_seeded(uint32_t n, uint32_t* x, uint32_t* block_idx_counter, int* block_infos, const uint32_t* totals,
+                   int rank) {
+    scan_body<true>(n, x, block_idx_counter, reinterpret_cast<uint64_t*>(block_infos), totals, rank);
 }
 
 __global__ void __launch_bounds__(256) reduce_u32_kernel(size_t n, const uint32_t* x, uint32_t* total) {
@@ -342,37 +441,52 @@ __global__ void __launch_bounds__(256) add_carry_kernel(size_t n, uint32_t* x, c
 
 namespace {
 
-size_t scan_tiles(size_t n) { return (n + kMinTile - 1) / kMinTile; }
+size_t scan_tiles(size_t n) { return (n + kTile - 1) / kTile; }
 
-using VarKernel = void (*)(uint32_t, uint32_t*, uint32_t*, int*, const uint32_t*, int);
-struct Variant { VarKernel k; int threads; int tile; };
-#define PRISM_VARIANT(T, V, W) Variant{scan_kernel_var<T, V, W>, T, T * 4 * V}
-const Variant kVariants[] = {
-    PRISM_VARIANT(256, 4, 1),   // 0
-    PRISM_VARIANT(256, 4, 2),   // 1
-    PRISM_VARIANT(512, 4, 1),   // 2
-    PRISM_VARIANT(512, 8, 1),   // 3
-    PRISM_VARIANT(512, 8, 2),   // 4
-    PRISM_VARIANT(256, 8, 2),   // 5
-    PRISM_VARIANT(1024, 4, 2),  // 6
-    PRISM_VARIANT(256, 16, 2),  // 7
-    PRISM_VARIANT(1024, 4, 1),  // 8
-    PRISM_VARIANT(512, 8, 4),   // 9
-    Variant{scan_kernel_var<512, 8, 1, false, true>, 512, 16384},   // 10 no ticket
-    Variant{scan_kernel_var<512, 8, 1, true, false>, 512, 16384},   // 11 no look-back (wrong results)
-    Variant{scan_kernel_var<512, 8, 1, false, false>, 512, 16384},  // 12 neither
-    Variant{scan_kernel_var<256, 4, 1, false, true>, 256, 4096},    // 13 no ticket
-    Variant{scan_kernel_var<256, 4, 1, false, false>, 256, 4096},   // 14 neither
-    Variant{scan_kernel_var<256, 8, 1, false, true>, 256, 8192},    // 15 no ticket
-};
-int scan_variant() {
-    static int v = -2;
-    if (v == -2) {
-        const char* e = getenv("PRISM_B200_SCAN_VARIANT");
-        v = e ? atoi(e) : -1;
-        if (v >= static_cast<int>(sizeof(kVariants) / sizeof(kVariants[0]))) v = -1;
+// Resident CTAs of the persistent kernel on the current device (SMs x CTAs per SM), found
+// once per device; also raises the kernels' dynamic shared-memory limit.
+int persistent_grid(unsigned* out) {
+    static unsigned cached[64] = {};
+    int dev = 0;
+    PRISM_CUDA_TRY(cudaGetDevice(&dev));
+    const bool cacheable = dev >= 0 && dev < 64;
+    if (cacheable && cached[dev]) {
+        *out = cached[dev];
+        return PRISM_B200_OK;
     }
-    return v;
+    int sms = 0, per_sm = 0;
+    PRISM_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    PRISM_CUDA_TRY(cudaFuncSetAttribute(scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        static_cast<int>(kSmemBytes)));
+    PRISM_CUDA_TRY(cudaFuncSetAttribute(scan_kernel_seeded, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        static_cast<int>(kSmemBytes)));
+    PRISM_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, scan_kernel, kThreads, kSmemBytes));
+    if (per_sm < 1 || sms < 1) return set_error(PRISM_B200_ERR_CUDA, "scan: the kernel does not fit on an SM");
+    *out = static_cast<unsigned>(sms * per_sm);
+    if (cacheable) cached[dev] = *out;
+    return PRISM_B200_OK;
+}
+
+// Re-arms the scratch (ticket, abort flag, every record: one memset where the reference
+// issues two, evals/4090_scan/main.cu:81-82) and launches the kernel.
+int scan_enqueue(size_t n, uint32_t* x, void* scratch, const uint32_t* totals, int rank, bool seeded,
+                 cudaStream_t stream) {
+    const uint32_t tiles = static_cast<uint32_t>(scan_tiles(n));
+    uint32_t* header = static_cast<uint32_t*>(scratch);
+    uint64_t* desc = reinterpret_cast<uint64_t*>(static_cast<char*>(scratch) + kHeaderBytes);
+    unsigned grid = 0;
+    if (int rc = persistent_grid(&grid)) return rc;
+    if (grid > tiles) grid = tiles;
+    PRISM_CUDA_TRY(cudaMemsetAsync(scratch, 0, kHeaderBytes + static_cast<size_t>(tiles) * sizeof(uint64_t), stream));
+    if (seeded)
+        scan_kernel_seeded<<<grid, kThreads, kSmemBytes, stream>>>(static_cast<uint32_t>(n), x, header,
+                                                                   reinterpret_cast<int*>(desc), totals, rank);
+    else
+        scan_kernel<<<grid, kThreads, kSmemBytes, stream>>>(static_cast<uint32_t>(n), x, header,
+                                                            reinterpret_cast<int*>(desc));
+    PRISM_CUDA_TRY(cudaGetLastError());
+    count_launch();
+    return PRISM_B200_OK;
 }
 
 int scan_launch(size_t n, uint32_t* x, void* workspace, const uint32_t* totals, int rank, bool seeded,
@@ -386,28 +500,7 @@ int scan_launch(size_t n, uint32_t* x, void* workspace, const uint32_t* totals, 
     if (seeded && (rank < 0 || (rank > 0 && !totals)))
         return set_error(PRISM_B200_ERR_INVALID_ARGUMENT, "scan_seeded: bad rank/totals");
     if (int rc = bind_status_word()) return rc;
-
-    const int var = scan_variant();
-    const int tile_elems = var >= 0 ? kVariants[var].tile : ScanCfg<kThreads, kVec>::kTile;
-    const uint32_t tiles = static_cast<uint32_t>((n + tile_elems - 1) / tile_elems);
-    uint32_t* header = static_cast<uint32_t*>(workspace);
-    uint64_t* desc = reinterpret_cast<uint64_t*>(static_cast<char*>(workspace) + kHeaderBytes);
-    // One memset re-arms ticket, abort flag and every record (the reference
-    // issues two, evals/4090_scan/main.cu:81-82).
-    PRISM_CUDA_TRY(cudaMemsetAsync(workspace, 0, kHeaderBytes + static_cast<size_t>(tiles) * sizeof(uint64_t), stream));
-    if (var >= 0)
-        kVariants[var].k<<<tiles, kVariants[var].threads, 0, stream>>>(static_cast<uint32_t>(n), x, header,
-                                                                       reinterpret_cast<int*>(desc), totals,
-                                                                       seeded ? rank : 0);
-    else if (seeded)
-        scan_kernel_seeded<<<tiles, kThreads, 0, stream>>>(static_cast<uint32_t>(n), x, header,
-                                                            reinterpret_cast<int*>(desc), totals, rank);
-    else
-        scan_kernel<<<tiles, kThreads, 0, stream>>>(static_cast<uint32_t>(n), x, header,
-                                                     reinterpret_cast<int*>(desc));
-    PRISM_CUDA_TRY(cudaGetLastError());
-    count_launch();
-    return PRISM_B200_OK;
+    return scan_enqueue(n, x, workspace, totals, rank, seeded, stream);
 }
 
 unsigned streaming_grid(size_t n4) {
@@ -437,7 +530,7 @@ using namespace prism_b200;
 namespace prism_b200 {
 namespace {
 constexpr size_t kStaticMaxN = 1ull << 28;  // elements (1 GiB of data)
-constexpr size_t kStaticScratchBytes = kHeaderBytes + (kStaticMaxN / kMinTile) * sizeof(uint64_t);  // 524,416 B
+constexpr size_t kStaticScratchBytes = kHeaderBytes + (kStaticMaxN / kTile) * sizeof(uint64_t);  // 524,416 B
 }  // namespace
 }  // namespace prism_b200
 
@@ -481,28 +574,10 @@ extern "C" int prism_b200_scan_static(size_t n, uint32_t* x, void* stream) {
         return set_error(PRISM_B200_ERR_MISALIGNED, "scan_static: x not 16-byte aligned");
     void* scratch = nullptr;
     if (int rc = static_scratch_address(&scratch)) return rc;
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
-    constexpr int tile_elems = ScanCfg<kThreads, kVec>::kTile;
-    const uint32_t tiles = static_cast<uint32_t>((n + tile_elems - 1) / tile_elems);
-    uint32_t* header = static_cast<uint32_t*>(scratch);
-    uint64_t* desc = reinterpret_cast<uint64_t*>(static_cast<char*>(scratch) + kHeaderBytes);
-    // The array still holds the previous call's ticket, abort flag and records.
-    PRISM_CUDA_TRY(cudaMemsetAsync(scratch, 0, kHeaderBytes + static_cast<size_t>(tiles) * sizeof(uint64_t), s));
-    scan_kernel<<<tiles, kThreads, 0, s>>>(static_cast<uint32_t>(n), x, header, reinterpret_cast<int*>(desc));
-    PRISM_CUDA_TRY(cudaGetLastError());
-    count_launch();
-    return PRISM_B200_OK;
+    // The array still holds the previous call's ticket, abort flag and records; scan_enqueue clears
+    // what this call will use.  It does not set up the pinned status word (that would allocate).
+    return scan_enqueue(n, x, scratch, nullptr, 0, false, static_cast<cudaStream_t>(stream));
 }
-
-#ifdef PRISM_SCAN_TRACE
-extern "C" int prism_b200_scan_trace(unsigned long long* out, unsigned int* polls) {
-    cudaMemcpyFromSymbol(out, g_trace, sizeof(unsigned long long) * 4 * 65536);
-    cudaMemcpyFromSymbol(polls, g_trace_polls, 4);
-    unsigned int z = 0;
-    cudaMemcpyToSymbol(g_trace_polls, &z, 4);
-    return 0;
-}
-#endif
 
 extern "C" int prism_b200_scan_workspace_size(size_t n, size_t* bytes) {
     if (!bytes) return set_error(PRISM_B200_ERR_INVALID_ARGUMENT, "scan_workspace_size: null bytes");

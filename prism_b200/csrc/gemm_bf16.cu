@@ -129,11 +129,12 @@ __device__ __forceinline__ uint32_t pack_bf16(uint32_t lo_f32_bits, uint32_t hi_
 }
 
 // Tile t -> (n-tile, m-tile): GROUP_M m-tiles are walked for each n-tile before n advances.
-__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& tm, int& tn) {
-    const int per_group = g16::GROUP_M * tiles_n;
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& tm, int& tn,
+                                            int group_m = g16::GROUP_M) {
+    const int per_group = group_m * tiles_n;
     const int group = t / per_group;
-    const int first_m = group * g16::GROUP_M;
-    const int rows = min(g16::GROUP_M, tiles_m - first_m);
+    const int first_m = group * group_m;
+    const int rows = min(group_m, tiles_m - first_m);
     const int in = t - group * per_group;
     tm = first_m + in % rows;
     tn = in / rows;
@@ -336,6 +337,267 @@ cutlass_my_h100_match_no_tail(int M, int N, int K, __nv_bfloat16* C, const __gri
     }
 }
 
+// ============================================================================
+// Two-CTA form: a cluster of two CTAs on neighbouring SMs computes one 256 (n) x
+// 256 (m) tile with tcgen05.mma.cta_group::2.  Each CTA loads its own 128 rows of
+// both operands (32 KB per stage instead of 48 KB, six stages instead of four) and
+// holds the accumulator rows of its own 128 n; the tensor cores of each SM read the
+// other SM's half of the m-side operand through the pair, so every operand byte is
+// staged once per pair instead of once per CTA.
+//   * CTA 0 (the leader) issues every MMA.  The TMA loads of both CTAs complete on
+//     the LEADER's "full" barrier (the .cta_group::2 form of the load allows the
+//     barrier to live in the other CTA); the leader expects both CTAs' bytes.
+//   * After the MMAs of a stage the leader commits twice: to its own "empty"
+//     barrier and, through its cluster address, to the other CTA's.  The same for
+//     "accumulator full".  No multicast qualifier is used anywhere.
+//   * The epilogue warps of both CTAs arrive on the leader's "accumulator empty"
+//     barrier (count 8).
+//   * The two CTAs synchronise as a cluster after barrier set-up and before tensor
+//     memory is released, so neither can touch a barrier or operand of a CTA that
+//     is not there yet or has already left.
+// ============================================================================
+namespace g16 {
+struct PairCfg {
+    static constexpr int BLOCK = 256;      // tile edge of the pair, both in n and in m
+    static constexpr int HALF = 128;       // rows of either operand staged by one CTA
+    static constexpr int STAGES = 6;
+    static constexpr uint32_t HALF_BYTES = HALF * BLOCK_K * 2;
+    static constexpr uint32_t STAGE_BYTES = 2 * HALF_BYTES;  // per CTA
+    static constexpr size_t SMEM_BYTES = 1024 + static_cast<size_t>(STAGES) * STAGE_BYTES + (2 * STAGES + 4) * 8 + 16;
+};
+}  // namespace g16
+
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// Address of a shared-memory object of CTA `rank` of this cluster, in the shared::cluster window.
+__device__ __forceinline__ uint32_t cluster_addr(const void* smem_ptr, uint32_t rank) {
+    uint32_t out;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(smem_u32(smem_ptr)), "r"(rank));
+    return out;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar_addr) : "memory");
+}
+// TMA load whose completion is counted on a barrier that may live in the other CTA of the pair.
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, int x, int y, uint32_t cluster_bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(cluster_bar)
+        : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                               uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        "}\n" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit_pair(uint32_t cluster_bar_addr) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar_addr)
+                 : "memory");
+}
+
+template <int GROUP>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(g16::THREADS, 1)
+cutlass_my_h100_match_no_tail_pair(int M, int N, int K, __nv_bfloat16* C, const __grid_constant__ CUtensorMap tensorMapA,
+                                   const __grid_constant__ CUtensorMap tensorMapB) {
+    using namespace g16;
+    using P_ = PairCfg;
+    constexpr int STAGES = P_::STAGES;
+    constexpr uint32_t IDESC = instr_desc(P_::BLOCK, P_::BLOCK);  // M = 256 across the pair, N = 256
+
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    unsigned char* ring = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);  // same offset in both CTAs
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(ring + STAGES * P_::STAGE_BYTES);
+    uint64_t* empty_bar = full_bar + STAGES;
+    uint64_t* acc_full_bar = empty_bar + STAGES;   // [2]
+    uint64_t* acc_empty_bar = acc_full_bar + 2;    // [2], only the leader's are used
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty_bar + 2);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+    volatile uint32_t* never_flag = tmem_slot + 2;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_cta_rank();
+    const bool leader = rank == 0;
+    const int pair = blockIdx.x >> 1;
+    const int pairs = gridDim.x >> 1;
+    const int tiles_m = M / P_::BLOCK;
+    const int tiles_n = N / P_::BLOCK;
+    const int total_tiles = tiles_m * tiles_n;
+    const int k_blocks = K / BLOCK_K;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(&acc_full_bar[a], 1);
+            mbar_init(&acc_empty_bar[a], 2 * EPI_WARPS);
+        }
+        *abort_flag = 0;
+        *never_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        __syncwarp();
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"(static_cast<uint32_t>(TMEM_COLS))
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    cluster_sync_all();   // barriers of both CTAs are initialised, tensor memory is allocated
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    bool timed_out = false;
+
+    if (warp == 0) {
+        // ------------------------- TMA producer (both CTAs) -------------------------
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tensorMapA)) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tensorMapB)) : "memory");
+            int stage = 0;
+            uint32_t phase = 0;
+            for (int t = pair; t < total_tiles && !timed_out; t += pairs) {
+                int tm, tn;
+                tile_coords(t, tiles_m, tiles_n, tm, tn, GROUP);
+                const int n_row = tn * P_::BLOCK + static_cast<int>(rank) * P_::HALF;
+                const int m_row = tm * P_::BLOCK + static_cast<int>(rank) * P_::HALF;
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag)) {
+                        timed_out = true;
+                        break;
+                    }
+                    unsigned char* p_dst = ring + stage * P_::STAGE_BYTES;
+                    unsigned char* q_dst = p_dst + P_::HALF_BYTES;
+                    const uint32_t leader_full = cluster_addr(&full_bar[stage], 0);
+                    if (leader) mbar_arrive_expect_tx(&full_bar[stage], 2 * P_::STAGE_BYTES);  // both CTAs' bytes
+                    tma_load_2d_pair(p_dst, &tensorMapB, kb * BLOCK_K, n_row, leader_full);
+                    tma_load_2d_pair(q_dst, &tensorMapA, kb * BLOCK_K, m_row, leader_full);
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------- MMA issuer (leader only) -------------------------
+        if (leader && lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc = 0;
+            uint32_t acc_phase = 0;
+            for (int t = pair; t < total_tiles && !timed_out; t += pairs) {
+                if (!mbar_wait_bounded(&acc_empty_bar[acc], acc_phase ^ 1u, abort_flag)) {
+                    timed_out = true;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * P_::BLOCK);
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag)) {
+                        timed_out = true;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t p_addr = smem_u32(ring + stage * P_::STAGE_BYTES);
+                    const uint64_t p_desc = smem_desc_k_sw128(p_addr);
+                    const uint64_t q_desc = smem_desc_k_sw128(p_addr + P_::HALF_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BLOCK_K / UMMA_K; ++k)
+                        umma_bf16_pair(d_tmem, p_desc + 2u * k, q_desc + 2u * k, IDESC, (kb | k) != 0 ? 1u : 0u);
+                    umma_commit_pair(cluster_addr(&empty_bar[stage], 0));   // frees the stage in this CTA ...
+                    umma_commit_pair(cluster_addr(&empty_bar[stage], 1));   // ... and in the other one
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (timed_out) break;
+                umma_commit_pair(cluster_addr(&acc_full_bar[acc], 0));
+                umma_commit_pair(cluster_addr(&acc_full_bar[acc], 1));
+                if (++acc == 2) {
+                    acc = 0;
+                    acc_phase ^= 1u;
+                }
+            }
+        }
+    } else {
+        // ------------------------- epilogue warps (both CTAs) -------------------------
+        const int quarter = warp & 3;
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        for (int t = pair; t < total_tiles; t += pairs) {
+            int tm, tn;
+            tile_coords(t, tiles_m, tiles_n, tm, tn, GROUP);
+            const bool ready = mbar_wait_bounded(&acc_full_bar[acc], acc_phase, abort_flag);
+            if (!__all_sync(0xffffffffu, ready)) {
+                timed_out = true;
+                break;
+            }
+            tc_fence_after();
+            const size_t n = static_cast<size_t>(tn) * P_::BLOCK + rank * P_::HALF + quarter * 32 + lane;
+            __nv_bfloat16* c_row = C + n * static_cast<size_t>(M) + static_cast<size_t>(tm) * P_::BLOCK;
+            const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                                   static_cast<uint32_t>(acc * P_::BLOCK);
+#pragma unroll 2
+            for (int c = 0; c < P_::BLOCK; c += 32) {
+                uint32_t r[32];
+                tmem_ld_32cols(t_row + c, r);
+                tmem_ld_wait();
+                uint4* dst = reinterpret_cast<uint4*>(c_row + c);
+#pragma unroll
+                for (int v = 0; v < 4; ++v) {
+                    uint4 o;
+                    o.x = pack_bf16(r[8 * v + 0], r[8 * v + 1]);
+                    o.y = pack_bf16(r[8 * v + 2], r[8 * v + 3]);
+                    o.z = pack_bf16(r[8 * v + 4], r[8 * v + 5]);
+                    o.w = pack_bf16(r[8 * v + 6], r[8 * v + 7]);
+                    dst[v] = o;
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(cluster_addr(&acc_empty_bar[acc], 0));  // the leader's barrier
+            if (++acc == 2) {
+                acc = 0;
+                acc_phase ^= 1u;
+            }
+        }
+    }
+
+    if (timed_out) {
+        *abort_flag = 1;
+        raise_device_status(DEV_GEMM_PIPE_TIMEOUT);
+    }
+    __syncwarp();
+    tc_fence_before();
+    cluster_sync_all();   // nobody leaves while the other CTA may still read its operands or signal its barriers
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                     "r"(static_cast<uint32_t>(TMEM_COLS))
+                     : "memory");
+    }
+}
+
 namespace {
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -416,6 +678,54 @@ int launch_gemm(int dev, int sms, int M, int N, int K, const void* A, const void
     return PRISM_B200_OK;
 }
 
+int launch_gemm_pair(int dev, int M, int N, int K, const void* A, const void* B, void* C, cudaStream_t s) {
+    using P_ = g16::PairCfg;
+    CUtensorMap map_a, map_b;
+    if (int rc = get_tensor_map(dev, A, M, K, P_::HALF, &map_a)) return rc;
+    if (int rc = get_tensor_map(dev, B, N, K, P_::HALF, &map_b)) return rc;
+    static int group = 0;  // TUNING: PRISM_B200_GEMM_GROUP = m-tiles walked per n-tile (4, 8, 16, 32)
+    if (group == 0) {
+        const char* e = getenv("PRISM_B200_GEMM_GROUP");
+        group = e ? atoi(e) : 8;
+        if (group != 4 && group != 16 && group != 32) group = 8;
+    }
+    auto kern = group == 4 ? cutlass_my_h100_match_no_tail_pair<4>
+              : group == 16 ? cutlass_my_h100_match_no_tail_pair<16>
+              : group == 32 ? cutlass_my_h100_match_no_tail_pair<32>
+                            : cutlass_my_h100_match_no_tail_pair<8>;
+    static int max_pairs[64] = {};
+    int pairs_cap = (dev >= 0 && dev < 64) ? max_pairs[dev] : 0;
+    cudaLaunchConfig_t cfg = {};
+    cfg.blockDim = dim3(g16::THREADS);
+    cfg.dynamicSmemBytes = P_::SMEM_BYTES;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (pairs_cap == 0) {
+        PRISM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            static_cast<int>(P_::SMEM_BYTES)));
+        int sms = 0;
+        PRISM_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+        cfg.gridDim = dim3(static_cast<unsigned>(sms / 2 * 2));
+        int clusters = 0;
+        PRISM_CUDA_TRY(cudaOccupancyMaxActiveClusters(&clusters, kern, &cfg));
+        if (clusters < 1) return set_error(PRISM_B200_ERR_CUDA, "gemm_bf16: no 2-CTA cluster fits on this device");
+        pairs_cap = clusters;
+        if (dev >= 0 && dev < 64) max_pairs[dev] = clusters;
+    }
+    const int tiles = (M / P_::BLOCK) * (N / P_::BLOCK);
+    const int pairs = tiles < pairs_cap ? tiles : pairs_cap;
+    cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs));
+    PRISM_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, M, N, K, static_cast<__nv_bfloat16*>(C), map_a, map_b));
+    count_launch();
+    return PRISM_B200_OK;
+}
+
 }  // namespace
 }  // namespace prism_b200
 
@@ -441,6 +751,14 @@ extern "C" int prism_b200_gemm_bf16(int M, int N, int K, const uint16_t* A, cons
         if (dev >= 0 && dev < 64) sm_count[dev] = sms;
     }
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    {
+        static int use_pair = -1;  // TUNING: PRISM_B200_GEMM_PAIR=1 selects the two-CTA kernel where the shape allows
+        if (use_pair < 0) {
+            const char* e = getenv("PRISM_B200_GEMM_PAIR");
+            use_pair = (e && e[0] == '1') ? 1 : 0;
+        }
+        if (use_pair && M % 256 == 0 && N % 256 == 0) return launch_gemm_pair(dev, M, N, K, A, B, C, s);
+    }
     // 256-wide m-tiles halve the operand traffic per flop; fall back to 128 when M
     // does not divide or when the wider tile would leave a poorly filled last wave.
     bool wide = (M % 256 == 0);

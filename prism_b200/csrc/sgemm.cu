@@ -218,7 +218,7 @@ my_sgemm_kernel_4(int M, int N, int K, float alpha, float* A, float* B, float be
 // Kernel 5: the throughput kernel (generated/my_sgemm_kernel_5.cu:1-84 with
 // loadFromGmem_our / processFromSmem_our, evals/4090_sgemm/my_kernel_utils.cuh:13-89).
 //
-// CTA tile 128 x 128, k-slice 32, STAGES-deep ring in shared memory.
+// CTA tile 128 x 128, k-slice 32, three-stage ring in shared memory, 128 threads.
 //   Staging: a k-slice is 128 row copies of A (128 B each) and 32 row copies of B
 //     (512 B each) issued with cp.async.bulk, a quarter by each warp (one or two
 //     copies per lane); they complete on the stage's "full" mbarrier.  A rows land
@@ -229,21 +229,26 @@ my_sgemm_kernel_4(int M, int N, int K, float alpha, float* A, float* B, float be
 //     rows  wm0 + (lane & 7) + 8 i  (i = 0..7) and columns  wn0 + 16 j + 4 (lane >> 3) .. +3
 //     (j = 0..3): 8 x 16 = 128 accumulators.  Per 4 k it reads 8 x 16 B of A (one per
 //     row, 4 consecutive k) and 4 x 4 x 16 B of B, all conflict-free, for 512 FMAs.
-//     With PACKED the FMAs are issued as fma.rn.f32x2 on column pairs, which halves
-//     the FMA issue slots and leaves room for the shared-memory reads.
+//     With PACKED the FMAs are issued as fma.rn.f32x2 on column pairs (two
+//     independent fp32 FMAs per instruction: the same bits as the scalar form,
+//     37 -> 49 TFLOP/s at 4096^3).
 //   A "full"/"empty" mbarrier pair per stage hands slices back and forth; every
 //   wait is bounded.
+//   Measured and rejected: an 8-warp 8 x 8-per-lane form, 16-wide k-slices, a stage
+//     refilled two slices late, splitting the last wave's tiles into column halves (a lone
+//     CTA on an SM already runs nearly twice as fast), and dropping the duplicating moves
+//     (no faster): every form settles near 0.65 FMA per lane per clock.
 // Needs M % 128 == 0, N % 128 == 0, K % 32 == 0 and 16-byte aligned A, B, C.
 // ============================================================================
 namespace k5 {
 constexpr int BM = 128, BN = 128, BK = 32;
-constexpr int A_STRIDE = BK + 4;                       // floats
-constexpr int A_STAGE = BM * A_STRIDE;                 // floats
-constexpr int B_STAGE = BK * BN;                       // floats
-constexpr uint32_t STAGE_TX_BYTES = (BM * BK + BK * BN) * sizeof(float);
-constexpr size_t smem_bytes(int stages) {
-    return static_cast<size_t>(stages) * (A_STAGE + B_STAGE) * sizeof(float) + 2 * stages * 8 + 16;
-}
+constexpr int STAGES = 3;
+constexpr int WARPS = 4;
+constexpr int THREADS = WARPS * 32;
+constexpr int A_STRIDE = BK + 4;        // floats
+constexpr int A_STAGE = BM * A_STRIDE;  // floats
+constexpr int B_STAGE = BK * BN;        // floats
+constexpr size_t SMEM_BYTES = static_cast<size_t>(STAGES) * (A_STAGE + B_STAGE) * sizeof(float) + 2 * STAGES * 8 + 16;
 }  // namespace k5
 
 __device__ __forceinline__ void bulk_copy_g2s(void* dst_smem, const void* src, uint32_t bytes, uint64_t* bar) {
@@ -265,21 +270,13 @@ __device__ __forceinline__ void fma2(unsigned long long& acc, unsigned long long
     asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc) : "l"(a), "l"(b));
 }
 
-// PACKED : fma.rn.f32x2 on column pairs (else scalar fmaf)
-// WARPS  : 4 (8 x 16 outputs per lane, NV = 4) or 8 (8 x 8 outputs per lane, NV = 2)
-// STAGES : depth of the shared-memory ring
-// MINB   : CTAs per SM asked of the compiler
-template <bool PACKED, int WARPS, int STAGES, int MINB>
-__global__ void __launch_bounds__(WARPS * 32, MINB)
-my_sgemm_kernel_5(int M, int N, int K, float alpha, float* A, float* B, float beta, float* C, int num_blocks_N) {
+// One 128 x 128 tile of C at (row0, col0); NV = 16-byte B vectors per lane per k.
+template <bool PACKED, int NV>
+__device__ __forceinline__ void k5_tile(int N, int K, float alpha, const float* A, const float* B, float beta, float* C,
+                                        int row0, int col0, unsigned char* smem_raw) {
     using namespace k5;
-    static_assert(WARPS == 4 || WARPS == 8, "2 x 2 or 2 x 4 warp tiles");
-    constexpr int NV = WARPS == 4 ? 4 : 2;            // 16-byte B vectors per lane per k
-    constexpr int WN = 16 * NV;                       // warp tile columns
-    constexpr int WARPS_N = BN / WN;
-    constexpr int B_WARP = WARPS == 4 ? 0 : 4;        // the warp that copies the B rows
-    constexpr int COPY_WARPS = WARPS == 4 ? 4 : 5;
-    extern __shared__ __align__(128) unsigned char smem_raw[];
+    constexpr int TILE_N = 32 * NV;   // columns of this tile
+    constexpr int WN = 16 * NV;       // warp tile columns
     float* As = reinterpret_cast<float*>(smem_raw);
     float* Bs = As + STAGES * A_STAGE;
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(Bs + STAGES * B_STAGE);
@@ -288,13 +285,11 @@ my_sgemm_kernel_5(int M, int N, int K, float alpha, float* A, float* B, float be
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int row0 = (blockIdx.x / num_blocks_N) * BM;
-    const int col0 = (blockIdx.x % num_blocks_N) * BN;
     const int k_slices = K / BK;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
-            mbar_init(&full_bar[s], COPY_WARPS);
+            mbar_init(&full_bar[s], WARPS);
             mbar_init(&empty_bar[s], WARPS);
         }
         *abort_flag = 0;
@@ -302,31 +297,26 @@ my_sgemm_kernel_5(int M, int N, int K, float alpha, float* A, float* B, float be
     }
     __syncthreads();
 
-    // Warps 0-3 copy 32 rows of A each (lane = row); warp B_WARP also copies the 32 rows
-    // of B.  A copying warp announces its bytes on the stage's "full" barrier first.
-    const bool copies_a = warp < 4;
-    const bool copies_b = warp == B_WARP;
-    const float* a_src = A + static_cast<size_t>(row0 + (warp & 3) * 32 + lane) * K;
-    const float* b_src = B + static_cast<size_t>(lane) * N + col0;
+    // Each warp copies its quarter of a k-slice: 32 rows of A (lane = row) and 8 rows
+    // of B (lanes 0-7), and announces those bytes on the stage's "full" barrier first.
+    const float* a_src = A + static_cast<size_t>(row0 + warp * 32 + lane) * K;
+    const float* b_src = B + static_cast<size_t>(warp * 8 + (lane & 7)) * N + col0;
     auto issue_slice = [&](int t) {
         const int s = t % STAGES;
-        if (lane == 0)
-            mbar_arrive_expect_tx(&full_bar[s], (copies_a ? 32u * BK * 4u : 0u) + (copies_b ? 32u * BN * 4u : 0u));
+        if (lane == 0) mbar_arrive_expect_tx(&full_bar[s], 32u * BK * 4u + 8u * TILE_N * 4u);
         __syncwarp();
-        if (copies_a)
-            bulk_copy_g2s(As + s * A_STAGE + (warp * 32 + lane) * A_STRIDE, a_src + t * BK, BK * sizeof(float),
-                          &full_bar[s]);
-        if (copies_b)
-            bulk_copy_g2s(Bs + s * B_STAGE + lane * BN, b_src + static_cast<size_t>(t) * BK * N, BN * sizeof(float),
-                          &full_bar[s]);
+        bulk_copy_g2s(As + s * A_STAGE + (warp * 32 + lane) * A_STRIDE, a_src + t * BK, BK * sizeof(float),
+                      &full_bar[s]);
+        if (lane < 8)
+            bulk_copy_g2s(Bs + s * B_STAGE + (warp * 8 + lane) * TILE_N, b_src + static_cast<size_t>(t) * BK * N,
+                          TILE_N * sizeof(float), &full_bar[s]);
     };
-    if (copies_a || copies_b)
-        for (int t = 0; t < STAGES - 1 && t < k_slices; ++t) issue_slice(t);
+    for (int t = 0; t < STAGES - 1 && t < k_slices; ++t) issue_slice(t);
 
     const int tm = lane & 7;
     const int tn = lane >> 3;
-    const int wm0 = (warp / WARPS_N) * 64;
-    const int wn0 = (warp % WARPS_N) * WN;
+    const int wm0 = (warp >> 1) * 64;
+    const int wn0 = (warp & 1) * WN;
 
     unsigned long long acc2[PACKED ? 8 : 1][PACKED ? 2 * NV : 1];
     float acc[PACKED ? 1 : 8][PACKED ? 1 : 4 * NV];
@@ -346,10 +336,10 @@ my_sgemm_kernel_5(int M, int N, int K, float alpha, float* A, float* B, float be
     for (int t = 0; t < k_slices; ++t) {
         const int s = t % STAGES;
         const uint32_t round = static_cast<uint32_t>(t / STAGES);
-        // Refill the stage that slice t-1 used with slice t+STAGES-1, once every warp
-        // has released it.
+        // Refill the stage that slice t-1 used with slice t+STAGES-1, once all four
+        // warps have released it.
         const int refill = t + STAGES - 1;
-        if ((copies_a || copies_b) && refill < k_slices) {
+        if (refill < k_slices) {
             if (t >= 1 && !mbar_wait_bounded(&empty_bar[(t - 1) % STAGES], static_cast<uint32_t>((t - 1) / STAGES) & 1u,
                                              abort_flag)) {
                 ok = false;
@@ -374,7 +364,7 @@ my_sgemm_kernel_5(int M, int N, int K, float alpha, float* A, float* B, float be
                     ulonglong2 b[NV];
 #pragma unroll
                     for (int j = 0; j < NV; ++j)
-                        b[j] = *reinterpret_cast<const ulonglong2*>(b_base + (kk + k4) * BN + j * 16);
+                        b[j] = *reinterpret_cast<const ulonglong2*>(b_base + (kk + k4) * TILE_N + j * 16);
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
                         const float av = k4 == 0 ? a[i].x : k4 == 1 ? a[i].y : k4 == 2 ? a[i].z : a[i].w;
@@ -388,7 +378,8 @@ my_sgemm_kernel_5(int M, int N, int K, float alpha, float* A, float* B, float be
                 } else {
                     float4 b[NV];
 #pragma unroll
-                    for (int j = 0; j < NV; ++j) b[j] = *reinterpret_cast<const float4*>(b_base + (kk + k4) * BN + j * 16);
+                    for (int j = 0; j < NV; ++j)
+                        b[j] = *reinterpret_cast<const float4*>(b_base + (kk + k4) * TILE_N + j * 16);
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
                         const float av = k4 == 0 ? a[i].x : k4 == 1 ? a[i].y : k4 == 2 ? a[i].z : a[i].w;
@@ -438,6 +429,15 @@ my_sgemm_kernel_5(int M, int N, int K, float alpha, float* A, float* B, float be
     }
 }
 
+template <bool PACKED>
+__global__ void __launch_bounds__(k5::THREADS, 2)
+my_sgemm_kernel_5(int M, int N, int K, float alpha, float* A, float* B, float beta, float* C, int num_blocks_N) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    const int bid = static_cast<int>(blockIdx.x);
+    k5_tile<PACKED, 4>(N, K, alpha, A, B, beta, C, (bid / num_blocks_N) * k5::BM, (bid % num_blocks_N) * k5::BN,
+                       smem_raw);
+}
+
 namespace {
 
 inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
@@ -456,7 +456,7 @@ int launch_generic(int M, int N, int K, float alpha, const float* A, const float
     return PRISM_B200_OK;
 }
 
-int g_k5_variant = 0;  // fma.rn.f32x2 form of kernel 5; PRISM_B200_SGEMM_SCALAR=1 selects the plain fmaf form
+bool g_k5_scalar = false;  // PRISM_B200_SGEMM_SCALAR=1 selects the plain fmaf form of kernel 5 (same bits, slower)
 bool g_k5_env_read = false;
 
 }  // namespace
@@ -513,36 +513,23 @@ extern "C" int prism_b200_sgemm(int kernel_id, int M, int N, int K, float alpha,
     }
     case 5: {
         if (M % k5::BM == 0 && N % k5::BN == 0 && K % k5::BK == 0 && K > 0 && vec_ok) {
-            using Kern = void (*)(int, int, int, float, float*, float*, float, float*, int);
-            struct Var { Kern k; int threads; int stages; };
-            // 0: packed, 4 warps, 8x16 per lane, 3 stages, 2 CTAs/SM (default)   1: scalar fmaf form of 0
-            // TUNING ONLY (PRISM_B200_SGEMM_VARIANT): 2: 8 warps 8x8 per lane   3: 4 warps, 2 stages, 3 CTAs/SM
-            static const Var vars[] = {
-                {my_sgemm_kernel_5<true, 4, 3, 2>, 128, 3},  {my_sgemm_kernel_5<false, 4, 3, 2>, 128, 3},
-                {my_sgemm_kernel_5<true, 8, 3, 2>, 256, 3},  {my_sgemm_kernel_5<true, 4, 2, 3>, 128, 2},
-                {my_sgemm_kernel_5<true, 8, 2, 3>, 256, 2},  {my_sgemm_kernel_5<true, 8, 4, 1>, 256, 4},
-            };
             if (!g_k5_env_read) {
                 const char* e = getenv("PRISM_B200_SGEMM_SCALAR");
-                g_k5_variant = (e && e[0] == '1') ? 1 : 0;
-                const char* v = getenv("PRISM_B200_SGEMM_VARIANT");
-                if (v && atoi(v) >= 0 && atoi(v) < static_cast<int>(sizeof(vars) / sizeof(vars[0]))) g_k5_variant = atoi(v);
+                g_k5_scalar = e && e[0] == '1';
                 g_k5_env_read = true;
             }
-            const Var& var = vars[g_k5_variant];
-            const int nbn = N / k5::BN;
-            const unsigned blocks = static_cast<unsigned>((M / k5::BM) * nbn);
-            static bool attr_set[8][64] = {};
+            auto kern = g_k5_scalar ? my_sgemm_kernel_5<false> : my_sgemm_kernel_5<true>;
+            static bool attr_set[2][64] = {};
             int dev = 0;
             PRISM_CUDA_TRY(cudaGetDevice(&dev));
-            const size_t smem = k5::smem_bytes(var.stages);
-            if (dev < 0 || dev >= 64 || !attr_set[g_k5_variant][dev]) {
-                PRISM_CUDA_TRY(cudaFuncSetAttribute(var.k, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                    static_cast<int>(smem)));
-                if (dev >= 0 && dev < 64) attr_set[g_k5_variant][dev] = true;
+            if (dev < 0 || dev >= 64 || !attr_set[g_k5_scalar][dev]) {
+                PRISM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                    static_cast<int>(k5::SMEM_BYTES)));
+                if (dev >= 0 && dev < 64) attr_set[g_k5_scalar][dev] = true;
             }
-            var.k<<<blocks, var.threads, smem, s>>>(M, N, K, alpha, const_cast<float*>(A), const_cast<float*>(B), beta,
-                                                    C, nbn);
+            const int nbn = N / k5::BN;
+            kern<<<static_cast<unsigned>((M / k5::BM) * nbn), k5::THREADS, k5::SMEM_BYTES, s>>>(
+                M, N, K, alpha, const_cast<float*>(A), const_cast<float*>(B), beta, C, nbn);
         } else {
             rc = launch_generic(M, N, K, alpha, A, B, beta, C, s);
         }

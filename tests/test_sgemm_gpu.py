@@ -54,6 +54,15 @@ def test_kernel5_tile_edges(pb, shape):
     assert O.sgemm_rel_error(out, O.sgemm_cpu(-0.75, A, B, 2.0, C)) <= O.SGEMM_TOL
 
 
+def test_kernel5_more_tiles_than_resident_ctas(pb):
+    """18 x 18 = 324 tiles on 296 resident CTAs: a second, partly filled wave."""
+    M = N = 2304
+    K = 96
+    A, B, C = O.sgemm_inputs(M, N, K, seed=2304)
+    out = _run(pb, 5, 1.5, A, B, 0.5, C)
+    assert O.sgemm_rel_error(out, O.sgemm_cpu(1.5, A, B, 0.5, C)) <= O.SGEMM_TOL
+
+
 def test_kernel5_scalar_and_packed_fma_agree(pb, monkeypatch):
     """fma.rn.f32x2 is two independent fp32 FMAs: both forms of kernel 5 must agree bit for bit.
     (The scalar form is selected by an environment variable read at first use, so it is run in a child.)"""
@@ -98,7 +107,7 @@ def test_linearity_at_4096(pb):
     pb.run_my_kernel(5, S, S, S, 2.0, a, b, 0.0, c2)
     torch.cuda.synchronize()
     assert torch.equal(c2, 2.0 * c1)
-    rows = [0, 1, 127, 128, 2047, 4095]
+    rows = [0, 1, 127, 128, 2047, 3583, 3584, 3999, 4095]
     ref = A[rows].astype(np.float64) @ B.astype(np.float64)
     got = c1[rows].cpu().numpy()
     assert O.sgemm_rel_error(got, ref) <= O.SGEMM_TOL

@@ -119,6 +119,23 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
     }
 }
 
+// The same wait for a role that can afford to react late: sleeps between probes, so that a warp
+// that waits for tens of microseconds does not spend issue slots and power on polling.
+__device__ __forceinline__ bool mbar_wait_bounded_sleepy(uint64_t* bar, uint32_t parity,
+                                                         volatile uint32_t* abort_flag, unsigned sleep_ns,
+                                                         unsigned long long limit_ns = kWaitLimitNs) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_timer_ns();
+    for (uint32_t i = 1;; ++i) {
+        __nanosleep(sleep_ns);
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 15u) == 0u) {
+            if (*abort_flag) return false;
+            if (global_timer_ns() - t0 > limit_ns) return false;
+        }
+    }
+}
+
 __device__ __forceinline__ void fence_barrier_init() {
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }

@@ -206,7 +206,7 @@ cutlass_my_h100_match_no_tail(int M, int N, int K, __nv_bfloat16* C, const __gri
                 int tm, tn;
                 tile_coords(t, tiles_m, tiles_n, tm, tn);
                 for (int kb = 0; kb < k_blocks; ++kb) {
-                    if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag)) {
+                    if (!mbar_wait_bounded_sleepy(&empty_bar[stage], phase ^ 1u, abort_flag, 40)) {
                         timed_out = true;
                         break;
                     }
@@ -286,7 +286,9 @@ cutlass_my_h100_match_no_tail(int M, int N, int K, __nv_bfloat16* C, const __gri
             int tm, tn;
             tile_coords(t, tiles_m, tiles_n, tm, tn);
             // Warp-uniform outcome: the TMEM loads below need the whole warp converged.
-            const bool ready = mbar_wait_bounded(&acc_full_bar[acc], acc_phase, abort_flag);
+            // One lane polls, with sleeps in between (the wait lasts most of a tile's main loop);
+            // the other 31 lanes block at the vote.
+            const bool ready = lane != 0 || mbar_wait_bounded_sleepy(&acc_full_bar[acc], acc_phase, abort_flag, 200);
             if (!__all_sync(0xffffffffu, ready)) {
                 timed_out = true;
                 break;
@@ -479,7 +481,7 @@ cutlass_my_h100_match_no_tail_pair(int M, int N, int K, __nv_bfloat16* C, const 
                 const int n_row = tn * P_::BLOCK + static_cast<int>(rank) * P_::HALF;
                 const int m_row = tm * P_::BLOCK + static_cast<int>(rank) * P_::HALF;
                 for (int kb = 0; kb < k_blocks; ++kb) {
-                    if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag)) {
+                    if (!mbar_wait_bounded_sleepy(&empty_bar[stage], phase ^ 1u, abort_flag, 40)) {
                         timed_out = true;
                         break;
                     }
@@ -546,7 +548,9 @@ cutlass_my_h100_match_no_tail_pair(int M, int N, int K, __nv_bfloat16* C, const 
         for (int t = pair; t < total_tiles; t += pairs) {
             int tm, tn;
             tile_coords(t, tiles_m, tiles_n, tm, tn, GROUP);
-            const bool ready = mbar_wait_bounded(&acc_full_bar[acc], acc_phase, abort_flag);
+            // One lane polls, with sleeps in between (the wait lasts most of a tile's main loop);
+            // the other 31 lanes block at the vote.
+            const bool ready = lane != 0 || mbar_wait_bounded_sleepy(&acc_full_bar[acc], acc_phase, abort_flag, 200);
             if (!__all_sync(0xffffffffu, ready)) {
                 timed_out = true;
                 break;
@@ -589,6 +593,234 @@ cutlass_my_h100_match_no_tail_pair(int M, int N, int K, __nv_bfloat16* C, const 
     __syncwarp();
     tc_fence_before();
     cluster_sync_all();   // nobody leaves while the other CTA may still read its operands or signal its barriers
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                     "r"(static_cast<uint32_t>(TMEM_COLS))
+                     : "memory");
+    }
+}
+
+// ============================================================================
+// Two-CTA, two-row-block form: each CTA of the pair owns TWO 128-row n blocks, so the
+// pair computes 512 (n) x 256 (m) per tile and each m-side operand byte staged in
+// shared memory feeds two MMAs instead of one (48 KB per stage for 2 x 128 x 256 x 64
+// MACs per CTA, against 32 KB for half of that in the form above).  Shared-memory and
+// L2 traffic per flop drop by a quarter, which is what lets the tensor pipe stay busy.
+// The two accumulators take all 512 tensor-memory columns, so they cannot be
+// double-buffered: the epilogue of a tile is not hidden behind the next main loop.  It
+// is kept short instead -- eight epilogue warps, two per lane quarter, one accumulator
+// each -- and the producer already prefetches the next tile's stages while it runs.
+// Barriers and pairing are as in the kernel above.
+// ============================================================================
+// TUNING ONLY (set from PRISM_B200_GEMM_SLEEP / PRISM_B200_GEMM_ORDER): producer sleep between polls in ns
+// (0 = plain polling) and MMA issue order (0 = accumulators interleaved, 1 = one after the other).
+__device__ int g_tune_sleep_ns = 40;
+__device__ int g_tune_order = 0;
+
+namespace g16 {
+struct WideCfg {
+    static constexpr int TILE_N = 512;     // n rows per pair tile (2 CTAs x 2 blocks x 128)
+    static constexpr int TILE_M = 256;     // m rows per pair tile
+    static constexpr int HALF = 128;
+    static constexpr int STAGES = 4;
+    static constexpr int EPI_WARPS = 8;
+    static constexpr int THREADS = 64 + 32 * EPI_WARPS;
+    static constexpr uint32_t BLOCK_BYTES = HALF * BLOCK_K * 2;   // one 128-row operand block
+    static constexpr uint32_t STAGE_BYTES = 3 * BLOCK_BYTES;      // P0, P1, Q half
+    static constexpr size_t SMEM_BYTES = 1024 + static_cast<size_t>(STAGES) * STAGE_BYTES + (2 * STAGES + 2) * 8 + 16;
+};
+}  // namespace g16
+
+template <int GROUP>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(g16::WideCfg::THREADS, 1)
+cutlass_my_h100_match_no_tail_pair_wide(int M, int N, int K, __nv_bfloat16* C,
+                                        const __grid_constant__ CUtensorMap tensorMapA,
+                                        const __grid_constant__ CUtensorMap tensorMapB) {
+    using namespace g16;
+    using W_ = WideCfg;
+    constexpr int STAGES = W_::STAGES;
+    constexpr uint32_t IDESC = instr_desc(256, W_::TILE_M);  // 256 n rows across the pair per MMA, 256 m columns
+
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    unsigned char* ring = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(ring + STAGES * W_::STAGE_BYTES);
+    uint64_t* empty_bar = full_bar + STAGES;
+    uint64_t* acc_full_bar = empty_bar + STAGES;   // [1]
+    uint64_t* acc_empty_bar = acc_full_bar + 1;    // [1], only the leader's is used
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty_bar + 1);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_cta_rank();
+    const bool leader = rank == 0;
+    const int pair = blockIdx.x >> 1;
+    const int pairs = gridDim.x >> 1;
+    const int tiles_m = M / W_::TILE_M;
+    const int tiles_n = N / W_::TILE_N;
+    const int total_tiles = tiles_m * tiles_n;
+    const int k_blocks = K / BLOCK_K;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        mbar_init(acc_full_bar, 1);
+        mbar_init(acc_empty_bar, 2 * W_::EPI_WARPS);
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        __syncwarp();
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"(static_cast<uint32_t>(TMEM_COLS))
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    cluster_sync_all();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    bool timed_out = false;
+
+    if (warp == 0) {
+        // ------------------------- TMA producer (both CTAs) -------------------------
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tensorMapA)) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tensorMapB)) : "memory");
+            int stage = 0;
+            uint32_t phase = 0;
+            for (int t = pair; t < total_tiles && !timed_out; t += pairs) {
+                int tm, tn;
+                tile_coords(t, tiles_m, tiles_n, tm, tn, GROUP);
+                // This CTA's two n blocks and its half of the m rows.
+                const int n_row0 = tn * W_::TILE_N + static_cast<int>(rank) * 256;
+                const int m_row = tm * W_::TILE_M + static_cast<int>(rank) * W_::HALF;
+                const int sleep_ns = g_tune_sleep_ns;
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    const bool got = sleep_ns ? mbar_wait_bounded_sleepy(&empty_bar[stage], phase ^ 1u, abort_flag, sleep_ns)
+                                              : mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag);
+                    if (!got) {
+                        timed_out = true;
+                        break;
+                    }
+                    unsigned char* dst = ring + stage * W_::STAGE_BYTES;
+                    const uint32_t leader_full = cluster_addr(&full_bar[stage], 0);
+                    if (leader) mbar_arrive_expect_tx(&full_bar[stage], 2 * W_::STAGE_BYTES);
+                    tma_load_2d_pair(dst, &tensorMapB, kb * BLOCK_K, n_row0, leader_full);
+                    tma_load_2d_pair(dst + W_::BLOCK_BYTES, &tensorMapB, kb * BLOCK_K, n_row0 + W_::HALF, leader_full);
+                    tma_load_2d_pair(dst + 2 * W_::BLOCK_BYTES, &tensorMapA, kb * BLOCK_K, m_row, leader_full);
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------- MMA issuer (leader only) -------------------------
+        if (leader && lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            uint32_t tile_phase = 0;
+            for (int t = pair; t < total_tiles && !timed_out; t += pairs) {
+                if (!mbar_wait_bounded(acc_empty_bar, tile_phase ^ 1u, abort_flag)) {   // both CTAs drained both accumulators
+                    timed_out = true;
+                    break;
+                }
+                tc_fence_after();
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag)) {
+                        timed_out = true;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t base = smem_u32(ring + stage * W_::STAGE_BYTES);
+                    const uint64_t p0_desc = smem_desc_k_sw128(base);
+                    const uint64_t p1_desc = smem_desc_k_sw128(base + W_::BLOCK_BYTES);
+                    const uint64_t q_desc = smem_desc_k_sw128(base + 2 * W_::BLOCK_BYTES);
+                    if (g_tune_order == 0) {
+#pragma unroll
+                        for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
+                            const uint32_t accumulate = (kb | k) != 0 ? 1u : 0u;
+                            umma_bf16_pair(tmem_base, p0_desc + 2u * k, q_desc + 2u * k, IDESC, accumulate);
+                            umma_bf16_pair(tmem_base + 256u, p1_desc + 2u * k, q_desc + 2u * k, IDESC, accumulate);
+                        }
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < BLOCK_K / UMMA_K; ++k)
+                            umma_bf16_pair(tmem_base, p0_desc + 2u * k, q_desc + 2u * k, IDESC, (kb | k) != 0 ? 1u : 0u);
+#pragma unroll
+                        for (int k = 0; k < BLOCK_K / UMMA_K; ++k)
+                            umma_bf16_pair(tmem_base + 256u, p1_desc + 2u * k, q_desc + 2u * k, IDESC, (kb | k) != 0 ? 1u : 0u);
+                    }
+                    umma_commit_pair(cluster_addr(&empty_bar[stage], 0));
+                    umma_commit_pair(cluster_addr(&empty_bar[stage], 1));
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (timed_out) break;
+                umma_commit_pair(cluster_addr(acc_full_bar, 0));
+                umma_commit_pair(cluster_addr(acc_full_bar, 1));
+                tile_phase ^= 1u;
+            }
+        }
+    } else {
+        // ------------------------- epilogue warps (both CTAs) -------------------------
+        // Warps 2-9: warp index mod 4 picks the 32-lane quarter of tensor memory it can reach;
+        // the two warps of a quarter take one accumulator (n block) each.
+        const int quarter = warp & 3;
+        const int block = (warp - 2) >> 2;
+        uint32_t tile_phase = 0;
+        for (int t = pair; t < total_tiles; t += pairs) {
+            int tm, tn;
+            tile_coords(t, tiles_m, tiles_n, tm, tn, GROUP);
+            const bool ready = lane != 0 || mbar_wait_bounded_sleepy(acc_full_bar, tile_phase, abort_flag, 200);
+            if (!__all_sync(0xffffffffu, ready)) {
+                timed_out = true;
+                break;
+            }
+            tc_fence_after();
+            const size_t n = static_cast<size_t>(tn) * W_::TILE_N + rank * 256 + block * W_::HALF + quarter * 32 + lane;
+            __nv_bfloat16* c_row = C + n * static_cast<size_t>(M) + static_cast<size_t>(tm) * W_::TILE_M;
+            const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(block * 256);
+#pragma unroll 2
+            for (int c = 0; c < W_::TILE_M; c += 32) {
+                uint32_t r[32];
+                tmem_ld_32cols(t_row + c, r);
+                tmem_ld_wait();
+                uint4* dst = reinterpret_cast<uint4*>(c_row + c);
+#pragma unroll
+                for (int v = 0; v < 4; ++v) {
+                    uint4 o;
+                    o.x = pack_bf16(r[8 * v + 0], r[8 * v + 1]);
+                    o.y = pack_bf16(r[8 * v + 2], r[8 * v + 3]);
+                    o.z = pack_bf16(r[8 * v + 4], r[8 * v + 5]);
+                    o.w = pack_bf16(r[8 * v + 6], r[8 * v + 7]);
+                    dst[v] = o;
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(cluster_addr(acc_empty_bar, 0));
+            tile_phase ^= 1u;
+        }
+    }
+
+    if (timed_out) {
+        *abort_flag = 1;
+        raise_device_status(DEV_GEMM_PIPE_TIMEOUT);
+    }
+    __syncwarp();
+    tc_fence_before();
+    cluster_sync_all();
     if (warp == 1) {
         __syncwarp();
         tc_fence_after();
@@ -647,9 +879,15 @@ int get_tensor_map(int dev, const void* ptr, int rows, int k, int box_rows, CUte
     const cuuint64_t strides[1] = {static_cast<cuuint64_t>(k) * 2};
     const cuuint32_t box[2] = {static_cast<cuuint32_t>(g16::BLOCK_K), static_cast<cuuint32_t>(box_rows)};
     const cuuint32_t estr[2] = {1, 1};
+    static int promo = -1;  // TUNING: PRISM_B200_GEMM_L2PROMO = 0 none, 1 64B, 2 128B, 3 256B
+    if (promo < 0) {
+        const char* e = getenv("PRISM_B200_GEMM_L2PROMO");
+        promo = e ? atoi(e) : 3;
+        if (promo < 0 || promo > 3) promo = 3;
+    }
     CUresult r = g_encode(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                          static_cast<CUtensorMapL2promotion>(promo), CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return set_error(PRISM_B200_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d", (int)r);
     if (g_maps.size() > 4096) g_maps.clear();
     g_maps.emplace(key, m);
@@ -678,26 +916,14 @@ int launch_gemm(int dev, int sms, int M, int N, int K, const void* A, const void
     return PRISM_B200_OK;
 }
 
-int launch_gemm_pair(int dev, int M, int N, int K, const void* A, const void* B, void* C, cudaStream_t s) {
-    using P_ = g16::PairCfg;
-    CUtensorMap map_a, map_b;
-    if (int rc = get_tensor_map(dev, A, M, K, P_::HALF, &map_a)) return rc;
-    if (int rc = get_tensor_map(dev, B, N, K, P_::HALF, &map_b)) return rc;
-    static int group = 0;  // TUNING: PRISM_B200_GEMM_GROUP = m-tiles walked per n-tile (4, 8, 16, 32)
-    if (group == 0) {
-        const char* e = getenv("PRISM_B200_GEMM_GROUP");
-        group = e ? atoi(e) : 8;
-        if (group != 4 && group != 16 && group != 32) group = 8;
-    }
-    auto kern = group == 4 ? cutlass_my_h100_match_no_tail_pair<4>
-              : group == 16 ? cutlass_my_h100_match_no_tail_pair<16>
-              : group == 32 ? cutlass_my_h100_match_no_tail_pair<32>
-                            : cutlass_my_h100_match_no_tail_pair<8>;
-    static int max_pairs[64] = {};
-    int pairs_cap = (dev >= 0 && dev < 64) ? max_pairs[dev] : 0;
+using PairKernel = void (*)(int, int, int, __nv_bfloat16*, const CUtensorMap, const CUtensorMap);
+
+// Launches one of the two-CTA kernels: persistent, as many pairs as the device holds at once.
+int launch_pair_kernel(PairKernel kern, int* pairs_cache, int threads, size_t smem, int tiles, int dev, int M, int N,
+                       int K, const CUtensorMap& map_a, const CUtensorMap& map_b, void* C, cudaStream_t s) {
     cudaLaunchConfig_t cfg = {};
-    cfg.blockDim = dim3(g16::THREADS);
-    cfg.dynamicSmemBytes = P_::SMEM_BYTES;
+    cfg.blockDim = dim3(static_cast<unsigned>(threads));
+    cfg.dynamicSmemBytes = smem;
     cfg.stream = s;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -706,9 +932,9 @@ int launch_gemm_pair(int dev, int M, int N, int K, const void* A, const void* B,
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
+    int pairs_cap = *pairs_cache;
     if (pairs_cap == 0) {
-        PRISM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                            static_cast<int>(P_::SMEM_BYTES)));
+        PRISM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
         int sms = 0;
         PRISM_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
         cfg.gridDim = dim3(static_cast<unsigned>(sms / 2 * 2));
@@ -716,14 +942,61 @@ int launch_gemm_pair(int dev, int M, int N, int K, const void* A, const void* B,
         PRISM_CUDA_TRY(cudaOccupancyMaxActiveClusters(&clusters, kern, &cfg));
         if (clusters < 1) return set_error(PRISM_B200_ERR_CUDA, "gemm_bf16: no 2-CTA cluster fits on this device");
         pairs_cap = clusters;
-        if (dev >= 0 && dev < 64) max_pairs[dev] = clusters;
+        *pairs_cache = clusters;
     }
-    const int tiles = (M / P_::BLOCK) * (N / P_::BLOCK);
     const int pairs = tiles < pairs_cap ? tiles : pairs_cap;
     cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs));
     PRISM_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, M, N, K, static_cast<__nv_bfloat16*>(C), map_a, map_b));
     count_launch();
     return PRISM_B200_OK;
+}
+
+int raster_group() {
+    static int group = 0;  // TUNING: PRISM_B200_GEMM_GROUP = m-tiles walked per n-tile (4, 8, 16)
+    if (group == 0) {
+        const char* e = getenv("PRISM_B200_GEMM_GROUP");
+        group = e ? atoi(e) : 8;
+        if (group != 4 && group != 16) group = 8;
+    }
+    return group;
+}
+
+int launch_gemm_pair(int dev, int M, int N, int K, const void* A, const void* B, void* C, cudaStream_t s) {
+    using P_ = g16::PairCfg;
+    CUtensorMap map_a, map_b;
+    if (int rc = get_tensor_map(dev, A, M, K, P_::HALF, &map_a)) return rc;
+    if (int rc = get_tensor_map(dev, B, N, K, P_::HALF, &map_b)) return rc;
+    const int group = raster_group();
+    PairKernel kern = group == 4 ? cutlass_my_h100_match_no_tail_pair<4>
+                    : group == 16 ? cutlass_my_h100_match_no_tail_pair<16>
+                                  : cutlass_my_h100_match_no_tail_pair<8>;
+    static int max_pairs[3][64] = {};
+    static int scratch = 0;
+    int* cache = (dev >= 0 && dev < 64) ? &max_pairs[group == 4 ? 0 : group == 16 ? 2 : 1][dev] : &(scratch = 0);
+    return launch_pair_kernel(kern, cache, g16::THREADS, P_::SMEM_BYTES, (M / P_::BLOCK) * (N / P_::BLOCK), dev, M, N, K,
+                              map_a, map_b, C, s);
+}
+
+int launch_gemm_pair_wide(int dev, int M, int N, int K, const void* A, const void* B, void* C, cudaStream_t s) {
+    using W_ = g16::WideCfg;
+    static bool tuned = false;
+    if (!tuned) {
+        tuned = true;
+        if (const char* e = getenv("PRISM_B200_GEMM_SLEEP")) { int v = atoi(e); cudaMemcpyToSymbol(g_tune_sleep_ns, &v, 4); }
+        if (const char* e = getenv("PRISM_B200_GEMM_ORDER")) { int v = atoi(e); cudaMemcpyToSymbol(g_tune_order, &v, 4); }
+    }
+    CUtensorMap map_a, map_b;
+    if (int rc = get_tensor_map(dev, A, M, K, W_::HALF, &map_a)) return rc;
+    if (int rc = get_tensor_map(dev, B, N, K, W_::HALF, &map_b)) return rc;
+    const int group = raster_group();
+    PairKernel kern = group == 4 ? cutlass_my_h100_match_no_tail_pair_wide<4>
+                    : group == 16 ? cutlass_my_h100_match_no_tail_pair_wide<16>
+                                  : cutlass_my_h100_match_no_tail_pair_wide<8>;
+    static int max_pairs[3][64] = {};
+    static int scratch = 0;
+    int* cache = (dev >= 0 && dev < 64) ? &max_pairs[group == 4 ? 0 : group == 16 ? 2 : 1][dev] : &(scratch = 0);
+    return launch_pair_kernel(kern, cache, W_::THREADS, W_::SMEM_BYTES, (M / W_::TILE_M) * (N / W_::TILE_N), dev, M, N, K,
+                              map_a, map_b, C, s);
 }
 
 }  // namespace
@@ -752,12 +1025,26 @@ extern "C" int prism_b200_gemm_bf16(int M, int N, int K, const uint16_t* A, cons
     }
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     {
-        static int use_pair = -1;  // TUNING: PRISM_B200_GEMM_PAIR=1 selects the two-CTA kernel where the shape allows
-        if (use_pair < 0) {
+        // Two-CTA tiles (256 x 256 per pair) once there are at least two waves of them; smaller
+        // problems fill the machine better with one-CTA tiles.  PRISM_B200_GEMM_PAIR=0/1 overrides.
+        static int force_pair = -2;
+        if (force_pair == -2) {
             const char* e = getenv("PRISM_B200_GEMM_PAIR");
-            use_pair = (e && e[0] == '1') ? 1 : 0;
+            force_pair = e ? (e[0] == '1' ? 1 : 0) : -1;
         }
-        if (use_pair && M % 256 == 0 && N % 256 == 0) return launch_gemm_pair(dev, M, N, K, A, B, C, s);
+        const bool pair_ok = M % 256 == 0 && N % 256 == 0;
+        const long long pair_tiles = static_cast<long long>(M / 256) * (N / 256);
+        const bool pair = force_pair == 1 ? pair_ok : force_pair == 0 ? false : (pair_ok && pair_tiles >= sms);
+        // 512 x 256 pair tiles once there are at least two waves of those; PRISM_B200_GEMM_PAIR=2 forces them.
+        const bool wide_ok = M % 256 == 0 && N % 512 == 0;
+        static int force_wide = -2;
+        if (force_wide == -2) {
+            const char* e = getenv("PRISM_B200_GEMM_PAIR");
+            force_wide = e ? (e[0] == '2' ? 1 : 0) : -1;
+        }
+        const bool wide = force_wide == 1 ? wide_ok : force_wide == 0 ? false : (wide_ok && pair_tiles / 2 >= sms);
+        if (wide) return launch_gemm_pair_wide(dev, M, N, K, A, B, C, s);
+        if (pair) return launch_gemm_pair(dev, M, N, K, A, B, C, s);
     }
     // 256-wide m-tiles halve the operand traffic per flop; fall back to 128 when M
     // does not divide or when the wider tile would leave a poorly filled last wave.

@@ -44,6 +44,45 @@ def test_matches_fp64_oracle(pb, shape):
     assert ok, f"worst error / bound = {worst}"
 
 
+_CHILD = """
+import sys, numpy as np, torch
+sys.path.insert(0, %r)
+import prism_b200 as pb
+from oracle import cpu_oracle as O
+worst = 0.0
+for (M, N, K) in %r:
+    A, B = O.gemm_bf16_inputs(M, N, K, seed=M + N + K)
+    a = torch.from_numpy(A.view(np.int16)).cuda().view(torch.bfloat16)
+    b = torch.from_numpy(B.view(np.int16)).cuda().view(torch.bfloat16)
+    c = torch.full((N, M), float('nan'), dtype=torch.bfloat16, device='cuda')
+    pb.runmyh100(M, N, K, a, b, c); torch.cuda.synchronize()
+    ok, w = O.gemm_bf16_check(c.view(torch.int16).cpu().numpy().view(np.uint16), O.gemm_bf16_cpu(A, B))
+    assert ok, (M, N, K, w)
+    worst = max(worst, w)
+assert pb.last_error()[0] == 0, pb.last_error()
+print('ok', worst)
+"""
+
+
+@pytest.mark.parametrize("mode,shapes", [
+    # one-CTA kernels only
+    ("0", [(256, 256, 128), (1024, 1024, 512), (2048, 4096, 256)]),
+    # two-CTA kernel, 256 x 256 pair tiles: one tile, several k-blocks (ring wrap), more tiles than pairs
+    ("1", [(256, 256, 64), (256, 512, 1024), (1024, 2048, 320), (4096, 4096, 256)]),
+    # two-CTA kernel, 512 x 256 pair tiles
+    ("2", [(256, 512, 64), (512, 512, 1024), (1024, 2048, 320), (4096, 4096, 256), (2048, 8192, 128)]),
+])
+def test_every_kernel_form_forced(mode, shapes):
+    """The launcher picks a kernel form by problem size; each form is forced here on small and
+    multi-wave shapes (the choice is read from the environment once per process, hence the child)."""
+    import os
+    import subprocess
+    env = dict(os.environ, PRISM_B200_GEMM_PAIR=mode)
+    r = subprocess.run([sys.executable, "-c", _CHILD % (str(ROOT), shapes)], env=env, capture_output=True, text=True,
+                       timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+
+
 def test_layout_is_column_major_and_exact_on_small_integers(pb):
     """Integer-valued inputs with small K: every product and sum is exact in fp32 and in bf16,
     so the result must equal the oracle bit for bit, which also pins the C[n * M + m] layout."""

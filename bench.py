@@ -41,7 +41,11 @@ SCAN_NG = 1 << 30
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel,
 # from the ncu captures summarised under profiles/ (None = not captured).
-NCU_TRAFFIC_BYTES = {"gemm_bf16": None, "sgemm": None, "scan": None}
+NCU_TRAFFIC_BYTES = {
+    "gemm_bf16": 969.7e6,   # 8192^3: 849.7 MB read + 119.9 MB written      (profiles/gemm_bf16_pair_wide_8192.md)
+    "sgemm": 563.8e6,       # 4096^3: 505.7 MB read + 58.1 MB written        (profiles/sgemm_kernel5_4096.md)
+    "scan": 1913.6e6,       # 2^28: 4 x the 478.4 MB captured at 2^26        (profiles/scan_kernel_2p26.md)
+}
 
 
 def load_peaks() -> dict:
@@ -56,19 +60,57 @@ def load_peaks() -> dict:
 
 # --------------------------------------------------------------------------- clocks
 class ClockSampler:
-    """Samples nvidia-smi while the timed region runs."""
+    """Samples SM clock, power and throttle reasons while the timed region runs (NVML, every 5 ms;
+    read-only queries).  Falls back to `nvidia-smi -lms` if NVML cannot be loaded."""
 
+    REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+               0x80: "hw_power_brake_slowdown"}
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, gpu_index: int):
         self.gpu = gpu_index
+        self.samples: list[tuple[float, float, int]] = []
+        self.sm_max = None
+        self.stop_flag = threading.Event()
+        self.thread = None
         self.proc = None
         self.lines: list[str] = []
-        self.thread = None
+        self.nvml = None
+
+    def _physical_index(self) -> int:
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+        if vis:
+            ids = [v.strip() for v in vis.split(",") if v.strip()]
+            if self.gpu < len(ids) and ids[self.gpu].isdigit():
+                return int(ids[self.gpu])
+        return self.gpu
 
     def start(self):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            h = pynvml.nvmlDeviceGetHandleByIndex(self._physical_index())
+            self.sm_max = float(pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM))
+            self.nvml = (pynvml, h)
+        except Exception:
+            self.nvml = None
+        if self.nvml is not None:
+            def loop():
+                nv, h = self.nvml
+                get_reasons = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+                    getattr(nv, "nvmlDeviceGetCurrentClocksThrottleReasons")
+                while not self.stop_flag.is_set():
+                    try:
+                        self.samples.append((float(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)),
+                                             nv.nvmlDeviceGetPowerUsage(h) / 1000.0, int(get_reasons(h))))
+                    except Exception:
+                        pass
+                    time.sleep(0.005)
+            self.thread = threading.Thread(target=loop, daemon=True)
+            self.thread.start()
+            return
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
@@ -83,30 +125,46 @@ class ClockSampler:
         self.thread.start()
 
     def stop(self) -> dict:
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        sm, smax, power, reasons = [], None, [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for ln in self.lines:
-            f = [t.strip() for t in ln.split(",")]
-            if len(f) < 9:
-                continue
+        reasons: set[str] = set()
+        if self.nvml is not None:
+            self.stop_flag.set()
+            self.thread.join(timeout=2)
+            for _, _, mask in self.samples:
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        reasons.add(name)
+            sm = sorted(c for c, _, _ in self.samples)
+            power = [p for _, p, _ in self.samples]
+            smax = self.sm_max
+        elif self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
             try:
-                sm.append(float(f[1])); smax = float(f[2]); power.append(float(f[3]))
-            except ValueError:
-                continue
-            for nm, val in zip(names, f[5:9]):
-                if val.lower().startswith("active"):
-                    reasons.add(nm)
-        sm.sort()
-        # the busiest half of the samples = the samples under load
-        load = sm[len(sm) // 2:] if sm else []
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+            sm, smax, power = [], None, []
+            names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+            for ln in self.lines:
+                f = [t.strip() for t in ln.split(",")]
+                if len(f) < 9:
+                    continue
+                try:
+                    sm.append(float(f[1])); smax = float(f[2]); power.append(float(f[3]))
+                except ValueError:
+                    continue
+                for nm, val in zip(names, f[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(nm)
+            sm.sort()
+        else:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no NVML and no nvidia-smi"]}
+        # the samples with the highest power draw are the ones taken under load
+        if self.nvml is not None and self.samples:
+            by_power = sorted(self.samples, key=lambda t: t[1])
+            load = sorted(c for c, _, _ in by_power[len(by_power) // 2:])
+        else:
+            load = sm[: max(1, len(sm) // 2)] if sm else []
         return {"sm_mhz": (load[len(load) // 2] if load else None), "sm_max_mhz": smax,
                 "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
 

@@ -614,11 +614,6 @@ cutlass_my_h100_match_no_tail_pair(int M, int N, int K, __nv_bfloat16* C, const 
 // each -- and the producer already prefetches the next tile's stages while it runs.
 // Barriers and pairing are as in the kernel above.
 // ============================================================================
-// TUNING ONLY (set from PRISM_B200_GEMM_SLEEP / PRISM_B200_GEMM_ORDER): producer sleep between polls in ns
-// (0 = plain polling) and MMA issue order (0 = accumulators interleaved, 1 = one after the other).
-__device__ int g_tune_sleep_ns = 40;
-__device__ int g_tune_order = 0;
-
 namespace g16 {
 struct WideCfg {
     static constexpr int TILE_N = 512;     // n rows per pair tile (2 CTAs x 2 blocks x 128)
@@ -701,11 +696,8 @@ cutlass_my_h100_match_no_tail_pair_wide(int M, int N, int K, __nv_bfloat16* C,
                 // This CTA's two n blocks and its half of the m rows.
                 const int n_row0 = tn * W_::TILE_N + static_cast<int>(rank) * 256;
                 const int m_row = tm * W_::TILE_M + static_cast<int>(rank) * W_::HALF;
-                const int sleep_ns = g_tune_sleep_ns;
                 for (int kb = 0; kb < k_blocks; ++kb) {
-                    const bool got = sleep_ns ? mbar_wait_bounded_sleepy(&empty_bar[stage], phase ^ 1u, abort_flag, sleep_ns)
-                                              : mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag);
-                    if (!got) {
+                    if (!mbar_wait_bounded_sleepy(&empty_bar[stage], phase ^ 1u, abort_flag, 40)) {
                         timed_out = true;
                         break;
                     }
@@ -744,20 +736,11 @@ cutlass_my_h100_match_no_tail_pair_wide(int M, int N, int K, __nv_bfloat16* C,
                     const uint64_t p0_desc = smem_desc_k_sw128(base);
                     const uint64_t p1_desc = smem_desc_k_sw128(base + W_::BLOCK_BYTES);
                     const uint64_t q_desc = smem_desc_k_sw128(base + 2 * W_::BLOCK_BYTES);
-                    if (g_tune_order == 0) {
 #pragma unroll
-                        for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
-                            const uint32_t accumulate = (kb | k) != 0 ? 1u : 0u;
-                            umma_bf16_pair(tmem_base, p0_desc + 2u * k, q_desc + 2u * k, IDESC, accumulate);
-                            umma_bf16_pair(tmem_base + 256u, p1_desc + 2u * k, q_desc + 2u * k, IDESC, accumulate);
-                        }
-                    } else {
-#pragma unroll
-                        for (int k = 0; k < BLOCK_K / UMMA_K; ++k)
-                            umma_bf16_pair(tmem_base, p0_desc + 2u * k, q_desc + 2u * k, IDESC, (kb | k) != 0 ? 1u : 0u);
-#pragma unroll
-                        for (int k = 0; k < BLOCK_K / UMMA_K; ++k)
-                            umma_bf16_pair(tmem_base + 256u, p1_desc + 2u * k, q_desc + 2u * k, IDESC, (kb | k) != 0 ? 1u : 0u);
+                    for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
+                        const uint32_t accumulate = (kb | k) != 0 ? 1u : 0u;
+                        umma_bf16_pair(tmem_base, p0_desc + 2u * k, q_desc + 2u * k, IDESC, accumulate);
+                        umma_bf16_pair(tmem_base + 256u, p1_desc + 2u * k, q_desc + 2u * k, IDESC, accumulate);
                     }
                     umma_commit_pair(cluster_addr(&empty_bar[stage], 0));
                     umma_commit_pair(cluster_addr(&empty_bar[stage], 1));
@@ -879,15 +862,9 @@ int get_tensor_map(int dev, const void* ptr, int rows, int k, int box_rows, CUte
     const cuuint64_t strides[1] = {static_cast<cuuint64_t>(k) * 2};
     const cuuint32_t box[2] = {static_cast<cuuint32_t>(g16::BLOCK_K), static_cast<cuuint32_t>(box_rows)};
     const cuuint32_t estr[2] = {1, 1};
-    static int promo = -1;  // TUNING: PRISM_B200_GEMM_L2PROMO = 0 none, 1 64B, 2 128B, 3 256B
-    if (promo < 0) {
-        const char* e = getenv("PRISM_B200_GEMM_L2PROMO");
-        promo = e ? atoi(e) : 3;
-        if (promo < 0 || promo > 3) promo = 3;
-    }
     CUresult r = g_encode(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                          static_cast<CUtensorMapL2promotion>(promo), CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return set_error(PRISM_B200_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d", (int)r);
     if (g_maps.size() > 4096) g_maps.clear();
     g_maps.emplace(key, m);
@@ -951,52 +928,30 @@ int launch_pair_kernel(PairKernel kern, int* pairs_cache, int threads, size_t sm
     return PRISM_B200_OK;
 }
 
-int raster_group() {
-    static int group = 0;  // TUNING: PRISM_B200_GEMM_GROUP = m-tiles walked per n-tile (4, 8, 16)
-    if (group == 0) {
-        const char* e = getenv("PRISM_B200_GEMM_GROUP");
-        group = e ? atoi(e) : 8;
-        if (group != 4 && group != 16) group = 8;
-    }
-    return group;
-}
-
+// m-tiles walked per n-tile: 8 for the 256 x 256 pair tiles, 16 for the 512 x 256 ones
+// (measured best of 4 / 8 / 16 / 32 at 8192^3 on a B200).
 int launch_gemm_pair(int dev, int M, int N, int K, const void* A, const void* B, void* C, cudaStream_t s) {
     using P_ = g16::PairCfg;
     CUtensorMap map_a, map_b;
     if (int rc = get_tensor_map(dev, A, M, K, P_::HALF, &map_a)) return rc;
     if (int rc = get_tensor_map(dev, B, N, K, P_::HALF, &map_b)) return rc;
-    const int group = raster_group();
-    PairKernel kern = group == 4 ? cutlass_my_h100_match_no_tail_pair<4>
-                    : group == 16 ? cutlass_my_h100_match_no_tail_pair<16>
-                                  : cutlass_my_h100_match_no_tail_pair<8>;
-    static int max_pairs[3][64] = {};
-    static int scratch = 0;
-    int* cache = (dev >= 0 && dev < 64) ? &max_pairs[group == 4 ? 0 : group == 16 ? 2 : 1][dev] : &(scratch = 0);
-    return launch_pair_kernel(kern, cache, g16::THREADS, P_::SMEM_BYTES, (M / P_::BLOCK) * (N / P_::BLOCK), dev, M, N, K,
-                              map_a, map_b, C, s);
+    static int max_pairs[64] = {};
+    int uncached = 0;
+    int* cache = (dev >= 0 && dev < 64) ? &max_pairs[dev] : &uncached;
+    return launch_pair_kernel(cutlass_my_h100_match_no_tail_pair<8>, cache, g16::THREADS, P_::SMEM_BYTES,
+                              (M / P_::BLOCK) * (N / P_::BLOCK), dev, M, N, K, map_a, map_b, C, s);
 }
 
 int launch_gemm_pair_wide(int dev, int M, int N, int K, const void* A, const void* B, void* C, cudaStream_t s) {
     using W_ = g16::WideCfg;
-    static bool tuned = false;
-    if (!tuned) {
-        tuned = true;
-        if (const char* e = getenv("PRISM_B200_GEMM_SLEEP")) { int v = atoi(e); cudaMemcpyToSymbol(g_tune_sleep_ns, &v, 4); }
-        if (const char* e = getenv("PRISM_B200_GEMM_ORDER")) { int v = atoi(e); cudaMemcpyToSymbol(g_tune_order, &v, 4); }
-    }
     CUtensorMap map_a, map_b;
     if (int rc = get_tensor_map(dev, A, M, K, W_::HALF, &map_a)) return rc;
     if (int rc = get_tensor_map(dev, B, N, K, W_::HALF, &map_b)) return rc;
-    const int group = raster_group();
-    PairKernel kern = group == 4 ? cutlass_my_h100_match_no_tail_pair_wide<4>
-                    : group == 16 ? cutlass_my_h100_match_no_tail_pair_wide<16>
-                                  : cutlass_my_h100_match_no_tail_pair_wide<8>;
-    static int max_pairs[3][64] = {};
-    static int scratch = 0;
-    int* cache = (dev >= 0 && dev < 64) ? &max_pairs[group == 4 ? 0 : group == 16 ? 2 : 1][dev] : &(scratch = 0);
-    return launch_pair_kernel(kern, cache, W_::THREADS, W_::SMEM_BYTES, (M / W_::TILE_M) * (N / W_::TILE_N), dev, M, N, K,
-                              map_a, map_b, C, s);
+    static int max_pairs[64] = {};
+    int uncached = 0;
+    int* cache = (dev >= 0 && dev < 64) ? &max_pairs[dev] : &uncached;
+    return launch_pair_kernel(cutlass_my_h100_match_no_tail_pair_wide<16>, cache, W_::THREADS, W_::SMEM_BYTES,
+                              (M / W_::TILE_M) * (N / W_::TILE_N), dev, M, N, K, map_a, map_b, C, s);
 }
 
 }  // namespace

@@ -1,0 +1,95 @@
+"""The sharded paths on real GPUs: one child process per GPU over NCCL.  Needs at least two GPUs;
+the host-side logic alone is covered on CPU by tests/test_sharding_host.py."""
+import os
+import socket
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+pytestmark = pytest.mark.gpu
+
+_RANK = r"""
+import os, sys
+import numpy as np, torch, torch.distributed as dist
+sys.path.insert(0, %(root)r)
+import prism_b200 as pb
+from prism_b200 import sharded
+from oracle import cpu_oracle as O
+
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+dev = torch.device("cuda", rank)
+
+# scan: contiguous chunks of one seeded array, both schedules, ragged length
+n = (1 << 22) + 12345
+full = O.scan_inputs(n, seed=5, high=1 << 20)
+expect = O.scan_cpu(full)
+lo, hi = sharded.chunk_bounds(n, world, rank)
+for schedule in sharded.ShardedScan.SCHEDULES:
+    x = torch.from_numpy(full[lo:hi].view(np.int32).copy()).to(dev)
+    scan = sharded.ShardedScan(hi - lo, dev, schedule=schedule)
+    scan(x)
+    torch.cuda.synchronize()
+    assert np.array_equal(x.cpu().numpy().view(np.uint32), expect[lo:hi]), (schedule, rank)
+    assert sum(scan.totals_int64()) & 0xFFFFFFFF == int(expect[-1])
+
+# bf16 GEMM: rows of M sharded, B replicated, no collective
+M, N, K = 256 * world, 512, 256
+A, B = O.gemm_bf16_inputs(M, N, K, seed=9)
+plan = sharded.RowShardedGemmBF16(M, N, K)
+a = torch.from_numpy(A[plan.lo:plan.hi].view(np.int16)).to(dev).view(torch.bfloat16)
+b = torch.from_numpy(B.view(np.int16)).to(dev).view(torch.bfloat16)
+c = torch.empty((N, plan.rows), dtype=torch.bfloat16, device=dev)
+plan(a, b, c)
+torch.cuda.synchronize()
+ref = O.gemm_bf16_cpu(A[plan.lo:plan.hi], B)
+ok, worst = O.gemm_bf16_check(c.view(torch.int16).cpu().numpy().view(np.uint16), ref)
+assert ok, worst
+
+# SGEMM the same way
+A, B, C = O.sgemm_inputs(M, 256, 128, seed=3)
+sp = sharded.RowShardedSgemm(M, 256, 128)
+ta, tb, tc = (torch.from_numpy(np.ascontiguousarray(t)).to(dev) for t in (A[sp.lo:sp.hi], B, C[sp.lo:sp.hi]))
+sp(1.5, ta, tb, 0.5, tc)
+torch.cuda.synchronize()
+err = O.sgemm_rel_error(tc.cpu().numpy(), O.sgemm_cpu(1.5, A[sp.lo:sp.hi], B, 0.5, C[sp.lo:sp.hi]))
+assert err <= O.SGEMM_TOL, err
+assert pb.last_error()[0] == 0, pb.last_error()
+dist.barrier()
+dist.destroy_process_group()
+print("rank", rank, "ok")
+"""
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def test_sharded_scan_and_gemm_over_nccl():
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs at least two GPUs")
+    port = _free_port()
+    procs = []
+    for rank in range(world):
+        env = dict(os.environ, RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
+                   MASTER_PORT=str(port))
+        procs.append(subprocess.Popen([sys.executable, "-c", _RANK % {"root": str(ROOT)}], env=env,
+                                      stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
+    outs = []
+    for p in procs:
+        try:
+            out, _ = p.communicate(timeout=600)
+        except subprocess.TimeoutExpired:
+            p.kill()
+            out, _ = p.communicate()
+        outs.append(out)
+    for rank, (p, out) in enumerate(zip(procs, outs)):
+        assert p.returncode == 0, f"rank {rank} failed:\n{out[-3000:]}"

@@ -179,6 +179,7 @@ def dist_setup(n_gpus: int):
     if world > 1:
         import torch.distributed as dist
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")   # stdout carries the one JSON line only
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     return world, rank, local
 
@@ -284,7 +285,7 @@ def run_gemm_bf16(args, world, rank, peaks):
                 "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                 "peak_source": f"{peaks['source']} cuBLAS bf16 burst", "frac_of_sustained": achieved / peaks["bf16_tflops_sustained"],
                 "frac_of_nominal_2250": achieved / 2250.0,
-                "traffic": NCU_TRAFFIC_BYTES["gemm_bf16"]}
+                "traffic": NCU_TRAFFIC_BYTES["gemm_bf16"] if (S == GEMM_S and world == 1) else None}
     line = {"metric": "bf16 GEMM TFLOP/s (D = A*B^T, M=N=K=%d, fp32 accumulate, bf16 out)" % S, "value": value,
             "unit": "TFLOP/s", "ms_per_step": ms, "scaling": "strong", "dtype": "bf16",
             "config": {"workload": "gemm_bf16 %dx%dx%d, A and B K-major, C column-major, values 0.1*normal bf16" % (S, S, S),
@@ -343,7 +344,7 @@ def run_sgemm(args, world, rank, peaks, steps=None, warmup=None):
                          "peak": peak_nominal, "unit": "TFLOP/s", "frac": achieved / peak_nominal,
                          "peak_source": "148 SMs x 128 FMA/clk x 2 x %.0f MHz (max SM clock)" % sm_max,
                          "frac_at_observed_clock": achieved / peak_at_clock, "observed_sm_mhz": sm_load,
-                         "traffic": NCU_TRAFFIC_BYTES["sgemm"]},
+                         "traffic": NCU_TRAFFIC_BYTES["sgemm"] if (S == SGEMM_S and world == 1) else None},
             "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": op.h2d_bytes, "d2h_bytes_per_step": op.d2h_bytes},
             "gpu_launches": launches, "clocks": clocks, "rel_error_sampled_rows": err, "spot_check_ok": err <= 1e-5}
@@ -396,7 +397,7 @@ def run_scan(args, world, rank, peaks, steps=None, warmup=None):
                          "frac": achieved / peak, "peak_source": f"{peaks['source']} copy bandwidth",
                          "frac_of_nominal_8000": achieved / 8000.0,
                          "note": "8 B/element algorithmic; per-GPU rate of the whole step (all passes)",
-                         "traffic": NCU_TRAFFIC_BYTES["scan"]},
+                         "traffic": NCU_TRAFFIC_BYTES["scan"] if n == SCAN_N1 else None},
             "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "spot_check_ok": ok}
 
 

@@ -84,6 +84,17 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
     return LIB_PATH
 
 
+def build_evals() -> Path:
+    """Compile the evaluation programs under prism_b200/evals (needs the library built)."""
+    evals = PKG_DIR / "evals"
+    r = subprocess.run(["make", "-C", str(evals), f"NVCC={_nvcc()}"], stdout=subprocess.PIPE, stderr=subprocess.STDOUT,
+                       text=True)
+    if r.returncode != 0:
+        sys.stdout.write(r.stdout)
+        raise RuntimeError("prism_b200/evals: build failed")
+    return evals / "build"
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--force", action="store_true")

@@ -1,0 +1,61 @@
+"""The evaluation programs (prism_b200/evals) on small sizes: they must pass their own checks against
+cuBLAS / CUB / a CPU loop and print lines in the formats the reference's plotting script parses
+(evals/plot_results.py:18-108; the patterns below restate what that script looks for)."""
+import re
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+EVALS = ROOT / "prism_b200" / "evals"
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def binaries():
+    sys.path.insert(0, str(ROOT))
+    from prism_b200 import build
+    build.build_library()
+    build.build_evals()
+    return EVALS / "build"
+
+
+def _run(cmd):
+    r = subprocess.run([str(c) for c in cmd], capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    return r.stdout
+
+
+def test_sgemm_sweep_format_and_checks(binaries):
+    out = _run([binaries / "sgemm_sweep", 512])
+    assert out.count("PASSED") == 5 and "FAILED" not in out
+    perf = out.split("Starting Performance Sweep")[1]
+    sizes = [int(m.group(1)) for m in re.finditer(r"^Size:\s+(\d+)x(\d+)x(\d+)", perf, re.M)]
+    assert sizes == [256, 512]
+    assert len(re.findall(r"^\[cuBLAS FP32\]", perf, re.M)) == 2
+    assert [int(k) for k in re.findall(r"^\[My Kernel (\d+)\]", perf, re.M)] == [1, 2, 3, 4, 5] * 2
+    vals = re.findall(r"performance:\s+\(\s*([\d.]+)\)\s+GFLOPS.*size:\s+\((\d+)\)", perf)
+    assert len(vals) == 12 and all(float(v) > 0 for v, _ in vals)
+
+
+def test_scan_bench_format_and_checks(binaries):
+    out = _run([binaries / "scan_bench", 21])
+    assert "mismatch" not in out
+    lines = out.strip().splitlines()
+    assert "Size" in lines[0] and "CUB (GB/s)" in lines[0] and lines[1].startswith("---")
+    rows = []
+    for ln in lines[2:]:
+        parts = re.split(r"\s*\|\s*", ln.strip())
+        rows.append((int(parts[0]), float(parts[1].split()[1]), float(parts[2].split()[1])))
+    assert [r[0] for r in rows] == [1 << 20, 1 << 21]
+    assert all(cub > 0 and ours > 0 for _, cub, ours in rows)
+
+
+def test_bf16_bench_format_and_checks(binaries):
+    out = _run([binaries / "bf16_bench", 1024])
+    assert "Passed correctness verification!" in out
+    k = re.search(r"Kernel:\s+.*performance:\s+\(\s*([\d.]+)\)\s+TFLOPS.*size:\s+\((\d+)\)", out)
+    c = re.search(r"cuBLAS:\s+.*performance:\s+\(\s*([\d.]+)\)\s+TFLOPS.*size:\s+\((\d+)\)", out)
+    assert k and c and int(k.group(2)) == 1024 and float(k.group(1)) > 0 and float(c.group(1)) > 0

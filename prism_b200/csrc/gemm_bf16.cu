@@ -624,7 +624,10 @@ struct WideCfg {
     static constexpr int THREADS = 64 + 32 * EPI_WARPS;
     static constexpr uint32_t BLOCK_BYTES = HALF * BLOCK_K * 2;   // one 128-row operand block
     static constexpr uint32_t STAGE_BYTES = 3 * BLOCK_BYTES;      // P0, P1, Q half
-    static constexpr size_t SMEM_BYTES = 1024 + static_cast<size_t>(STAGES) * STAGE_BYTES + (2 * STAGES + 2) * 8 + 16;
+    static constexpr uint32_t BAR_BYTES = 128;                    // barriers, TMEM slot, abort flag
+    static constexpr uint32_t EPI_WARP_BYTES = 32 * 128;          // 32 rows x 64 bf16 per epilogue warp
+    static constexpr size_t SMEM_BYTES =
+        1024 + static_cast<size_t>(STAGES) * STAGE_BYTES + BAR_BYTES + EPI_WARPS * EPI_WARP_BYTES;
 };
 }  // namespace g16
 
@@ -647,6 +650,7 @@ cutlass_my_h100_match_no_tail_pair_wide(int M, int N, int K, __nv_bfloat16* C,
     uint64_t* acc_empty_bar = acc_full_bar + 1;    // [1], only the leader's is used
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty_bar + 1);
     volatile uint32_t* abort_flag = tmem_slot + 1;
+    unsigned char* epi_smem = ring + STAGES * W_::STAGE_BYTES + W_::BAR_BYTES;   // 128-byte aligned
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -771,24 +775,39 @@ cutlass_my_h100_match_no_tail_pair_wide(int M, int N, int K, __nv_bfloat16* C,
                 break;
             }
             tc_fence_after();
-            const size_t n = static_cast<size_t>(tn) * W_::TILE_N + rank * 256 + block * W_::HALF + quarter * 32 + lane;
-            __nv_bfloat16* c_row = C + n * static_cast<size_t>(M) + static_cast<size_t>(tm) * W_::TILE_M;
+            // A lane reads one accumulator row (one n, consecutive m).  Writing that row straight to
+            // global memory would make every store instruction touch 32 different lines, 16 bytes
+            // each; instead the warp passes 32 rows x 64 columns at a time through shared memory
+            // (16-byte chunks XOR-swizzled by row, conflict-free both ways) and stores whole
+            // 128-byte lines: 4 rows per instruction.
+            const size_t n_warp = static_cast<size_t>(tn) * W_::TILE_N + rank * 256 + block * W_::HALF + quarter * 32;
+            __nv_bfloat16* c_warp = C + n_warp * static_cast<size_t>(M) + static_cast<size_t>(tm) * W_::TILE_M;
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(block * 256);
-#pragma unroll 2
-            for (int c = 0; c < W_::TILE_M; c += 32) {
-                uint32_t r[32];
-                tmem_ld_32cols(t_row + c, r);
+            unsigned char* stage_buf = epi_smem + (warp - 2) * W_::EPI_WARP_BYTES;
+            for (int c0 = 0; c0 < W_::TILE_M; c0 += 64) {
+                uint32_t r0[32], r1[32];
+                tmem_ld_32cols(t_row + c0, r0);
+                tmem_ld_32cols(t_row + c0 + 32, r1);
                 tmem_ld_wait();
-                uint4* dst = reinterpret_cast<uint4*>(c_row + c);
 #pragma unroll
-                for (int v = 0; v < 4; ++v) {
+                for (int ch = 0; ch < 8; ++ch) {
+                    const uint32_t* r = ch < 4 ? &r0[8 * ch] : &r1[8 * (ch - 4)];
                     uint4 o;
-                    o.x = pack_bf16(r[8 * v + 0], r[8 * v + 1]);
-                    o.y = pack_bf16(r[8 * v + 2], r[8 * v + 3]);
-                    o.z = pack_bf16(r[8 * v + 4], r[8 * v + 5]);
-                    o.w = pack_bf16(r[8 * v + 6], r[8 * v + 7]);
-                    dst[v] = o;
+                    o.x = pack_bf16(r[0], r[1]);
+                    o.y = pack_bf16(r[2], r[3]);
+                    o.z = pack_bf16(r[4], r[5]);
+                    o.w = pack_bf16(r[6], r[7]);
+                    *reinterpret_cast<uint4*>(stage_buf + lane * 128 + ((ch ^ (lane & 7)) << 4)) = o;
                 }
+                __syncwarp();
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int row = 4 * j + (lane >> 3);
+                    const int ch = lane & 7;
+                    const uint4 v = *reinterpret_cast<const uint4*>(stage_buf + row * 128 + ((ch ^ (row & 7)) << 4));
+                    *reinterpret_cast<uint4*>(c_warp + static_cast<size_t>(row) * M + c0 + ch * 8) = v;
+                }
+                __syncwarp();
             }
             tc_fence_before();
             __syncwarp();
@@ -980,26 +999,40 @@ extern "C" int prism_b200_gemm_bf16(int M, int N, int K, const uint16_t* A, cons
     }
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     {
-        // Two-CTA tiles (256 x 256 per pair) once there are at least two waves of them; smaller
-        // problems fill the machine better with one-CTA tiles.  PRISM_B200_GEMM_PAIR=0/1 overrides.
-        static int force_pair = -2;
-        if (force_pair == -2) {
+        // Which form: estimated main-loop time in units of one 128 x 256 tile on one SM, waves x
+        // tile size / (measured relative efficiency of the form).  Small problems (under 2^35
+        // multiply-adds) stay with the one-CTA forms, whose launch costs less.
+        // PRISM_B200_GEMM_PAIR = 0 / 1 / 2 forces one-CTA / 256 x 256 pair / 512 x 256 pair (used by the tests).
+        static int forced = -2;
+        if (forced == -2) {
             const char* e = getenv("PRISM_B200_GEMM_PAIR");
-            force_pair = e ? (e[0] == '1' ? 1 : 0) : -1;
+            forced = e ? atoi(e) : -1;
         }
         const bool pair_ok = M % 256 == 0 && N % 256 == 0;
-        const long long pair_tiles = static_cast<long long>(M / 256) * (N / 256);
-        const bool pair = force_pair == 1 ? pair_ok : force_pair == 0 ? false : (pair_ok && pair_tiles >= sms);
-        // 512 x 256 pair tiles once there are at least two waves of those; PRISM_B200_GEMM_PAIR=2 forces them.
         const bool wide_ok = M % 256 == 0 && N % 512 == 0;
-        static int force_wide = -2;
-        if (force_wide == -2) {
-            const char* e = getenv("PRISM_B200_GEMM_PAIR");
-            force_wide = e ? (e[0] == '2' ? 1 : 0) : -1;
+        int form = 0;  // 0 one CTA, 1 pair, 2 wide pair
+        if (forced >= 0) {
+            form = (forced == 2 && wide_ok) ? 2 : (forced == 1 && pair_ok) ? 1 : 0;
+        } else if (static_cast<double>(M) * N * K >= 34359738368.0) {
+            const int pairs = sms / 2 > 0 ? sms / 2 : 1;
+            auto waves = [](long long tiles, int slots) { return static_cast<double>((tiles + slots - 1) / slots); };
+            const double t_single = waves(static_cast<long long>(M / 128) * (N / 128), sms) * 0.5 / 0.75;
+            double best = t_single;
+            if (M % 256 == 0) {
+                const double t = waves(static_cast<long long>(M / 256) * (N / 128), sms) / 0.93;
+                if (t < best) best = t;
+            }
+            if (pair_ok) {
+                const double t = waves(static_cast<long long>(M / 256) * (N / 256), pairs) / 0.97;
+                if (t < best) { best = t; form = 1; }
+            }
+            if (wide_ok) {
+                const double t = waves(static_cast<long long>(M / 256) * (N / 512), pairs) * 2.0;
+                if (t <= best) { best = t; form = 2; }
+            }
         }
-        const bool wide = force_wide == 1 ? wide_ok : force_wide == 0 ? false : (wide_ok && pair_tiles / 2 >= sms);
-        if (wide) return launch_gemm_pair_wide(dev, M, N, K, A, B, C, s);
-        if (pair) return launch_gemm_pair(dev, M, N, K, A, B, C, s);
+        if (form == 2) return launch_gemm_pair_wide(dev, M, N, K, A, B, C, s);
+        if (form == 1) return launch_gemm_pair(dev, M, N, K, A, B, C, s);
     }
     // 256-wide m-tiles halve the operand traffic per flop; fall back to 128 when M
     // does not divide or when the wider tile would leave a poorly filled last wave.

@@ -55,6 +55,15 @@ int prism_b200_last_error(int* code, char* msg, size_t len);
 /* Clears the sticky error state (host side and the device status word). */
 void prism_b200_clear_error(void);
 
+/*
+ * Exercises the device-side error path without any fault: one warp waits at most limit_ns
+ * (1 ns .. 10 ms) for a barrier that nothing completes, records the timeout and returns.  After the
+ * stream is synchronised prism_b200_last_error() reports PRISM_B200_ERR_DEVICE_TIMEOUT; the context
+ * stays usable.  The reference has no device-side error path (its waits spin without bound,
+ * generated/lookback_to_prev_blocks.cu:13-14, evals/h100_bench/utils.cuh:259-273).
+ */
+int prism_b200_selftest_wait_timeout(unsigned long long limit_ns, void* stream);
+
 /* Number of kernels this library has launched since load (all entry points). */
 unsigned long long prism_b200_launch_count(void);
 

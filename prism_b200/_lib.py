@@ -29,6 +29,7 @@ SIGNATURES = {
     "prism_b200_last_error": (c_int, [POINTER(c_int), c_char_p, c_size_t]),
     "prism_b200_clear_error": (None, []),
     "prism_b200_launch_count": (c_ulonglong, []),
+    "prism_b200_selftest_wait_timeout": (c_int, [c_ulonglong, c_void_p]),
     "prism_b200_sgemm": (c_int, [c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_float, c_void_p, c_void_p]),
     "prism_b200_scan_workspace_size": (c_int, [c_size_t, POINTER(c_size_t)]),
     "prism_b200_scan": (c_int, [c_size_t, c_void_p, c_void_p, c_void_p]),

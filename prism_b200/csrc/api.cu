@@ -55,6 +55,33 @@ uint32_t* device_status_word() {
 
 using namespace prism_b200;
 
+// One warp waits, with the given limit, on a barrier phase that nothing completes, reports the
+// timeout through the status word and returns: the path every kernel here takes when one of its
+// bounded waits runs out, in its smallest form.
+__global__ void selftest_wait_timeout_kernel(unsigned long long limit_ns) {
+    __shared__ uint64_t bar;
+    __shared__ uint32_t never;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        never = 0;
+        fence_barrier_init();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        if (!mbar_wait_bounded(&bar, 0, &never, limit_ns)) raise_device_status(DEV_SELFTEST_TIMEOUT);
+    }
+}
+
+extern "C" int prism_b200_selftest_wait_timeout(unsigned long long limit_ns, void* stream) {
+    if (limit_ns == 0 || limit_ns > 10ull * 1000 * 1000)
+        return set_error(PRISM_B200_ERR_INVALID_ARGUMENT, "selftest_wait_timeout: limit must be 1 ns .. 10 ms");
+    if (int rc = bind_status_word()) return rc;
+    selftest_wait_timeout_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(limit_ns);
+    PRISM_CUDA_TRY(cudaGetLastError());
+    count_launch();
+    return PRISM_B200_OK;
+}
+
 extern "C" int prism_b200_version(void) { return 100; }
 
 extern "C" int prism_b200_last_error(int* code, char* msg, size_t len) {
@@ -66,6 +93,7 @@ extern "C" int prism_b200_last_error(int* code, char* msg, size_t len) {
             const char* which = dev == DEV_SCAN_LOOKBACK_TIMEOUT ? "scan look-back"
                               : dev == DEV_SGEMM_PIPE_TIMEOUT    ? "sgemm smem pipeline"
                               : dev == DEV_GEMM_PIPE_TIMEOUT     ? "bf16 gemm pipeline"
+                              : dev == DEV_SELFTEST_TIMEOUT      ? "self-test (as requested)"
                                                                   : "unknown";
             snprintf(g_msg, sizeof(g_msg), "device-side wait ran out in %s (status 0x%08x)", which, dev);
         }

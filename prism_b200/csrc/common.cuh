@@ -26,6 +26,7 @@ enum : uint32_t {
     DEV_SCAN_LOOKBACK_TIMEOUT = 0x5CA10001u,
     DEV_SGEMM_PIPE_TIMEOUT    = 0x56E30001u,
     DEV_GEMM_PIPE_TIMEOUT     = 0xB16E0001u,
+    DEV_SELFTEST_TIMEOUT      = 0x5E1F0001u,
 };
 
 #define PRISM_CUDA_TRY(expr)                                            \

@@ -360,12 +360,16 @@ cutlass_my_h100_match_no_tail(int M, int N, int K, __nv_bfloat16* C, const __gri
 // ============================================================================
 namespace g16 {
 struct PairCfg {
+    static constexpr int EPI_WARPS = 4;
     static constexpr int BLOCK = 256;      // tile edge of the pair, both in n and in m
     static constexpr int HALF = 128;       // rows of either operand staged by one CTA
     static constexpr int STAGES = 6;
     static constexpr uint32_t HALF_BYTES = HALF * BLOCK_K * 2;
     static constexpr uint32_t STAGE_BYTES = 2 * HALF_BYTES;  // per CTA
-    static constexpr size_t SMEM_BYTES = 1024 + static_cast<size_t>(STAGES) * STAGE_BYTES + (2 * STAGES + 4) * 8 + 16;
+    static constexpr uint32_t BAR_BYTES = 256;                // barriers, TMEM slot, flags
+    static constexpr uint32_t EPI_WARP_BYTES = 32 * 128;      // 32 rows x 64 bf16 per epilogue warp
+    static constexpr size_t SMEM_BYTES =
+        1024 + static_cast<size_t>(STAGES) * STAGE_BYTES + BAR_BYTES + EPI_WARPS * EPI_WARP_BYTES;
 };
 }  // namespace g16
 
@@ -429,6 +433,7 @@ cutlass_my_h100_match_no_tail_pair(int M, int N, int K, __nv_bfloat16* C, const 
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty_bar + 2);
     volatile uint32_t* abort_flag = tmem_slot + 1;
     volatile uint32_t* never_flag = tmem_slot + 2;
+    unsigned char* epi_smem = ring + STAGES * P_::STAGE_BYTES + P_::BAR_BYTES;   // 128-byte aligned
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -556,25 +561,37 @@ cutlass_my_h100_match_no_tail_pair(int M, int N, int K, __nv_bfloat16* C, const 
                 break;
             }
             tc_fence_after();
-            const size_t n = static_cast<size_t>(tn) * P_::BLOCK + rank * P_::HALF + quarter * 32 + lane;
-            __nv_bfloat16* c_row = C + n * static_cast<size_t>(M) + static_cast<size_t>(tm) * P_::BLOCK;
+            // 32 rows x 64 columns at a time through shared memory (16-byte chunks XOR-swizzled by
+            // row), so that every store instruction writes four whole 128-byte lines.
+            const size_t n_warp = static_cast<size_t>(tn) * P_::BLOCK + rank * P_::HALF + quarter * 32;
+            __nv_bfloat16* c_warp = C + n_warp * static_cast<size_t>(M) + static_cast<size_t>(tm) * P_::BLOCK;
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                                    static_cast<uint32_t>(acc * P_::BLOCK);
-#pragma unroll 2
-            for (int c = 0; c < P_::BLOCK; c += 32) {
-                uint32_t r[32];
-                tmem_ld_32cols(t_row + c, r);
+            unsigned char* stage_buf = epi_smem + (warp - 2) * P_::EPI_WARP_BYTES;
+            for (int c0 = 0; c0 < P_::BLOCK; c0 += 64) {
+                uint32_t r0[32], r1[32];
+                tmem_ld_32cols(t_row + c0, r0);
+                tmem_ld_32cols(t_row + c0 + 32, r1);
                 tmem_ld_wait();
-                uint4* dst = reinterpret_cast<uint4*>(c_row + c);
 #pragma unroll
-                for (int v = 0; v < 4; ++v) {
+                for (int ch = 0; ch < 8; ++ch) {
+                    const uint32_t* r = ch < 4 ? &r0[8 * ch] : &r1[8 * (ch - 4)];
                     uint4 o;
-                    o.x = pack_bf16(r[8 * v + 0], r[8 * v + 1]);
-                    o.y = pack_bf16(r[8 * v + 2], r[8 * v + 3]);
-                    o.z = pack_bf16(r[8 * v + 4], r[8 * v + 5]);
-                    o.w = pack_bf16(r[8 * v + 6], r[8 * v + 7]);
-                    dst[v] = o;
+                    o.x = pack_bf16(r[0], r[1]);
+                    o.y = pack_bf16(r[2], r[3]);
+                    o.z = pack_bf16(r[4], r[5]);
+                    o.w = pack_bf16(r[6], r[7]);
+                    *reinterpret_cast<uint4*>(stage_buf + lane * 128 + ((ch ^ (lane & 7)) << 4)) = o;
                 }
+                __syncwarp();
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int row = 4 * j + (lane >> 3);
+                    const int ch = lane & 7;
+                    const uint4 v = *reinterpret_cast<const uint4*>(stage_buf + row * 128 + ((ch ^ (row & 7)) << 4));
+                    *reinterpret_cast<uint4*>(c_warp + static_cast<size_t>(row) * M + c0 + ch * 8) = v;
+                }
+                __syncwarp();
             }
             tc_fence_before();
             __syncwarp();

@@ -368,7 +368,8 @@ def run_scan(args, world, rank, peaks, steps=None, warmup=None):
     sampler.start()
     l0 = pb.launch_count()
     total_ms, per = time_steps(lambda: scan(x), steps, warmup, world, reset=lambda: x.copy_(src))
-    launches = (pb.launch_count() - l0) - warmup * (1 if world == 1 else 2)
+    per_step = 1 if world == 1 else (3 if scan.schedule == "peer_words" else 2)
+    launches = (pb.launch_count() - l0) - warmup * per_step
     clocks = sampler.stop()
     ms = total_ms / steps
     nbytes = 8.0 * n_total
@@ -391,7 +392,9 @@ def run_scan(args, world, rank, peaks, steps=None, warmup=None):
             "unit": "GB/s", "ms_per_step": ms, "scaling": "strong" if world > 1 else "weak", "dtype": "u32",
             "config": {"workload": f"scan n=2^{n_total.bit_length() - 1} int32 values in {{0,1}}, in place",
                        "sharding": f"contiguous chunks over {world} GPU(s); " +
-                       ("single pass" if world == 1 else f"{args.scan_schedule}: one all-gather of per-shard totals"),
+                       ("single pass" if world == 1 else
+                        f"{scan.schedule}: " + ("per-shard totals stored into peer memory over NVLink, no collective"
+                                                if scan.schedule == "peer_words" else "one all-gather of per-shard totals")),
                        "elements_per_gpu": n, "l2": "input restored from a pristine copy before every step (untimed); array larger than L2"},
             "roofline": {"bound": "hbm", "kernel": "scan_kernel", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "peak_source": f"{peaks['source']} copy bandwidth",
@@ -556,7 +559,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=["gemm_bf16", "sgemm", "scan"], default="gemm_bf16")
-    ap.add_argument("--scan-schedule", choices=["reduce_then_scan", "scan_then_carry"], default="reduce_then_scan")
+    ap.add_argument("--scan-schedule", choices=["peer_words", "reduce_then_scan", "scan_then_carry"], default=None,
+                    help="sharded scan schedule (default: peer_words on more than one GPU)")
     ap.add_argument("--size", type=int, default=0,
                     help="square GEMM size for --workload gemm_bf16/sgemm (default 8192 / 4096); smaller sizes are for profiling")
     ap.add_argument("--scan-log2n", type=int, default=0, help="scan length 2^k (default: 28 on one GPU, 30 sharded)")

@@ -129,6 +129,26 @@ int prism_b200_scan_add_carry(size_t n, uint32_t* x, const uint32_t* totals,
                               int rank, void* stream);
 
 /*
+ * The same exchange without a collective call, over peer memory (NVLink / NVSwitch).  Every rank
+ * owns an array `slots` of 2 * world 64-bit words that all ranks can write (peer-mapped or
+ * symmetric memory, zeroed once).  Per call, with a non-zero `epoch` that changes from call to call
+ * (1, 2, 3, ...) and is the same on every rank:
+ *   1. prism_b200_reduce_u32: total of the chunk,
+ *   2. prism_b200_scan_publish_total: stores {epoch, total} into slot (epoch & 1) * world + rank of
+ *      EVERY rank's array; peer_slots is a device array of the world base addresses,
+ *   3. prism_b200_scan_seeded_peers: scans the chunk; the first tile waits (bounded, 1 s) until all
+ *      world words of this epoch have arrived in its own array and starts from the sum of the lower
+ *      ranks' totals.
+ * Waiting for every rank's word, together with the two alternating halves of the array, is what
+ * makes it safe for a rank to run a whole call ahead of another.  world <= 32.  No counterpart in
+ * the reference.
+ */
+int prism_b200_scan_publish_total(const uint32_t* total, uint64_t* const* peer_slots, int world,
+                                  int rank, uint32_t epoch, void* stream);
+int prism_b200_scan_seeded_peers(size_t n, uint32_t* x, void* workspace, const uint64_t* slots,
+                                 int rank, int world, uint32_t epoch, void* stream);
+
+/*
  * Scan without caller-provided scratch and without any allocation.  No
  * counterpart in the reference (its launcher always takes a workspace,
  * evals/4090_scan/main.cu:68-86).

@@ -25,6 +25,7 @@ from ._lib import PrismB200Error, last_error, load  # noqa: F401
 __all__ = [
     "run_my_kernel", "get_workspace_size", "launch_scan", "runmyh100",
     "sgemm", "scan_", "scan_static_", "scan_workspace", "gemm_bf16", "reduce_u32", "scan_seeded_", "scan_add_carry_",
+    "scan_publish_total", "scan_seeded_peers_",
     "launch_count", "last_error", "clear_error", "version", "PrismB200Error",
 ]
 
@@ -150,6 +151,32 @@ def scan_seeded_(x: torch.Tensor, workspace: torch.Tensor, totals: torch.Tensor,
     with torch.cuda.device(x.device):
         _lib.check(load().prism_b200_scan_seeded(x.numel(), x.data_ptr(), workspace.data_ptr(), totals.data_ptr(),
                                                  int(rank), _stream(x)))
+    return x
+
+
+def scan_publish_total(total: torch.Tensor, peer_slots_dev: int, world: int, rank: int, epoch: int) -> None:
+    """Store {epoch, total[0]} into every rank's slot array.  `peer_slots_dev` is the device address of an
+    array of `world` base addresses (e.g. `buffer_ptrs_dev` of a torch symmetric-memory handle)."""
+    _require_cuda("total", total, _SCAN_DTYPES)
+    with torch.cuda.device(total.device):
+        _lib.check(load().prism_b200_scan_publish_total(total.data_ptr(), ctypes.c_void_p(int(peer_slots_dev)),
+                                                        int(world), int(rank), int(epoch), _stream(total)))
+
+
+def scan_seeded_peers_(x: torch.Tensor, workspace: torch.Tensor, slots: torch.Tensor, rank: int, world: int,
+                       epoch: int) -> torch.Tensor:
+    """Scan a shard in place; its first tile waits for all ranks' {epoch, total} words in `slots`
+    (2 * world int64 words in this GPU's memory, written by the peers) and starts from the lower ranks' sum."""
+    _require_cuda("x", x, _SCAN_DTYPES)
+    _require_cuda("workspace", workspace)
+    _require_cuda("slots", slots, torch.int64)
+    if slots.numel() < 2 * world:
+        raise ValueError("slots must hold 2 * world words")
+    if workspace.numel() * workspace.element_size() < get_workspace_size(x.numel()):
+        raise ValueError("workspace too small; see get_workspace_size(n)")
+    with torch.cuda.device(x.device):
+        _lib.check(load().prism_b200_scan_seeded_peers(x.numel(), x.data_ptr(), workspace.data_ptr(), slots.data_ptr(),
+                                                       int(rank), int(world), int(epoch), _stream(x)))
     return x
 
 

@@ -36,6 +36,8 @@ SIGNATURES = {
     "prism_b200_reduce_u32": (c_int, [c_size_t, c_void_p, c_void_p, c_void_p]),
     "prism_b200_scan_seeded": (c_int, [c_size_t, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
     "prism_b200_scan_add_carry": (c_int, [c_size_t, c_void_p, c_void_p, c_int, c_void_p]),
+    "prism_b200_scan_publish_total": (c_int, [c_void_p, c_void_p, c_int, c_int, ctypes.c_uint32, c_void_p]),
+    "prism_b200_scan_seeded_peers": (c_int, [c_size_t, c_void_p, c_void_p, c_void_p, c_int, c_int, ctypes.c_uint32, c_void_p]),
     "prism_b200_scan_static": (c_int, [c_size_t, c_void_p, c_void_p]),
     "prism_b200_gemm_bf16": (c_int, [c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
 }

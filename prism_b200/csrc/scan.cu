@@ -132,9 +132,23 @@ __device__ __forceinline__ uint32_t lookback(uint32_t tile, const uint64_t* desc
     }
 }
 
-template <bool SEEDED>
+// Where tile 0's exclusive prefix comes from.
+//   kSeedNone    0
+//   kSeedTotals  totals[0] + ... + totals[rank-1], an array in this GPU's memory (filled by an all-gather)
+//   kSeedPeers   the same sum, but each total arrives as a {epoch, total} word that the owning rank stores
+//                straight into this GPU's memory over NVLink; the look-back warp waits (bounded) until every
+//                rank's word carries this call's epoch
+enum { kSeedNone = 0, kSeedTotals = 1, kSeedPeers = 2 };
+
+__device__ __forceinline__ uint64_t ld_sys_u64(const uint64_t* p) {
+    uint64_t v;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+
+template <int SEED>
 __device__ __forceinline__ void scan_body(uint32_t n, uint32_t* x, uint32_t* header, uint64_t* desc,
-                                          const uint32_t* totals, int rank) {
+                                          const void* seed_src, int rank, int world, uint32_t epoch) {
     constexpr int S = kSlots;
     extern __shared__ __align__(128) unsigned char p_smem[];
     uint32_t* slots = reinterpret_cast<uint32_t*>(p_smem);
@@ -220,8 +234,26 @@ __device__ __forceinline__ void scan_body(uint32_t n, uint32_t* x, uint32_t* hea
             uint32_t exclusive = 0;
             bool failed = false;
             if (t == 0) {
-                if (SEEDED)
+                if (SEED == kSeedTotals) {
+                    const uint32_t* totals = static_cast<const uint32_t*>(seed_src);
                     for (int r = 0; r < rank; ++r) exclusive += totals[r];
+                } else if (SEED == kSeedPeers) {
+                    // Lane r waits for rank r's word of this epoch (every rank's, not only the lower
+                    // ones: that is what keeps a fast rank from overwriting a word nobody has read yet).
+                    const uint64_t* slots = static_cast<const uint64_t*>(seed_src) + (epoch & 1u) * world;
+                    uint64_t w = static_cast<uint64_t>(epoch);
+                    if (lane < world) {
+                        const unsigned long long t0 = global_timer_ns();
+                        w = ld_sys_u64(slots + lane);
+                        for (uint32_t spin = 1; static_cast<uint32_t>(w) != epoch; ++spin) {
+                            if ((spin & 63u) == 0u && (*abort_flag || global_timer_ns() - t0 > kWaitLimitNs)) break;
+                            __nanosleep(100);
+                            w = ld_sys_u64(slots + lane);
+                        }
+                    }
+                    failed = !__all_sync(0xffffffffu, static_cast<uint32_t>(w) == epoch);
+                    exclusive = warp_sum(lane < rank ? static_cast<uint32_t>(w >> 32) : 0u);
+                }
             } else {
                 exclusive = lookback(t, desc, header + 1, &failed);
             }
@@ -386,14 +418,33 @@ __device__ __forceinline__ void scan_body(uint32_t n, uint32_t* x, uint32_t* hea
 // counter word is followed by an abort flag and a record is one 64-bit word.
 __global__ void __launch_bounds__(kThreads, 3)
 scan_kernel(uint32_t n, uint32_t* x, uint32_t* block_idx_counter, int* block_infos) {
-    scan_body<false>(n, x, block_idx_counter, reinterpret_cast<uint64_t*>(block_infos), nullptr, 0);
+    scan_body<kSeedNone>(n, x, block_idx_counter, reinterpret_cast<uint64_t*>(block_infos), nullptr, 0, 1, 0);
 }
 
 // Sharded form: tile 0 starts from totals[0] + ... + totals[rank-1].
 __global__ void __launch_bounds__(kThreads, 3)
 scan_kernel_seeded(uint32_t n, uint32_t* x, uint32_t* block_idx_counter, int* block_infos, const uint32_t* totals,
                    int rank) {
-    scan_body<true>(n, x, block_idx_counter, reinterpret_cast<uint64_t*>(block_infos), totals, rank);
+    scan_body<kSeedTotals>(n, x, block_idx_counter, reinterpret_cast<uint64_t*>(block_infos), totals, rank, 1, 0);
+}
+
+// Sharded form without a collective call: the totals arrive as {epoch, total} words stored by the peers.
+__global__ void __launch_bounds__(kThreads, 3)
+scan_kernel_seeded_peers(uint32_t n, uint32_t* x, uint32_t* block_idx_counter, int* block_infos,
+                         const uint64_t* slots, int rank, int world, uint32_t epoch) {
+    scan_body<kSeedPeers>(n, x, block_idx_counter, reinterpret_cast<uint64_t*>(block_infos), slots, rank, world, epoch);
+}
+
+// Stores this rank's {epoch, total} word into every rank's slot array (its own included) with one
+// 64-bit system-scope store each: lane p writes to rank p's memory over NVLink.
+__global__ void publish_total_kernel(const uint32_t* total, uint64_t* const* peer_slots, int world, int rank,
+                                     uint32_t epoch) {
+    const int p = threadIdx.x;
+    if (p < world) {
+        const uint64_t w = static_cast<uint64_t>(epoch) | (static_cast<uint64_t>(*total) << 32);
+        uint64_t* dst = peer_slots[p] + (epoch & 1u) * world + rank;
+        asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(dst), "l"(w) : "memory");
+    }
 }
 
 __global__ void __launch_bounds__(256) reduce_u32_kernel(size_t n, const uint32_t* x, uint32_t* total) {
@@ -403,15 +454,17 @@ __global__ void __launch_bounds__(256) reduce_u32_kernel(size_t n, const uint32_
     const uint4* x4 = reinterpret_cast<const uint4*>(x);
     const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
     size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-    // Four independent 16-byte loads in flight per thread.
+    // The array is walked from its end to its start, so that what is still in L2 when the scan pass
+    // begins is the part the scan reads first.  Four independent 16-byte loads in flight per thread.
+    const uint4* top = x4 + (n4 - 1);
     for (; i + 3 * stride < n4; i += 4 * stride) {
-        const uint4 a = __ldcg(x4 + i), b = __ldcg(x4 + i + stride), c = __ldcg(x4 + i + 2 * stride),
-                    d = __ldcg(x4 + i + 3 * stride);
+        const uint4 a = __ldcg(top - i), b = __ldcg(top - (i + stride)), c = __ldcg(top - (i + 2 * stride)),
+                    d = __ldcg(top - (i + 3 * stride));
         acc += (a.x + a.y) + (a.z + a.w) + (b.x + b.y) + (b.z + b.w) + (c.x + c.y) + (c.z + c.w) + (d.x + d.y) +
                (d.z + d.w);
     }
     for (; i < n4; i += stride) {
-        const uint4 a = __ldcg(x4 + i);
+        const uint4 a = __ldcg(top - i);
         acc += (a.x + a.y) + (a.z + a.w);
     }
     if (blockIdx.x == 0 && threadIdx.x < (n & 3)) acc += x[n4 * 4 + threadIdx.x];
@@ -460,6 +513,8 @@ int persistent_grid(unsigned* out) {
                                         static_cast<int>(kSmemBytes)));
     PRISM_CUDA_TRY(cudaFuncSetAttribute(scan_kernel_seeded, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         static_cast<int>(kSmemBytes)));
+    PRISM_CUDA_TRY(cudaFuncSetAttribute(scan_kernel_seeded_peers, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        static_cast<int>(kSmemBytes)));
     PRISM_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, scan_kernel, kThreads, kSmemBytes));
     if (per_sm < 1 || sms < 1) return set_error(PRISM_B200_ERR_CUDA, "scan: the kernel does not fit on an SM");
     *out = static_cast<unsigned>(sms * per_sm);
@@ -469,8 +524,8 @@ int persistent_grid(unsigned* out) {
 
 // Re-arms the scratch (ticket, abort flag, every record: one memset where the reference
 // issues two, evals/4090_scan/main.cu:81-82) and launches the kernel.
-int scan_enqueue(size_t n, uint32_t* x, void* scratch, const uint32_t* totals, int rank, bool seeded,
-                 cudaStream_t stream) {
+int scan_enqueue(size_t n, uint32_t* x, void* scratch, const void* seed_src, int rank, int seed_mode,
+                 cudaStream_t stream, int world = 1, uint32_t epoch = 0) {
     const uint32_t tiles = static_cast<uint32_t>(scan_tiles(n));
     uint32_t* header = static_cast<uint32_t*>(scratch);
     uint64_t* desc = reinterpret_cast<uint64_t*>(static_cast<char*>(scratch) + kHeaderBytes);
@@ -478,9 +533,14 @@ int scan_enqueue(size_t n, uint32_t* x, void* scratch, const uint32_t* totals, i
     if (int rc = persistent_grid(&grid)) return rc;
     if (grid > tiles) grid = tiles;
     PRISM_CUDA_TRY(cudaMemsetAsync(scratch, 0, kHeaderBytes + static_cast<size_t>(tiles) * sizeof(uint64_t), stream));
-    if (seeded)
+    if (seed_mode == kSeedPeers)
+        scan_kernel_seeded_peers<<<grid, kThreads, kSmemBytes, stream>>>(
+            static_cast<uint32_t>(n), x, header, reinterpret_cast<int*>(desc), static_cast<const uint64_t*>(seed_src),
+            rank, world, epoch);
+    else if (seed_mode == kSeedTotals)
         scan_kernel_seeded<<<grid, kThreads, kSmemBytes, stream>>>(static_cast<uint32_t>(n), x, header,
-                                                                   reinterpret_cast<int*>(desc), totals, rank);
+                                                                   reinterpret_cast<int*>(desc),
+                                                                   static_cast<const uint32_t*>(seed_src), rank);
     else
         scan_kernel<<<grid, kThreads, kSmemBytes, stream>>>(static_cast<uint32_t>(n), x, header,
                                                             reinterpret_cast<int*>(desc));
@@ -489,18 +549,20 @@ int scan_enqueue(size_t n, uint32_t* x, void* scratch, const uint32_t* totals, i
     return PRISM_B200_OK;
 }
 
-int scan_launch(size_t n, uint32_t* x, void* workspace, const uint32_t* totals, int rank, bool seeded,
-                cudaStream_t stream) {
+int scan_launch(size_t n, uint32_t* x, void* workspace, const void* seed_src, int rank, int seed_mode,
+                cudaStream_t stream, int world = 1, uint32_t epoch = 0) {
     if (n == 0) return PRISM_B200_OK;
     if (!x || !workspace) return set_error(PRISM_B200_ERR_INVALID_ARGUMENT, "scan: null pointer");
     if (n >= (1ull << 32)) return set_error(PRISM_B200_ERR_TOO_LARGE, "scan: n=%zu must be below 2^32", n);
     if (reinterpret_cast<uintptr_t>(x) & 15u) return set_error(PRISM_B200_ERR_MISALIGNED, "scan: x not 16-byte aligned");
     if (reinterpret_cast<uintptr_t>(workspace) & 15u)
         return set_error(PRISM_B200_ERR_MISALIGNED, "scan: workspace not 16-byte aligned");
-    if (seeded && (rank < 0 || (rank > 0 && !totals)))
+    if (seed_mode == kSeedTotals && (rank < 0 || (rank > 0 && !seed_src)))
         return set_error(PRISM_B200_ERR_INVALID_ARGUMENT, "scan_seeded: bad rank/totals");
+    if (seed_mode == kSeedPeers && (!seed_src || world < 1 || world > 32 || rank < 0 || rank >= world || epoch == 0))
+        return set_error(PRISM_B200_ERR_INVALID_ARGUMENT, "scan_seeded_peers: need slots, 1 <= world <= 32, a rank below world and a non-zero epoch");
     if (int rc = bind_status_word()) return rc;
-    return scan_enqueue(n, x, workspace, totals, rank, seeded, stream);
+    return scan_enqueue(n, x, workspace, seed_src, rank, seed_mode, stream, world, epoch);
 }
 
 unsigned streaming_grid(size_t n4) {
@@ -576,7 +638,7 @@ extern "C" int prism_b200_scan_static(size_t n, uint32_t* x, void* stream) {
     if (int rc = static_scratch_address(&scratch)) return rc;
     // The array still holds the previous call's ticket, abort flag and records; scan_enqueue clears
     // what this call will use.  It does not set up the pinned status word (that would allocate).
-    return scan_enqueue(n, x, scratch, nullptr, 0, false, static_cast<cudaStream_t>(stream));
+    return scan_enqueue(n, x, scratch, nullptr, 0, kSeedNone, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int prism_b200_scan_workspace_size(size_t n, size_t* bytes) {
@@ -587,12 +649,27 @@ extern "C" int prism_b200_scan_workspace_size(size_t n, size_t* bytes) {
 }
 
 extern "C" int prism_b200_scan(size_t n, uint32_t* x, void* workspace, void* stream) {
-    return scan_launch(n, x, workspace, nullptr, 0, false, static_cast<cudaStream_t>(stream));
+    return scan_launch(n, x, workspace, nullptr, 0, kSeedNone, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int prism_b200_scan_seeded(size_t n, uint32_t* x, void* workspace, const uint32_t* totals, int rank,
                                       void* stream) {
-    return scan_launch(n, x, workspace, totals, rank, true, static_cast<cudaStream_t>(stream));
+    return scan_launch(n, x, workspace, totals, rank, kSeedTotals, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int prism_b200_scan_publish_total(const uint32_t* total, uint64_t* const* peer_slots, int world, int rank,
+                                             uint32_t epoch, void* stream) {
+    if (!total || !peer_slots || world < 1 || world > 32 || rank < 0 || rank >= world || epoch == 0)
+        return set_error(PRISM_B200_ERR_INVALID_ARGUMENT, "scan_publish_total: bad argument");
+    publish_total_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(total, peer_slots, world, rank, epoch);
+    PRISM_CUDA_TRY(cudaGetLastError());
+    count_launch();
+    return PRISM_B200_OK;
+}
+
+extern "C" int prism_b200_scan_seeded_peers(size_t n, uint32_t* x, void* workspace, const uint64_t* slots, int rank,
+                                            int world, uint32_t epoch, void* stream) {
+    return scan_launch(n, x, workspace, slots, rank, kSeedPeers, static_cast<cudaStream_t>(stream), world, epoch);
 }
 
 extern "C" int prism_b200_reduce_u32(size_t n, const uint32_t* x, uint32_t* total, void* stream) {

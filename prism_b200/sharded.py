@@ -3,14 +3,18 @@
 * GEMM (fp32 and bf16): rows of M are independent given all of B.  Rank r owns
   rows [r * M / g, (r + 1) * M / g) of A and of C; B is replicated.  There is no
   collective on the data path.
-* scan: rank r owns the r-th contiguous chunk.  The only exchange is one
-  all-gather of one uint32 total per rank.  Two schedules are offered:
-    "reduce_then_scan"  (default) total of the chunk (4 B/element read), all-gather,
-                        then ONE scan pass whose first tile starts from the sum of the
-                        lower ranks' totals (8 B/element): 12 B/element per rank;
+* scan: rank r owns the r-th contiguous chunk.  The only exchange is one uint32
+  total per rank.  Three schedules are offered:
+    "peer_words"        total of the chunk (4 B/element read); the total is stored as an
+                        {epoch, total} word straight into every rank's memory over NVLink
+                        (symmetric memory, no collective call, no host involvement); ONE scan
+                        pass whose first tile waits for the words and starts from the sum of
+                        the lower ranks' totals (8 B/element): 12 B/element per rank.  Default
+                        on CUDA with more than one rank.
+    "reduce_then_scan"  the same with an NCCL all-gather of the totals between the passes.
     "scan_then_carry"   local scan (8 B/element), all-gather of the last elements,
                         carry-add pass (8 B/element): 16 B/element per rank.
-  Both produce the scan of the concatenated array, bit for bit.
+  All produce the scan of the concatenated array, bit for bit.
 
 The reference has no multi-GPU code; its scan harness works on one device
 (evals/4090_scan/main.cu:96-128).
@@ -65,24 +69,49 @@ class _CudaOps:
     def scan_add_carry_(self, x, totals, rank):
         self._pb.scan_add_carry_(x, totals, rank)
 
+    def publish_total(self, total, peer_slots_dev, world, rank, epoch):
+        self._pb.scan_publish_total(total, peer_slots_dev, world, rank, epoch)
+
+    def scan_seeded_peers_(self, x, workspace, slots, rank, world, epoch):
+        self._pb.scan_seeded_peers_(x, workspace, slots, rank, world, epoch)
+
 
 class ShardedScan:
     """In-place inclusive scan of an array cut into one contiguous chunk per rank."""
 
-    SCHEDULES = ("reduce_then_scan", "scan_then_carry")
+    SCHEDULES = ("reduce_then_scan", "scan_then_carry")       # run anywhere a process group runs
+    PEER_SCHEDULE = "peer_words"                               # needs CUDA peer access (one node)
 
-    def __init__(self, n_local: int, device, group: Any = None, schedule: str = "reduce_then_scan", ops: Any = None):
-        if schedule not in self.SCHEDULES:
-            raise ValueError(f"schedule must be one of {self.SCHEDULES}")
+    def __init__(self, n_local: int, device, group: Any = None, schedule: str | None = None, ops: Any = None):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        on_cuda = torch.device(device).type == "cuda"
+        if schedule is None:
+            schedule = self.PEER_SCHEDULE if (on_cuda and self.world > 1 and ops is None) else "reduce_then_scan"
+        if schedule not in self.SCHEDULES + (self.PEER_SCHEDULE,):
+            raise ValueError(f"schedule must be one of {self.SCHEDULES + (self.PEER_SCHEDULE,)}")
+        if schedule == self.PEER_SCHEDULE and (self.world > 32 or not on_cuda):
+            raise ValueError("the peer_words schedule needs CUDA devices and at most 32 ranks")
         self.schedule = schedule
+        self.epoch = 0
+        self.slots = None
+        self.peer_slots_dev = 0
         self.ops = ops if ops is not None else _CudaOps()
         self.n_local = n_local
         self.workspace = self.ops.workspace(n_local, device)
         self.total = torch.zeros(1, dtype=torch.int32, device=device)
         self.totals = torch.zeros(self.world, dtype=torch.int32, device=device)
+        if self.schedule == self.PEER_SCHEDULE and self.world > 1:
+            # 2 * world words per rank, writable by every rank: torch's symmetric memory gives each
+            # rank the device addresses of all the peers' buffers.
+            import torch.distributed._symmetric_memory as symm
+            self.slots = symm.empty(2 * self.world, dtype=torch.int64, device=device)
+            self.slots.zero_()
+            self._symm = symm.rendezvous(self.slots, group if group is not None else dist.group.WORLD)
+            self.peer_slots_dev = int(self._symm.buffer_ptrs_dev)
+            torch.cuda.synchronize(device)
+            dist.barrier(group)   # every rank's words are zero before anyone publishes
 
     def _exchange(self, total: torch.Tensor) -> None:
         if self.world == 1:
@@ -93,7 +122,12 @@ class ShardedScan:
     def __call__(self, x_local: torch.Tensor) -> torch.Tensor:
         if x_local.numel() != self.n_local:
             raise ValueError(f"shard has {x_local.numel()} elements, planned for {self.n_local}")
-        if self.schedule == "reduce_then_scan":
+        if self.schedule == self.PEER_SCHEDULE and self.world > 1:
+            self.epoch += 1
+            self.ops.reduce_u32(x_local, self.total)
+            self.ops.publish_total(self.total, self.peer_slots_dev, self.world, self.rank, self.epoch)
+            self.ops.scan_seeded_peers_(x_local, self.workspace, self.slots, self.rank, self.world, self.epoch)
+        elif self.schedule in ("reduce_then_scan", self.PEER_SCHEDULE):
             if self.world > 1:
                 self.ops.reduce_u32(x_local, self.total)
                 self._exchange(self.total)
@@ -108,7 +142,10 @@ class ShardedScan:
         return x_local
 
     def totals_int64(self) -> list[int]:
-        """Per-rank totals as non-negative Python ints (for the host-side overflow check)."""
+        """Per-rank totals of the last call as non-negative Python ints (for the host-side overflow check)."""
+        if self.slots is not None and self.epoch > 0:
+            half = self.slots.cpu().tolist()[(self.epoch & 1) * self.world:][: self.world]
+            return [(int(w) >> 32) & 0xFFFFFFFF for w in half]
         return [int(v) & 0xFFFFFFFF for v in self.totals.cpu().tolist()]
 
 

@@ -30,13 +30,15 @@ n = (1 << 22) + 12345
 full = O.scan_inputs(n, seed=5, high=1 << 20)
 expect = O.scan_cpu(full)
 lo, hi = sharded.chunk_bounds(n, world, rank)
-for schedule in sharded.ShardedScan.SCHEDULES:
-    x = torch.from_numpy(full[lo:hi].view(np.int32).copy()).to(dev)
+for schedule in (sharded.ShardedScan.PEER_SCHEDULE,) + sharded.ShardedScan.SCHEDULES:
     scan = sharded.ShardedScan(hi - lo, dev, schedule=schedule)
-    scan(x)
-    torch.cuda.synchronize()
-    assert np.array_equal(x.cpu().numpy().view(np.uint32), expect[lo:hi]), (schedule, rank)
-    assert sum(scan.totals_int64()) & 0xFFFFFFFF == int(expect[-1])
+    for rep in range(3):   # repeated calls: epochs alternate between the two halves of the slot array
+        x = torch.from_numpy(full[lo:hi].view(np.int32).copy()).to(dev)
+        scan(x)
+        torch.cuda.synchronize()
+        assert np.array_equal(x.cpu().numpy().view(np.uint32), expect[lo:hi]), (schedule, rank, rep)
+        assert sum(scan.totals_int64()) & 0xFFFFFFFF == int(expect[-1]), (schedule, rank, rep)
+assert sharded.ShardedScan(hi - lo, dev).schedule == "peer_words"
 
 # bf16 GEMM: rows of M sharded, B replicated, no collective
 M, N, K = 256 * world, 512, 256

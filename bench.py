@@ -40,11 +40,11 @@ SCAN_N1 = 1 << 28
 SCAN_NG = 1 << 30
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel,
-# from the ncu captures summarised under profiles/ (None = not captured).
+# from the ncu captures whose summaries sit in the profiles/ folder (None = not captured).
 NCU_TRAFFIC_BYTES = {
-    "gemm_bf16": 969.7e6,   # 8192^3: 849.7 MB read + 119.9 MB written      (profiles/gemm_bf16_pair_wide_8192.md)
-    "sgemm": 563.8e6,       # 4096^3: 505.7 MB read + 58.1 MB written        (profiles/sgemm_kernel5_4096.md)
-    "scan": 1913.6e6,       # 2^28: 4 x the 478.4 MB captured at 2^26        (profiles/scan_kernel_2p26.md)
+    "gemm_bf16": 969.7e6,   # 8192^3: 849.7 MB read + 119.9 MB written
+    "sgemm": 563.8e6,       # 4096^3: 505.7 MB read + 58.1 MB written
+    "scan": 1913.6e6,       # 2^28: 4 x the 478.4 MB captured at 2^26
 }
 
 

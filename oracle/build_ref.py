@@ -24,7 +24,8 @@ from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
 REF_OUT = HERE / "_ref"
-DEFAULT_REFERENCE = os.environ.get("PRISM_REFERENCE", "/root/reference")
+# Root of a checkout of manya-bansal/prism; set PRISM_REFERENCE to point elsewhere.
+DEFAULT_REFERENCE = os.environ.get("PRISM_REFERENCE", str(HERE.parent.parent / "reference"))
 
 
 def _run(cmd: list[str]) -> None:

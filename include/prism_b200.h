@@ -157,7 +157,7 @@ int prism_b200_scan_seeded_peers(size_t n, uint32_t* x, void* workspace, const u
  * that only ever see buffers owned by their host application, loops that may
  * not block on the allocator, processes whose device memory is already all
  * handed out.  Same result as prism_b200_scan, in place, but the look-back
- * records live in a fixed 524,416-byte array inside the library's device image
+ * records live in a fixed 2,097,280-byte array inside the library's device image
  * (every GPU that loads the library holds it until exit), which bounds n:
  *   n <= 2^28 elements; larger n returns PRISM_B200_ERR_TOO_LARGE.
  * The call performs no cudaMalloc/cudaFree and calls no allocating routine.

@@ -21,13 +21,13 @@
 //                   (serial over 4 elements, four independent 5-step warp-shuffle
 //                   scans per lane, one 8-entry hand-off between warps), scanned
 //                   values back into the slot, tile aggregate published;
-//                   phase B, up to LAG tiles later: slot -> registers, add the
+//                   phase B, once the tile's prefix is known: slot -> registers, add the
 //                   exclusive prefix, 16-byte stores to global memory, slot released;
 //   look-back warp  resolves the exclusive prefix of the CTA's tiles in order, 32
 //                   predecessor records per probe, and publishes inclusive prefixes.
 // Between A and B a tile costs only shared memory, so loads keep flowing.
 //
-// A tile publishes ONE 64-bit record {state, value}; state says whether value is
+// A tile publishes ONE 64-bit record {state, value}, alone in a 32-byte sector; state says whether value is
 // the tile's own aggregate or its inclusive prefix.  Flag and value travel in one
 // relaxed 64-bit store, so they cannot tear and no fence is needed (the reference
 // packs the same way in BlockInfo, evals/4090_scan/main.cu:21-37, but keeps two
@@ -50,19 +50,22 @@ constexpr uint32_t kStateAggregate = 1u;
 constexpr uint32_t kStatePrefix = 2u;
 constexpr uint32_t kMaxPolls = 1u << 20;
 constexpr size_t kHeaderBytes = 128;  // [0] ticket, [1] abort flag; the records follow
+// 64-bit words between consecutive tiles' records: one 32-byte sector per record.  Packed records
+// (16 to a 128-byte line) cost 11 % of the throughput: up to 32 look-back warps poll each record
+// and the polls of neighbouring records then queue on the same sector.
+constexpr int kRecStride = 4;
 
 constexpr int kScanThreads = 256;               // 8 scan warps
-constexpr int kThreads = kScanThreads + 64;     // + producer warp + look-back warp
+constexpr int kLookbackWarps = 1;               // warp q resolves ring items q, q + kLookbackWarps, ... (more measured slower)
+constexpr int kThreads = kScanThreads + 32 + 32 * kLookbackWarps;  // + producer warp + look-back warps
 constexpr int kVecs = 4;                        // 16-byte vectors per lane
 constexpr int kTile = kScanThreads * 4 * kVecs; // 4096 elements = 16 KB
 constexpr int kWarpElems = 128 * kVecs;         // contiguous elements per scan warp
-constexpr int kSlots = 4;                       // ring depth: 3 CTAs of 64 KB per SM
-constexpr int kLag = 3;                         // tiles parked between phase A and phase B
+constexpr int kSlots = 4;                       // ring depth: 3 CTAs of 64 KB per SM (3, 5 and 6 measured slower)
 constexpr uint32_t kSentinel = 0xFFFFFFFFu;
-static_assert(kLag >= 1 && kLag <= kSlots - 1, "one slot must always be free for the producer");
 
 constexpr size_t kSlotBytes = static_cast<size_t>(kTile) * 4;
-constexpr size_t kSmemBytes = kSlots * kSlotBytes + 4 * kSlots * 8 /* barriers */ + 3 * kSlots * 4 + 2 * 8 * 4 + 32;
+constexpr size_t kSmemBytes = kSlots * kSlotBytes + 4 * kSlots * 8 /* barriers */ + 3 * kSlots * 4 + 2 * 8 * 4 + 48;
 
 __device__ __forceinline__ uint64_t ld_desc(const uint64_t* p) {
     uint64_t v;
@@ -92,6 +95,16 @@ __device__ __forceinline__ void bulk_load_tile(void* dst_smem, const void* src, 
                  : "memory");
 }
 
+// TUNING ONLY (-DPRISM_SCAN_TRACE): per-tile timestamps of the pipeline stages.
+#ifdef PRISM_SCAN_TRACE
+__device__ unsigned long long g_trace[8 * 65536];
+#define PRISM_TRACE(tile, k) do { if ((tile) < 65536u) g_trace[8 * (tile) + (k)] = global_timer_ns(); } while (0)
+#define PRISM_TRACE_VAL(tile, k, v) do { if ((tile) < 65536u) g_trace[8 * (tile) + (k)] = (v); } while (0)
+#else
+#define PRISM_TRACE(tile, k) do { } while (0)
+#define PRISM_TRACE_VAL(tile, k, v) do { } while (0)
+#endif
+
 // Sum of the tiles before `tile`, found by walking the records backwards 32 at a
 // time until one that already carries an inclusive prefix (the job of the reference's
 // lookback_to_prev_blocks, generated/lookback_to_prev_blocks.cu:8-25, done by a warp
@@ -103,16 +116,23 @@ __device__ __forceinline__ uint32_t lookback(uint32_t tile, const uint64_t* desc
     uint32_t exclusive = 0;
     long long idx = static_cast<long long>(tile) - 1 - lane;
     *failed = false;
+#ifdef PRISM_SCAN_TRACE
+    unsigned long long rounds = 0;
+#endif
     while (true) {
+#ifdef PRISM_SCAN_TRACE
+        ++rounds;
+        if (lane == 0) PRISM_TRACE_VAL(tile, 6, rounds);
+#endif
         // A slot before tile 0 behaves like a finished tile with prefix 0.
         uint64_t d = kStatePrefix;
         if (idx >= 0) {
             uint32_t polls = 0;
-            d = ld_desc(desc + idx);
+            d = ld_desc(desc + idx * kRecStride);
             while (static_cast<uint32_t>(d) == kStateInvalid) {
                 if (++polls >= kMaxPolls) break;
                 if ((polls & 1023u) == 0u && ld_flag(abort_flag) != 0u) break;
-                d = ld_desc(desc + idx);
+                d = ld_desc(desc + idx * kRecStride);
             }
         }
         const uint32_t state = static_cast<uint32_t>(d);
@@ -162,6 +182,7 @@ __device__ __forceinline__ void scan_body(uint32_t n, uint32_t* x, uint32_t* hea
     uint32_t* s_warp_total = s_excl + S;  // [2][8]
     volatile uint32_t* abort_flag = s_warp_total + 16;
     volatile uint32_t* s_ctrl = s_warp_total + 17;  // [2]: outcome of thread 0's bounded wait, double-buffered
+    volatile uint32_t* s_end_item = s_warp_total + 19;  // ring item that carried the end-of-work mark
 
     const int tid = threadIdx.x;
     const int lane = tid & 31;
@@ -176,6 +197,7 @@ __device__ __forceinline__ void scan_body(uint32_t n, uint32_t* x, uint32_t* hea
             mbar_init(&empty_bar[s], kScanThreads / 32);
         }
         *abort_flag = 0;
+        *s_end_item = 0xFFFFFFFFu;
         fence_barrier_init();
     }
     __syncthreads();
@@ -200,6 +222,7 @@ __device__ __forceinline__ void scan_body(uint32_t n, uint32_t* x, uint32_t* hea
                     break;
                 }
                 s_tile[s] = t;
+                PRISM_TRACE(t, 0);   // ticket drawn, load issued
                 const unsigned long long base = static_cast<unsigned long long>(t) * kTile;
                 const unsigned long long left = n - base;
                 const uint32_t cnt = left < kTile ? static_cast<uint32_t>(left) : kTile;
@@ -215,9 +238,10 @@ __device__ __forceinline__ void scan_body(uint32_t n, uint32_t* x, uint32_t* hea
         return;
     }
 
-    if (warp == kScanThreads / 32 + 1) {
+    if (warp > kScanThreads / 32) {
         // ------------------------------ look-back ------------------------------
-        for (uint32_t k = 0;; ++k) {
+        static_assert(kLookbackWarps >= 1 && kLookbackWarps <= kSlots, "one look-back warp per slot at most");
+        for (uint32_t k = static_cast<uint32_t>(warp - kScanThreads / 32 - 1);; k += kLookbackWarps) {
             const int s = k % S;
             const bool ready = mbar_wait_bounded(&agg_bar[s], (k / S) & 1u, abort_flag);
             if (!__all_sync(0xffffffffu, ready)) {
@@ -228,11 +252,12 @@ __device__ __forceinline__ void scan_body(uint32_t n, uint32_t* x, uint32_t* hea
                 }
                 break;
             }
+            if (k >= *s_end_item) break;   // the work ended before this ring item
             const uint32_t t = s_tile[s];
-            if (t == kSentinel) break;
             const uint32_t agg = s_agg[s];
             uint32_t exclusive = 0;
             bool failed = false;
+            if (lane == 0) PRISM_TRACE(t, 3);   // look-back starts
             if (t == 0) {
                 if (SEED == kSeedTotals) {
                     const uint32_t* totals = static_cast<const uint32_t*>(seed_src);
@@ -263,7 +288,8 @@ __device__ __forceinline__ void scan_body(uint32_t n, uint32_t* x, uint32_t* hea
                     atomicExch(header + 1, 1u);
                     raise_device_status(DEV_SCAN_LOOKBACK_TIMEOUT);
                 }
-                st_desc(desc + t, kStatePrefix, exclusive + agg);  // as write_block_prefix.cu:8-10
+                st_desc(desc + static_cast<size_t>(t) * kRecStride, kStatePrefix, exclusive + agg);  // as write_block_prefix.cu:8-10
+                PRISM_TRACE(t, 4);   // prefix published
                 s_excl[s] = exclusive;
                 mbar_arrive(&pre_bar[s]);
             }
@@ -279,39 +305,59 @@ __device__ __forceinline__ void scan_body(uint32_t n, uint32_t* x, uint32_t* hea
     const int vec0 = warp * kWarpElems + lane * 4;
     uint32_t i = 0, j = 0;  // ring items taken through phase A / phase B so far
     bool drained = false;
-    // Only thread 0 performs the bounded wait; the outcome reaches the other 255 scan
-    // threads through a named barrier, so that all of them always take the same branch
-    // (a thread that gave up on its own would leave the others stuck at the next barrier).
-    uint32_t waits = 0;
-    auto wait_uniform = [&](uint64_t* bar, uint32_t parity) -> bool {
-        volatile uint32_t* c = s_ctrl + (waits++ & 1u);
+    // Scheduling.  Phase A (which publishes the aggregate that every later tile waits for) runs as
+    // soon as a slot has landed, however many tiles are parked; phase B runs when the oldest parked
+    // tile's prefix is there.  Only thread 0 watches the two barriers, with a time limit; what it
+    // decides reaches the other 255 scan threads through a named barrier, so that all of them always
+    // take the same branch (a thread that gave up on its own would leave the others stuck at the
+    // next barrier).  The decision word is double-buffered because thread 0 can be one barrier ahead.
+    uint32_t decisions = 0;
+    auto decide = [&]() -> uint32_t {   // 0 = give up, 1 = phase A, 2 = phase B, 3 = all done
+        volatile uint32_t* c = s_ctrl + (decisions++ & 1u);
         if (tid == 0) {
-            const bool got = mbar_wait_bounded(bar, parity, abort_flag);
-            if (!got) {
-                *abort_flag = 1;
-                atomicExch(header + 1, 1u);
-                raise_device_status(DEV_SCAN_LOOKBACK_TIMEOUT);
+            uint32_t what = 0;
+            const bool can_a = !drained && i - j < static_cast<uint32_t>(S);
+            const bool can_b = j < i;
+            if (!can_a && !can_b) {
+                what = 3;
+            } else {
+                const unsigned long long t0 = global_timer_ns();
+                for (uint32_t spin = 0;; ++spin) {
+                    if (can_a && mbar_try_wait(&full_bar[i % S], (i / S) & 1u)) { what = 1; break; }
+                    if (can_b && mbar_try_wait(&pre_bar[j % S], (j / S) & 1u)) { what = 2; break; }
+                    if ((spin & 63u) == 63u && (*abort_flag || global_timer_ns() - t0 > kWaitLimitNs)) break;
+                }
+                if (what == 0) {
+                    *abort_flag = 1;
+                    atomicExch(header + 1, 1u);
+                    raise_device_status(DEV_SCAN_LOOKBACK_TIMEOUT);
+                }
             }
-            *c = got ? 1u : 0u;
+            *c = what;
         }
         asm volatile("bar.sync 1, %0;" ::"n"(kScanThreads) : "memory");
-        const bool got = *c != 0u;
-        if (got) (void)mbar_try_wait(bar, parity);  // this thread's own acquire of the completed phase
-        return got;
+        return *c;
     };
 
     while (true) {
-        if (!drained && i - j < static_cast<uint32_t>(kLag)) {
+        const uint32_t what = decide();
+        if (what == 0 || what == 3) break;
+        if (what == 1) {
             // ---------------- phase A on ring item i ----------------
             const int s = i % S;
-            if (!wait_uniform(&full_bar[s], (i / S) & 1u)) break;
+            (void)mbar_try_wait(&full_bar[s], (i / S) & 1u);   // this thread's own acquire of the completed phase
             const uint32_t t = s_tile[s];
             if (t == kSentinel) {
                 drained = true;
-                if (tid == 0) mbar_arrive(&agg_bar[s]);  // hands the end mark on to the look-back warp
+                if (tid == 0) {
+                    // Wake every look-back warp at its next ring item and tell it that the work ended here.
+                    *s_end_item = i;
+                    for (int m = 0; m < kLookbackWarps; ++m) mbar_arrive(&agg_bar[(i + m) % S]);
+                }
                 continue;
             }
             uint32_t* slot = slots + s * kTile;
+            if (tid == 0) PRISM_TRACE(t, 1);   // phase A starts (data landed and scan warps free)
             const unsigned long long base = static_cast<unsigned long long>(t) * kTile;
             const unsigned long long left = n - base;
             const uint32_t cnt = left < kTile ? static_cast<uint32_t>(left) : kTile;
@@ -364,8 +410,9 @@ __device__ __forceinline__ void scan_body(uint32_t n, uint32_t* x, uint32_t* hea
                 aggregate += tot;
             }
             if (tid == 0) {
-                if (t != 0) st_desc(desc + t, kStateAggregate, aggregate);  // as write_block_aggregate.cu:8-10
+                if (t != 0) st_desc(desc + static_cast<size_t>(t) * kRecStride, kStateAggregate, aggregate);  // as write_block_aggregate.cu:8-10
                 s_agg[s] = aggregate;
+                PRISM_TRACE(t, 2);   // aggregate published
                 mbar_arrive(&agg_bar[s]);
             }
             // Tile-local inclusive scan back into the slot; the same lane reads it again in phase B.
@@ -376,11 +423,12 @@ __device__ __forceinline__ void scan_body(uint32_t n, uint32_t* x, uint32_t* hea
                 *reinterpret_cast<uint4*>(slot + vec0 + q * 128) = v[q];
             }
             ++i;
-        } else if (j < i) {
+        } else {
             // ---------------- phase B on ring item j (update_with_new_data_and_writeback.cu) ----------------
             const int s = j % S;
-            if (!wait_uniform(&pre_bar[s], (j / S) & 1u)) break;
+            (void)mbar_try_wait(&pre_bar[s], (j / S) & 1u);
             const uint32_t t = s_tile[s];
+            if (tid == 0) PRISM_TRACE(t, 5);   // phase B starts
             const uint32_t add = s_excl[s];
             const uint32_t* slot = slots + s * kTile;
             const unsigned long long base = static_cast<unsigned long long>(t) * kTile;
@@ -405,8 +453,6 @@ __device__ __forceinline__ void scan_body(uint32_t n, uint32_t* x, uint32_t* hea
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty_bar[s]);
             ++j;
-        } else {
-            break;  // drained and every tile written
         }
     }
 }
@@ -416,20 +462,22 @@ __device__ __forceinline__ void scan_body(uint32_t n, uint32_t* x, uint32_t* hea
 // Same parameter list as the reference entry point (generated/scan_kernel.cu:1):
 // n elements, data in place, the ticket counter, the per-tile records.  Here the
 // counter word is followed by an abort flag and a record is one 64-bit word.
-__global__ void __launch_bounds__(kThreads, 3)
+constexpr int kCtasPerSm = static_cast<int>((227 * 1024) / (kSmemBytes + 1024));
+
+__global__ void __launch_bounds__(kThreads, kCtasPerSm)
 scan_kernel(uint32_t n, uint32_t* x, uint32_t* block_idx_counter, int* block_infos) {
     scan_body<kSeedNone>(n, x, block_idx_counter, reinterpret_cast<uint64_t*>(block_infos), nullptr, 0, 1, 0);
 }
 
 // Sharded form: tile 0 starts from totals[0] + ... + totals[rank-1].
-__global__ void __launch_bounds__(kThreads, 3)
+__global__ void __launch_bounds__(kThreads, kCtasPerSm)
 scan_kernel_seeded(uint32_t n, uint32_t* x, uint32_t* block_idx_counter, int* block_infos, const uint32_t* totals,
                    int rank) {
     scan_body<kSeedTotals>(n, x, block_idx_counter, reinterpret_cast<uint64_t*>(block_infos), totals, rank, 1, 0);
 }
 
 // Sharded form without a collective call: the totals arrive as {epoch, total} words stored by the peers.
-__global__ void __launch_bounds__(kThreads, 3)
+__global__ void __launch_bounds__(kThreads, kCtasPerSm)
 scan_kernel_seeded_peers(uint32_t n, uint32_t* x, uint32_t* block_idx_counter, int* block_infos,
                          const uint64_t* slots, int rank, int world, uint32_t epoch) {
     scan_body<kSeedPeers>(n, x, block_idx_counter, reinterpret_cast<uint64_t*>(block_infos), slots, rank, world, epoch);
@@ -532,7 +580,7 @@ int scan_enqueue(size_t n, uint32_t* x, void* scratch, const void* seed_src, int
     unsigned grid = 0;
     if (int rc = persistent_grid(&grid)) return rc;
     if (grid > tiles) grid = tiles;
-    PRISM_CUDA_TRY(cudaMemsetAsync(scratch, 0, kHeaderBytes + static_cast<size_t>(tiles) * sizeof(uint64_t), stream));
+    PRISM_CUDA_TRY(cudaMemsetAsync(scratch, 0, kHeaderBytes + static_cast<size_t>(tiles) * kRecStride * sizeof(uint64_t), stream));
     if (seed_mode == kSeedPeers)
         scan_kernel_seeded_peers<<<grid, kThreads, kSmemBytes, stream>>>(
             static_cast<uint32_t>(n), x, header, reinterpret_cast<int*>(desc), static_cast<const uint64_t*>(seed_src),
@@ -592,7 +640,7 @@ using namespace prism_b200;
 namespace prism_b200 {
 namespace {
 constexpr size_t kStaticMaxN = 1ull << 28;  // elements (1 GiB of data)
-constexpr size_t kStaticScratchBytes = kHeaderBytes + (kStaticMaxN / kTile) * sizeof(uint64_t);  // 524,416 B
+constexpr size_t kStaticScratchBytes = kHeaderBytes + (kStaticMaxN / kTile) * kRecStride * sizeof(uint64_t);  // 2,097,280 B
 }  // namespace
 }  // namespace prism_b200
 
@@ -641,10 +689,16 @@ extern "C" int prism_b200_scan_static(size_t n, uint32_t* x, void* stream) {
     return scan_enqueue(n, x, scratch, nullptr, 0, kSeedNone, static_cast<cudaStream_t>(stream));
 }
 
+#ifdef PRISM_SCAN_TRACE
+extern "C" int prism_b200_scan_trace(unsigned long long* out) {
+    return cudaMemcpyFromSymbol(out, g_trace, sizeof(unsigned long long) * 8 * 65536) == cudaSuccess ? 0 : 4;
+}
+#endif
+
 extern "C" int prism_b200_scan_workspace_size(size_t n, size_t* bytes) {
     if (!bytes) return set_error(PRISM_B200_ERR_INVALID_ARGUMENT, "scan_workspace_size: null bytes");
     if (n >= (1ull << 32)) return set_error(PRISM_B200_ERR_TOO_LARGE, "scan: n=%zu must be below 2^32", n);
-    *bytes = kHeaderBytes + scan_tiles(n) * sizeof(uint64_t);
+    *bytes = kHeaderBytes + scan_tiles(n) * kRecStride * sizeof(uint64_t);
     return PRISM_B200_OK;
 }
 

@@ -49,8 +49,8 @@ def test_workspace_size_is_host_only_and_monotonic():
         assert lib.prism_b200_scan_workspace_size(n, ctypes.byref(out)) == 0
         sizes.append(out.value)
     assert sizes == sorted(sizes) and sizes[0] > 0
-    # one 8-byte record per 4096-element tile plus a 128-byte header
-    assert sizes[4] == 128 + ((1 << 24) // 4096) * 8
+    # one record (a 32-byte sector) per 4096-element tile plus a 128-byte header
+    assert sizes[4] == 128 + ((1 << 24) // 4096) * 32
 
 
 def test_argument_errors_are_reported_not_fatal():

@@ -42,9 +42,9 @@ SCAN_NG = 1 << 30
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel,
 # from the ncu captures whose summaries sit in the profiles/ folder (None = not captured).
 NCU_TRAFFIC_BYTES = {
-    "gemm_bf16": 969.7e6,   # 8192^3: 849.7 MB read + 119.9 MB written
-    "sgemm": 563.8e6,       # 4096^3: 505.7 MB read + 58.1 MB written
-    "scan": 1913.6e6,       # 2^28: 4 x the 478.4 MB captured at 2^26
+    "gemm_bf16": 970.5e6,   # 8192^3: 850.5 MB read + 120.0 MB written
+    "sgemm": 549.0e6,       # 4096^3: 491.9 MB read + 57.1 MB written
+    "scan": 1919.3e6,       # 2^28: 4 x the 479.8 MB captured at 2^26
 }
 
 

@@ -111,6 +111,27 @@ def test_many_tiles_per_cta_4096(pb):
     assert np.all(np.abs(out[rows] - ref) <= 1e-2 * np.abs(ref) + 1e-2 * rms)
 
 
+def test_benchmark_size_8192(pb):
+    """8192^3, the headline configuration (512 x 256 two-CTA tiles, 6.9 waves): sampled rows against fp64
+    and the full-size symmetry C(A, B)^T == C(B, A), which the swapped call computes with the roles of the
+    lane and column operands exchanged."""
+    S = 8192
+    g = torch.Generator(device=DEV).manual_seed(8192)
+    a = (torch.randn((S, S), device=DEV, generator=g) * 0.1).to(torch.bfloat16)
+    b = (torch.randn((S, S), device=DEV, generator=g) * 0.1).to(torch.bfloat16)
+    c = torch.full((S, S), float("nan"), dtype=torch.bfloat16, device=DEV)
+    c2 = torch.full((S, S), float("nan"), dtype=torch.bfloat16, device=DEV)
+    pb.runmyh100(S, S, S, a, b, c)      # c[n, m]
+    pb.runmyh100(S, S, S, b, a, c2)     # c2[m, n]
+    torch.cuda.synchronize()
+    assert torch.equal(c, c2.t())
+    rows = [0, 1, 127, 128, 255, 256, 511, 512, 4095, 4096, 8191]
+    ref = (b[rows].double() @ a.double().t()).cpu().numpy()         # [n in rows, m]
+    got = c[rows].double().cpu().numpy()
+    rms = float(np.sqrt(np.mean(ref * ref)))
+    assert np.all(np.abs(got - ref) <= 1e-2 * np.abs(ref) + 1e-2 * rms)
+
+
 def test_agrees_with_cublas_like_the_reference_harness(pb):
     """The reference harness accepts |kernel - cuBLAS| <= 0.1 (evals/h100_bench/main.cu:43-55); same check here."""
     M, N, K = 1024, 1024, 1024

@@ -85,6 +85,33 @@ def test_scan_2_28_properties(pb):
     assert np.array_equal(xs, O.scan_cpu(inp[: 1 << 22].cpu().numpy().view(np.uint32)))
 
 
+def test_scan_2_30_properties(pb):
+    """The sharded benchmark's total size on one GPU (4 GiB): last element = int64 total, differences
+    reproduce the input, and the first and last 2^22 elements equal the oracle continued from the
+    int64 prefix before them."""
+    n = 1 << 30
+    g = torch.Generator(device=DEV).manual_seed(30)
+    x = torch.randint(0, 2, (n,), dtype=torch.int32, device=DEV, generator=g)
+    head = x[: 1 << 22].cpu().numpy().view(np.uint32).copy()
+    tail = x[-(1 << 22):].cpu().numpy().view(np.uint32).copy()
+    total = int(x.sum(dtype=torch.int64))
+    before_tail = int(x[: n - (1 << 22)].sum(dtype=torch.int64))
+    first = int(x[0])
+    # differences are checked in chunks against the input, which is regenerated from the same seed
+    pb.scan_(x)
+    assert int(x[-1]) == total and int(x[0]) == first
+    g2 = torch.Generator(device=DEV).manual_seed(30)
+    inp = torch.randint(0, 2, (n,), dtype=torch.int32, device=DEV, generator=g2)
+    step = 1 << 28
+    for lo in range(0, n, step):
+        hi = min(n, lo + step)
+        a = max(lo, 1)
+        assert torch.equal(x[a:hi] - x[a - 1:hi - 1], inp[a:hi]), lo
+    assert np.array_equal(x[: 1 << 22].cpu().numpy().view(np.uint32), O.scan_cpu(head))
+    expect_tail = (O.scan_cpu(tail).astype(np.uint64) + before_tail).astype(np.uint32)
+    assert np.array_equal(x[-(1 << 22):].cpu().numpy().view(np.uint32), expect_tail)
+
+
 @pytest.mark.parametrize("n", [16384, 32768, 1 << 20, 1 << 24])
 def test_scan_matches_reference_kernel(pb, ref_gpu, n):
     """Side by side with the reference's generated scan_kernel (recompiled for sm_100)."""

@@ -113,6 +113,35 @@ def test_linearity_at_4096(pb):
     assert O.sgemm_rel_error(got, ref) <= O.SGEMM_TOL
 
 
+def test_sweep_size_8192_sampled(pb):
+    """Largest size of the sweep: rows sampled against fp64 (inputs generated on the device)."""
+    S = 8192
+    g = torch.Generator(device=DEV).manual_seed(81920)
+    a = torch.rand((S, S), device=DEV, generator=g) * 2 - 1
+    b = torch.rand((S, S), device=DEV, generator=g) * 2 - 1
+    c0 = torch.rand((S, S), device=DEV, generator=g) * 2 - 1
+    c = c0.clone()
+    pb.run_my_kernel(5, S, S, S, 1.5, a, b, 0.5, c)
+    torch.cuda.synchronize()
+    rows = [0, 127, 128, 4095, 4096, 8064, 8191]
+    ref = (1.5 * (a[rows].double() @ b.double()) + 0.5 * c0[rows].double()).cpu().numpy()
+    assert O.sgemm_rel_error(c[rows].cpu().numpy(), ref) <= O.SGEMM_TOL
+
+
+def test_kernel5_misaligned_operand_takes_the_checked_kernel(pb):
+    """A pointer that is not 16-byte aligned cannot use the bulk-copy kernel; the dispatcher must not reject it."""
+    M = N = K = 256
+    A, B, C = O.sgemm_inputs(M, N, K, seed=77)
+    buf = torch.empty(M * K + 1, dtype=torch.float32, device=DEV)
+    a = buf[1:]
+    a.copy_(torch.from_numpy(A).reshape(-1))
+    b, c = torch.from_numpy(B).to(DEV), torch.from_numpy(C).to(DEV)
+    assert a.data_ptr() % 16 != 0
+    pb.run_my_kernel(5, M, N, K, 1.5, a, b, 0.5, c)
+    torch.cuda.synchronize()
+    assert O.sgemm_rel_error(c.cpu().numpy(), O.sgemm_cpu(1.5, A, B, 0.5, C)) <= O.SGEMM_TOL
+
+
 @pytest.mark.parametrize("k", [1, 2, 3, 4, 5])
 def test_matches_reference_kernels(pb, ref_gpu, k):
     """Side by side with the reference's generated kernel k (recompiled for sm_100, harness launch geometry)."""

@@ -43,7 +43,7 @@ SCAN_NG = 1 << 30
 # from the ncu captures whose summaries sit in the profiles/ folder (None = not captured).
 NCU_TRAFFIC_BYTES = {
     "gemm_bf16": 970.5e6,   # 8192^3: 850.5 MB read + 120.0 MB written
-    "sgemm": 549.0e6,       # 4096^3: 491.9 MB read + 57.1 MB written
+    "sgemm": 640.5e6,       # 4096^3: 579.5 MB read + 61.0 MB written
     "scan": 1919.3e6,       # 2^28: 4 x the 479.8 MB captured at 2^26
 }
 

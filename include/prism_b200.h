@@ -80,14 +80,15 @@ unsigned long long prism_b200_launch_count(void);
  *                                             which evals/run_4090.sh:67-69 renames to kernel 3)
  *   4  128x128x8 tiles, 8x8 register tile, 128-bit accesses
  *                                            (generated/my_sgemm_kernel_4.cu)
- *   5  warp-tiled 128x128 tile, 8x16 accumulators per thread; on B200 a
- *      bulk-copy (TMA) staged, mbarrier-pipelined FFMA kernel
+ *   5  warp-tiled 128x128 tile, 8x16 accumulators per thread; on B200 A is
+ *      transposed into shared memory, B arrives by cp.async, and the FMAs are
+ *      issued two at a time as fma.rn.f32x2
  *                                            (generated/my_sgemm_kernel_5.cu)
  *   6  register-tiled, scalar accesses       (generated/my_sgemm_kernel_3.cu,
  *                                             emitted by the reference but never launched by its harness)
  * Shapes: ids 1, 2 and 6 accept any positive M, N, K.  Ids 3, 4, 5 use their tiled
  * kernels when the shape divides the tile (3: multiples of 32; 4: M, N multiples of
- * 128, K of 8; 5: M, N multiples of 128, K of 32) and a bounds-checked tiled kernel
+ * 128, K of 8; 5: M, N multiples of 128, K of 16) and a bounds-checked tiled kernel
  * otherwise, so no shape is rejected and no shape reads out of bounds.
  * No TF32 and no tensor cores anywhere on this path.
  */

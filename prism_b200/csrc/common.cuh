@@ -24,7 +24,7 @@ uint32_t* device_status_word();
 enum : uint32_t {
     DEV_OK = 0,
     DEV_SCAN_LOOKBACK_TIMEOUT = 0x5CA10001u,
-    DEV_SGEMM_PIPE_TIMEOUT    = 0x56E30001u,
+    DEV_SGEMM_PIPE_TIMEOUT    = 0x56E30001u,  // reserved: the SGEMM kernels have no waits that can run out
     DEV_GEMM_PIPE_TIMEOUT     = 0xB16E0001u,
     DEV_SELFTEST_TIMEOUT      = 0x5E1F0001u,
 };

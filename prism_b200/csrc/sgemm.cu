@@ -9,10 +9,9 @@
 // `run_my_kernel` (evals/4090_sgemm/runner.cu:245-267).
 //
 // Kernels 1-4 and 6 are the small rungs of the ladder.  Kernel 5 is the one that
-// matters for throughput: its A and B tiles are brought into shared memory by
-// the bulk-copy engine (cp.async.bulk, one row per copy, completion counted on an
-// mbarrier), three stages deep, and four warps run an 8x16 register tile per lane
-// out of 128-bit shared-memory reads.
+// matters for throughput: the A slice is transposed on its way into shared memory
+// (coalesced 16-byte loads, k-major stores), the B slice arrives by cp.async, and
+// four warps run an 8x16 register tile per lane on packed fma.rn.f32x2.
 #include "common.cuh"
 
 namespace prism_b200 {
@@ -218,46 +217,37 @@ my_sgemm_kernel_4(int M, int N, int K, float alpha, float* A, float* B, float be
 // Kernel 5: the throughput kernel (generated/my_sgemm_kernel_5.cu:1-84 with
 // loadFromGmem_our / processFromSmem_our, evals/4090_sgemm/my_kernel_utils.cuh:13-89).
 //
-// CTA tile 128 x 128, k-slice 32, three-stage ring in shared memory, 128 threads.
-//   Staging: a k-slice is 128 row copies of A (128 B each) and 32 row copies of B
-//     (512 B each) issued with cp.async.bulk, a quarter by each warp (one or two
-//     copies per lane); they complete on the stage's "full" mbarrier.  A rows land
-//     with a stride of 36 floats, which puts any 8 consecutive rows on 8 different
-//     16-byte bank groups.  Four warps and no separate producer warp keep the CTA at
-//     two warps per scheduler with two CTAs per SM, so a lane may use 255 registers.
-//   Compute: 2 x 2 arrangement of 64 x 64 warp tiles.  A lane owns
-//     rows  wm0 + (lane & 7) + 8 i  (i = 0..7) and columns  wn0 + 16 j + 4 (lane >> 3) .. +3
-//     (j = 0..3): 8 x 16 = 128 accumulators.  Per 4 k it reads 8 x 16 B of A (one per
-//     row, 4 consecutive k) and 4 x 4 x 16 B of B, all conflict-free, for 512 FMAs.
-//     With PACKED the FMAs are issued as fma.rn.f32x2 on column pairs (two
-//     independent fp32 FMAs per instruction: the same bits as the scalar form,
-//     37 -> 51 TFLOP/s at 4096^3).
-//   A "full"/"empty" mbarrier pair per stage hands slices back and forth; every
-//   wait is bounded.
-//   Measured and rejected: an 8-warp 8 x 8-per-lane form, 16-wide k-slices, a stage
-//     refilled two slices late, splitting the last wave's tiles into column halves (a lone
-//     CTA on an SM already runs nearly twice as fast), and dropping the duplicating moves
-//     (no faster): every form settles near 0.65 FMA per lane per clock.
-// Needs M % 128 == 0, N % 128 == 0, K % 32 == 0 and 16-byte aligned A, B, C.
+// CTA tile 128 x 128 (or 64 x 128 when there are few tiles), k-slice 16, two shared-memory
+// buffers, 128 threads, two CTAs per SM (two warps per scheduler, so a lane may use 255 registers).
+//   Staging: the A slice (128 rows x 16 k) is read with coalesced 16-byte loads (four
+//     lanes per row) into registers while the current slice is consumed, then stored
+//     TRANSPOSED (k-major, row stride 132 floats) into the other buffer, so that a lane's
+//     rows for one k are two 16-byte reads and only 8 floats of A are live at a time.  The
+//     B slice (16 rows x 512 or 256 B) goes straight to shared memory with 16-byte
+//     cp.async, no registers.  One __syncthreads per slice.
+//   Compute: 2 x 2 arrangement of 64 x 64 warp tiles.  A lane owns rows
+//     wm0 + 4 (lane & 7) + {0..3} and 32 more down, and columns wn0 + 16 j + 4 (lane >> 3) .. +3
+//     (j = 0..3): 8 x 16 = 128 accumulators.  Per k it reads 2 x 16 B of A and 4 x 16 B
+//     of B (every read a broadcast of distinct contiguous 16-byte chunks) for 128 FMAs.
+//     With PACKED the FMAs are issued as fma.rn.f32x2 on column pairs: two independent
+//     fp32 FMAs per instruction, the same bits as the scalar form.  All eight duplicated
+//     A values are prepared first and the FMAs go column pair by column pair, so that
+//     consecutive instructions share their B operand.
+//   Measured on a B200 at 4096^3 / 8192^3 (TFLOP/s): this form 63.1 / 64.5; the same with
+//     B register-staged 55.9 / 57.3; with A through 4-byte cp.async 54.0 / 55.4; k-slices
+//     of 8 or 32: 58.9 / 60.4 and 57.9 / 61.5; A loaded one row per lane 56.3 / 57.6; a
+//     256-thread form with 8 x 8 outputs per lane 60.5 / 61.8; 256 x 128 tiles with one CTA per
+//     SM 52.2 / 60.4.  An earlier form that staged row-major A with cp.async.bulk through a
+//     three-stage mbarrier ring reached 51.5 / 53.6: its A fragments (four k per 16-byte
+//     read) kept 32 registers live and left the compiler no room to overlap reads and FMAs.
+//     A register-only loop of the same fma.rn.f32x2 pattern peaks at 69.3.
+// Needs M % 128 == 0, N % 128 == 0, K % 16 == 0 and 16-byte aligned A, B, C.
 // ============================================================================
 namespace k5 {
-constexpr int BM = 128, BN = 128, BK = 32;
-constexpr int STAGES = 3;
+constexpr int BM = 128, BN = 128, BK = 16;
 constexpr int WARPS = 4;
 constexpr int THREADS = WARPS * 32;
-constexpr int A_STRIDE = BK + 4;        // floats
-constexpr int A_STAGE = BM * A_STRIDE;  // floats
-constexpr int B_STAGE = BK * BN;        // floats
-constexpr size_t SMEM_BYTES = static_cast<size_t>(STAGES) * (A_STAGE + B_STAGE) * sizeof(float) + 2 * STAGES * 8 + 16;
-constexpr int kUnroll = 4;  // groups of 4 k-steps unrolled in the inner loop (1, 2 and 8 measured 1-5 % slower)
 }  // namespace k5
-
-__device__ __forceinline__ void bulk_copy_g2s(void* dst_smem, const void* src, uint32_t bytes, uint64_t* bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                     smem_u32(dst_smem)),
-                 "l"(src), "r"(bytes), "r"(smem_u32(bar))
-                 : "memory");
-}
 
 __device__ __forceinline__ unsigned long long pack2(float lo, float hi) {
     unsigned long long r;
@@ -270,54 +260,68 @@ __device__ __forceinline__ void unpack2(unsigned long long v, float& lo, float& 
 __device__ __forceinline__ void fma2(unsigned long long& acc, unsigned long long a, unsigned long long b) {
     asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc) : "l"(a), "l"(b));
 }
+__device__ __forceinline__ void cp_async16(void* dst_smem, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 
-// One 128 x 128 tile of C at (row0, col0); NV = 16-byte B vectors per lane per k.
-template <bool PACKED, int NV>
-__device__ __forceinline__ void k5_tile(int N, int K, float alpha, const float* A, const float* B, float beta, float* C,
-                                        int row0, int col0, unsigned char* smem_raw) {
+// WARPS_M x WARPS_N warps (four in all), each on a 64 x (16 NV) warp tile; NV = 16-byte B vectors
+// per lane per k.  <2, 2, 4>: the 128 x 128 tile.  <1, 4, 2>: a 64 x 128 tile of 64 x 32 warp
+// tiles (8 x 8 outputs per lane, three CTAs per SM) for problems with few tiles.
+template <bool PACKED, int WARPS_M, int WARPS_N, int NV>
+__global__ void __launch_bounds__(k5::THREADS, NV == 4 ? 2 : 3)
+my_sgemm_kernel_5(int M, int N, int K, float alpha, float* A, float* B, float beta, float* C, int num_blocks_N) {
     using namespace k5;
-    constexpr int TILE_N = 32 * NV;   // columns of this tile
-    constexpr int WN = 16 * NV;       // warp tile columns
-    float* As = reinterpret_cast<float*>(smem_raw);
-    float* Bs = As + STAGES * A_STAGE;
-    uint64_t* full_bar = reinterpret_cast<uint64_t*>(Bs + STAGES * B_STAGE);
-    uint64_t* empty_bar = full_bar + STAGES;
-    volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(empty_bar + STAGES);
+    static_assert(WARPS_M * WARPS_N == WARPS, "four warps");
+    constexpr int BM = 64 * WARPS_M;          // rows of the CTA tile (shadows k5::BM)
+    constexpr int WN = 16 * NV;               // columns of a warp tile
+    constexpr int TILE_N = WARPS_N * WN;      // columns of the CTA tile
+    constexpr int A_STRIDE = BM + 4;          // floats between consecutive k in the transposed A slice
+    constexpr int A_CH = BM * BK / 4 / THREADS;      // 16-byte chunks of A per thread per slice (4 or 2)
+    constexpr int B_CH = BK * TILE_N / 4 / THREADS;  // 16-byte chunks of B per thread per slice (4)
+    __shared__ __align__(16) float As[2][BK * A_STRIDE];
+    __shared__ __align__(16) float Bs[2][BK * TILE_N];
 
+    const int row0 = (static_cast<int>(blockIdx.x) / num_blocks_N) * BM;
+    const int col0 = (static_cast<int>(blockIdx.x) % num_blocks_N) * TILE_N;
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int k_slices = K / BK;
-
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) {
-            mbar_init(&full_bar[s], WARPS);
-            mbar_init(&empty_bar[s], WARPS);
-        }
-        *abort_flag = 0;
-        fence_barrier_init();
-    }
-    __syncthreads();
-
-    // Each warp copies its quarter of a k-slice: 32 rows of A (lane = row) and 8 rows
-    // of B (lanes 0-7), and announces those bytes on the stage's "full" barrier first.
-    const float* a_src = A + static_cast<size_t>(row0 + warp * 32 + lane) * K;
-    const float* b_src = B + static_cast<size_t>(warp * 8 + (lane & 7)) * N + col0;
-    auto issue_slice = [&](int t) {
-        const int s = t % STAGES;
-        if (lane == 0) mbar_arrive_expect_tx(&full_bar[s], 32u * BK * 4u + 8u * TILE_N * 4u);
-        __syncwarp();
-        bulk_copy_g2s(As + s * A_STAGE + (warp * 32 + lane) * A_STRIDE, a_src + t * BK, BK * sizeof(float),
-                      &full_bar[s]);
-        if (lane < 8)
-            bulk_copy_g2s(Bs + s * B_STAGE + (warp * 8 + lane) * TILE_N, b_src + static_cast<size_t>(t) * BK * N,
-                          TILE_N * sizeof(float), &full_bar[s]);
-    };
-    for (int t = 0; t < STAGES - 1 && t < k_slices; ++t) issue_slice(t);
-
     const int tm = lane & 7;
     const int tn = lane >> 3;
-    const int wm0 = (warp >> 1) * 64;
-    const int wn0 = (warp & 1) * WN;
+    const int wm0 = (warp / WARPS_N) * 64;
+    const int wn0 = (warp % WARPS_N) * WN;
+
+    // Chunk c of the A slice: row c / 4, k offset 4 (c % 4): four lanes read one row's 64 bytes.
+    float4 pa[A_CH];
+    auto load_a = [&](int k0) {
+#pragma unroll
+        for (int n = 0; n < A_CH; ++n) {
+            const int c = threadIdx.x + n * THREADS;
+            pa[n] = *reinterpret_cast<const float4*>(A + static_cast<size_t>(row0 + c / (BK / 4)) * K + k0 +
+                                                     (c % (BK / 4)) * 4);
+        }
+    };
+    auto store_a = [&](int buf) {
+#pragma unroll
+        for (int n = 0; n < A_CH; ++n) {
+            const int c = threadIdx.x + n * THREADS;
+            float* d = &As[buf][(c % (BK / 4)) * 4 * A_STRIDE + c / (BK / 4)];
+            d[0] = pa[n].x;
+            d[A_STRIDE] = pa[n].y;
+            d[2 * A_STRIDE] = pa[n].z;
+            d[3 * A_STRIDE] = pa[n].w;
+        }
+    };
+    auto copy_b = [&](int k0, int buf) {
+#pragma unroll
+        for (int n = 0; n < B_CH; ++n) {
+            const int c = threadIdx.x + n * THREADS;
+            const int r = c / (TILE_N / 4), c4 = c % (TILE_N / 4);
+            cp_async16(&Bs[buf][r * TILE_N + c4 * 4], B + static_cast<size_t>(k0 + r) * N + col0 + c4 * 4);
+        }
+        cp_async_commit();
+    };
 
     unsigned long long acc2[PACKED ? 8 : 1][PACKED ? 2 * NV : 1];
     float acc[PACKED ? 1 : 8][PACKED ? 1 : 4 * NV];
@@ -333,88 +337,68 @@ __device__ __forceinline__ void k5_tile(int N, int K, float alpha, const float* 
             for (int j = 0; j < 4 * NV; ++j) acc[i][j] = 0.f;
     }
 
-    bool ok = true;
-    for (int t = 0; t < k_slices; ++t) {
-        const int s = t % STAGES;
-        const uint32_t round = static_cast<uint32_t>(t / STAGES);
-        // Refill the stage that slice t-1 used with slice t+STAGES-1, once all four
-        // warps have released it.
-        const int refill = t + STAGES - 1;
-        if (refill < k_slices) {
-            if (t >= 1 && !mbar_wait_bounded(&empty_bar[(t - 1) % STAGES], static_cast<uint32_t>((t - 1) / STAGES) & 1u,
-                                             abort_flag)) {
-                ok = false;
-                break;
-            }
-            issue_slice(refill);
+    load_a(0);
+    copy_b(0, 0);
+    store_a(0);
+    cp_async_wait_all();
+    __syncthreads();
+
+    int buf = 0;
+    for (int k0 = 0; k0 < K; k0 += BK) {
+        // The other buffer was last read before the barrier that ended the previous slice.
+        const bool more = k0 + BK < K;
+        if (more) {
+            load_a(k0 + BK);
+            copy_b(k0 + BK, buf ^ 1);
         }
-        if (!mbar_wait_bounded(&full_bar[s], round & 1u, abort_flag)) {
-            ok = false;
-            break;
-        }
-        const float* a_base = As + s * A_STAGE + (wm0 + tm) * A_STRIDE;
-        const float* b_base = Bs + s * B_STAGE + wn0 + tn * 4;
-#pragma unroll kUnroll
-        for (int kk = 0; kk < BK; kk += 4) {
-            float4 a[8];
+        const float* a_base = &As[buf][wm0 + tm * 4];
+        const float* b_base = &Bs[buf][wn0 + tn * 4];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) a[i] = *reinterpret_cast<const float4*>(a_base + i * 8 * A_STRIDE + kk);
+        for (int k = 0; k < BK; ++k) {
+            const float4 alo = *reinterpret_cast<const float4*>(a_base + k * A_STRIDE);
+            const float4 ahi = *reinterpret_cast<const float4*>(a_base + k * A_STRIDE + 32);
+            const float av[8] = {alo.x, alo.y, alo.z, alo.w, ahi.x, ahi.y, ahi.z, ahi.w};
+            if constexpr (PACKED) {
+                ulonglong2 b[NV];
 #pragma unroll
-            for (int k4 = 0; k4 < 4; ++k4) {
-                if constexpr (PACKED) {
-                    ulonglong2 b[NV];
+                for (int j = 0; j < NV; ++j) b[j] = *reinterpret_cast<const ulonglong2*>(b_base + k * TILE_N + j * 16);
+                unsigned long long a2[8];
 #pragma unroll
-                    for (int j = 0; j < NV; ++j)
-                        b[j] = *reinterpret_cast<const ulonglong2*>(b_base + (kk + k4) * TILE_N + j * 16);
-                    // All eight duplicated A values first, then the FMAs column pair by column pair:
-                    // consecutive FMAs share their B operand.  Measured 3 % faster than row by row.
-                    unsigned long long a2[8];
+                for (int i = 0; i < 8; ++i) a2[i] = pack2(av[i], av[i]);
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const float av = k4 == 0 ? a[i].x : k4 == 1 ? a[i].y : k4 == 2 ? a[i].z : a[i].w;
-                        a2[i] = pack2(av, av);
-                    }
+                for (int j = 0; j < NV; ++j) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) fma2(acc2[i][2 * j + 0], a2[i], b[j].x);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) fma2(acc2[i][2 * j + 1], a2[i], b[j].y);
+                }
+            } else {
+                float4 b[NV];
+#pragma unroll
+                for (int j = 0; j < NV; ++j) b[j] = *reinterpret_cast<const float4*>(b_base + k * TILE_N + j * 16);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
 #pragma unroll
                     for (int j = 0; j < NV; ++j) {
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) fma2(acc2[i][2 * j + 0], a2[i], b[j].x);
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) fma2(acc2[i][2 * j + 1], a2[i], b[j].y);
-                    }
-                } else {
-                    float4 b[NV];
-#pragma unroll
-                    for (int j = 0; j < NV; ++j)
-                        b[j] = *reinterpret_cast<const float4*>(b_base + (kk + k4) * TILE_N + j * 16);
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const float av = k4 == 0 ? a[i].x : k4 == 1 ? a[i].y : k4 == 2 ? a[i].z : a[i].w;
-#pragma unroll
-                        for (int j = 0; j < NV; ++j) {
-                            acc[i][4 * j + 0] = fmaf(av, b[j].x, acc[i][4 * j + 0]);
-                            acc[i][4 * j + 1] = fmaf(av, b[j].y, acc[i][4 * j + 1]);
-                            acc[i][4 * j + 2] = fmaf(av, b[j].z, acc[i][4 * j + 2]);
-                            acc[i][4 * j + 3] = fmaf(av, b[j].w, acc[i][4 * j + 3]);
-                        }
+                        acc[i][4 * j + 0] = fmaf(av[i], b[j].x, acc[i][4 * j + 0]);
+                        acc[i][4 * j + 1] = fmaf(av[i], b[j].y, acc[i][4 * j + 1]);
+                        acc[i][4 * j + 2] = fmaf(av[i], b[j].z, acc[i][4 * j + 2]);
+                        acc[i][4 * j + 3] = fmaf(av[i], b[j].w, acc[i][4 * j + 3]);
                     }
                 }
             }
         }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&empty_bar[s]);
-    }
-    if (!ok) {
-        if (lane == 0) {
-            *abort_flag = 1;
-            raise_device_status(DEV_SGEMM_PIPE_TIMEOUT);
-        }
-        return;
+        if (more) store_a(buf ^ 1);
+        cp_async_wait_all();
+        __syncthreads();
+        buf ^= 1;
     }
 
     // C = alpha * acc + beta * C, 16 bytes at a time.
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-        float* c_row = C + static_cast<size_t>(row0 + wm0 + tm + 8 * i) * N + col0 + wn0 + tn * 4;
+        const int r = row0 + wm0 + (i < 4 ? tm * 4 + i : 32 + tm * 4 + (i - 4));
+        float* c_row = C + static_cast<size_t>(r) * N + col0 + wn0 + tn * 4;
 #pragma unroll
         for (int j = 0; j < NV; ++j) {
             float4* c = reinterpret_cast<float4*>(c_row + j * 16);
@@ -435,18 +419,21 @@ __device__ __forceinline__ void k5_tile(int N, int K, float alpha, const float* 
     }
 }
 
-template <bool PACKED>
-__global__ void __launch_bounds__(k5::THREADS, 2)
-my_sgemm_kernel_5(int M, int N, int K, float alpha, float* A, float* B, float beta, float* C, int num_blocks_N) {
-    extern __shared__ __align__(128) unsigned char smem_raw[];
-    const int bid = static_cast<int>(blockIdx.x);
-    k5_tile<PACKED, 4>(N, K, alpha, A, B, beta, C, (bid / num_blocks_N) * k5::BM, (bid % num_blocks_N) * k5::BN,
-                       smem_raw);
-}
-
 namespace {
 
 inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+int sm_count() {
+    static int n[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (n[dev] == 0) {
+        int v = 0;
+        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
+        n[dev] = v;
+    }
+    return n[dev];
+}
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -524,17 +511,16 @@ extern "C" int prism_b200_sgemm(int kernel_id, int M, int N, int K, float alpha,
                 g_k5_scalar = e && e[0] == '1';
                 g_k5_env_read = true;
             }
-            auto kern = g_k5_scalar ? my_sgemm_kernel_5<false> : my_sgemm_kernel_5<true>;
-            static bool attr_set[2][64] = {};
-            int dev = 0;
-            PRISM_CUDA_TRY(cudaGetDevice(&dev));
-            if (dev < 0 || dev >= 64 || !attr_set[g_k5_scalar][dev]) {
-                PRISM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                    static_cast<int>(k5::SMEM_BYTES)));
-                if (dev >= 0 && dev < 64) attr_set[g_k5_scalar][dev] = true;
-            }
+            // Fewer 128 x 128 tiles than half the SMs: halve the tile's height so twice as many SMs work
+            // (same k order per output element, so the same bits; 1024^3: 29 -> 37 TFLOP/s).
+            const long long tiles = static_cast<long long>(M / k5::BM) * (N / k5::BN);
+            const bool half_height = 2 * tiles <= sm_count();
+            auto kern = half_height
+                            ? (g_k5_scalar ? my_sgemm_kernel_5<false, 1, 4, 2> : my_sgemm_kernel_5<true, 1, 4, 2>)
+                            : (g_k5_scalar ? my_sgemm_kernel_5<false, 2, 2, 4> : my_sgemm_kernel_5<true, 2, 2, 4>);
             const int nbn = N / k5::BN;
-            kern<<<static_cast<unsigned>((M / k5::BM) * nbn), k5::THREADS, k5::SMEM_BYTES, s>>>(
+            const long long blocks = (half_height ? 2 : 1) * tiles;
+            kern<<<static_cast<unsigned>(blocks), k5::THREADS, 0, s>>>(
                 M, N, K, alpha, const_cast<float*>(A), const_cast<float*>(B), beta, C, nbn);
         } else {
             rc = launch_generic(M, N, K, alpha, A, B, beta, C, s);

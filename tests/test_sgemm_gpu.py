@@ -84,6 +84,18 @@ def test_kernel5_scalar_and_packed_fma_agree(pb, monkeypatch):
     assert np.array_equal(outs[0], outs[1])
 
 
+def test_kernel5_both_tile_forms(pb):
+    """Kernel 5 runs 128 x 128 tiles, or 64 x 128 tiles when fewer than half the SMs would get a tile.
+    1152 x 1152 (81 tiles) takes the first form, its top 512 rows alone (36 tiles) the second; both are
+    checked against fp64 and, having the same k order per element, against each other bit for bit."""
+    M, N, K = 1152, 1152, 80
+    A, B, C = O.sgemm_inputs(M, N, K, seed=1152)
+    big = _run(pb, 5, 1.5, A, B, 0.5, C)
+    small = _run(pb, 5, 1.5, A[:512].copy(), B, 0.5, C[:512].copy())
+    assert O.sgemm_rel_error(big, O.sgemm_cpu(1.5, A, B, 0.5, C)) <= O.SGEMM_TOL
+    assert np.array_equal(big[:512], small)
+
+
 @pytest.mark.parametrize("k", KERNELS)
 @pytest.mark.parametrize("shape", [(1, 1, 1), (33, 65, 17), (100, 130, 50), (129, 127, 31), (64, 64, 0)])
 def test_ragged_shapes_every_kernel(pb, k, shape):
@@ -129,7 +141,7 @@ def test_sweep_size_8192_sampled(pb):
 
 
 def test_kernel5_misaligned_operand_takes_the_checked_kernel(pb):
-    """A pointer that is not 16-byte aligned cannot use the bulk-copy kernel; the dispatcher must not reject it."""
+    """A pointer that is not 16-byte aligned cannot use the 16-byte-vector kernel; the dispatcher must not reject it."""
     M = N = K = 256
     A, B, C = O.sgemm_inputs(M, N, K, seed=77)
     buf = torch.empty(M * K + 1, dtype=torch.float32, device=DEV)

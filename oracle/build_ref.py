@@ -8,7 +8,10 @@
                                geometry, compiled for sm_100 with the reference Makefile's flags
                                (-O3 --use_fast_math -w; evals/4090_sgemm/Makefile:12-18, evals/4090_scan/Makefile:3-4).
 
-Steps 2 and 3 compile the reference's sources from where they lie (include path
+4. oracle/_ref/relink_sgemm_sweep  the reference's SGEMM sweep program (evals/4090_sgemm/main.cu), unmodified, linked
+                               against libprism_b200.so through relink_sgemm_runner.cu instead of its own runner.cu.
+
+Steps 2 to 4 compile the reference's sources from where they lie (include path
 = the reference root); nothing is copied.  They are skipped when the reference
 tree is absent (e.g. on a GPU box, which uses the files built beforehand).
 The bf16 kernel is not built: wgmma does not assemble for sm_100.
@@ -67,7 +70,26 @@ def build_reference(reference: str = DEFAULT_REFERENCE, force: bool = False) -> 
         _run([nvcc, "-arch=sm_100", "-O3", "--use_fast_math", "-w", "-cudart", "static", "-shared", "-Xcompiler", "-fPIC",
               f"-I{ref}", str(gpu_src), "-o", str(gpu_out)])
     built["gpu"] = gpu_out
+    relink = build_relinked_sgemm_sweep(ref, force)
+    if relink is not None:
+        built["relink_sgemm_sweep"] = relink
     return built
+
+
+def build_relinked_sgemm_sweep(ref: Path, force: bool = False) -> Path | None:
+    """The reference's own sweep main, compiled in place, on this library's `run_my_kernel`."""
+    main_cu = ref / "evals" / "4090_sgemm" / "main.cu"
+    lib = HERE.parent / "prism_b200" / "libprism_b200.so"
+    if not main_cu.exists() or not lib.exists():
+        return None
+    out = REF_OUT / "relink_sgemm_sweep"
+    runner = HERE / "relink_sgemm_runner.cu"
+    if force or not _newer(out, [runner, lib]):
+        nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+        _run([nvcc, "-arch=sm_100", "-O3", "-w", "-std=c++17", f"-I{main_cu.parent}", f"-I{HERE.parent / 'include'}",
+              str(main_cu), str(runner), "-o", str(out), "-lcublas", f"-L{lib.parent}", "-lprism_b200",
+              "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/../../prism_b200"])
+    return out
 
 
 if __name__ == "__main__":

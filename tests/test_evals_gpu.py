@@ -59,3 +59,19 @@ def test_bf16_bench_format_and_checks(binaries):
     k = re.search(r"Kernel:\s+.*performance:\s+\(\s*([\d.]+)\)\s+TFLOPS.*size:\s+\((\d+)\)", out)
     c = re.search(r"cuBLAS:\s+.*performance:\s+\(\s*([\d.]+)\)\s+TFLOPS.*size:\s+\((\d+)\)", out)
     assert k and c and int(k.group(2)) == 1024 and float(k.group(1)) > 0 and float(c.group(1)) > 0
+
+
+def test_reference_sgemm_sweep_relinked_against_this_library():
+    """The reference's own sweep program (evals/4090_sgemm/main.cu, compiled unmodified where a checkout of the
+    reference was present) linked against this library instead of its runner.cu: its cuBLAS comparison must pass
+    for kernels 1-5 and the sweep must print all six sizes.  Skipped where the binary was not built."""
+    exe = ROOT / "oracle" / "_ref" / "relink_sgemm_sweep"
+    if not exe.exists():
+        pytest.skip("oracle/_ref/relink_sgemm_sweep not built (needs a checkout of the reference at build time)")
+    out = _run([exe])
+    assert out.count("Correctness: PASSED") == 5 and "Divergence" not in out
+    perf = out.split("Starting Performance Sweep")[1]
+    sizes = [int(m.group(1)) for m in re.finditer(r"^Size:\s+(\d+)x(\d+)x(\d+)", perf, re.M)]
+    assert sizes == [256, 512, 1024, 2048, 4096, 8192]
+    vals = re.findall(r"performance:\s+\(\s*([\d.]+)\)\s+GFLOPS.*size:\s+\((\d+)\)", perf)
+    assert len(vals) == 36 and all(float(v) > 0 for v, _ in vals)

@@ -277,7 +277,7 @@ def run_gemm_bf16(args, world, rank, peaks):
     e2e_ms = e2e_total / e2e_steps
     e2e = {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
            "h2d_bytes_per_step": op.h2d_bytes, "d2h_bytes_per_step": op.d2h_bytes,
-           "pipeline": "%d blocks of B rows, upload / kernel / download on three streams" % len(op.blocks)}
+           "pipeline": "%d blocks of B rows, upload / kernel / download on three streams" % op.blocks}
 
     kernel_ms = sum(per) / len(per)     # this rank's kernel: rows x S x S
     achieved = 2.0 * rows * S * S / (kernel_ms * 1e-3) / 1e12
@@ -348,7 +348,7 @@ def run_sgemm(args, world, rank, peaks, steps=None, warmup=None):
                          "traffic": NCU_TRAFFIC_BYTES["sgemm"] if (S == SGEMM_S and world == 1) else None},
             "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": op.h2d_bytes, "d2h_bytes_per_step": op.d2h_bytes,
-                    "pipeline": "%d blocks of rows of M, upload / kernel / download on three streams" % len(op.blocks)},
+                    "pipeline": "%d blocks of rows of M, upload / kernel / download on three streams" % op.blocks},
             "gpu_launches": launches, "clocks": clocks, "rel_error_sampled_rows": err, "spot_check_ok": err <= 1e-5}
 
 
@@ -387,7 +387,7 @@ def run_scan(args, world, rank, peaks, steps=None, warmup=None):
         e2e_ms = e2e_total / 3
         e2e = {"value": nbytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_ms,
                "h2d_bytes_per_step": op.h2d_bytes, "d2h_bytes_per_step": op.d2h_bytes,
-               "pipeline": "%d blocks chained by their last element, upload / kernel / download on three streams" % len(op.blocks)}
+               "pipeline": "%d blocks chained by their last element, upload / kernel / download on three streams" % op.blocks}
     kernel_ms = sum(per) / len(per)
     achieved = 8.0 * n / (kernel_ms * 1e-3) / 1e9
     peak = peaks["hbm_gbs"]

@@ -191,6 +191,43 @@ int prism_b200_scan_static(size_t n, uint32_t* x, void* stream);
 int prism_b200_gemm_bf16(int M, int N, int K, const uint16_t* A, const uint16_t* B,
                          uint16_t* C, void* stream);
 
+/* ---- host-buffer plans ------------------------------------------------------ */
+
+/*
+ * The three operators for operands that live in HOST memory, which is how the reference
+ * harnesses hold theirs: they cudaMemcpy in, launch, cudaMemcpy out
+ * (evals/4090_scan/scan_harness.cuh:112-131, evals/4090_sgemm/main.cu:64-120,
+ * evals/h100_bench/main.cu:105-130).  A plan owns device staging buffers for one problem size
+ * and three streams; a run cuts the call into blocks that are contiguous on both sides and
+ * overlaps the upload of one block, the kernel on the one before and the download of the one
+ * before that (bf16 GEMM: A whole, then rows of B = row blocks of the N x M result; SGEMM: B
+ * whole, then rows of M of A and C; scan: blocks of the array, each seeded on the device with
+ * the last element of the block before).  Host buffers should be pinned (cudaHostAlloc /
+ * cudaHostRegister), otherwise the copies do not overlap; results are the same either way and
+ * bit-identical to the device-resident entry points.
+ * A run is asynchronous: it is ordered after the work already queued on `stream`, and `stream`
+ * waits for it; synchronise `stream` before reading the host result.  Runs of one plan must
+ * not overlap each other except through that ordering.  create/destroy allocate and free
+ * device memory, a run does not.  block_rows / block_elems = 0 picks the default (1024 rows;
+ * n / 16 elements, at least 2^22).  Operand layouts and dtypes are those of prism_b200_gemm_bf16,
+ * prism_b200_sgemm and prism_b200_scan.  A plan belongs to the device that was current when it
+ * was created.
+ */
+typedef struct prism_b200_host_plan prism_b200_host_plan;
+
+int prism_b200_host_gemm_bf16_create(int M, int N, int K, int block_rows, prism_b200_host_plan** plan);
+int prism_b200_host_gemm_bf16_run(prism_b200_host_plan* plan, const uint16_t* A_host, const uint16_t* B_host,
+                                  uint16_t* C_host, void* stream);
+int prism_b200_host_sgemm_create(int kernel_id, int M, int N, int K, int block_rows, prism_b200_host_plan** plan);
+int prism_b200_host_sgemm_run(prism_b200_host_plan* plan, float alpha, const float* A_host, const float* B_host,
+                              float beta, float* C_host, void* stream);
+int prism_b200_host_scan_create(size_t n, size_t block_elems, prism_b200_host_plan** plan);
+int prism_b200_host_scan_run(prism_b200_host_plan* plan, uint32_t* x_host, void* stream);
+/* Number of blocks a run is cut into (-1 for a bad handle). */
+int prism_b200_host_plan_blocks(const prism_b200_host_plan* plan);
+/* Waits for the plan's streams, then frees its buffers, streams and events. */
+void prism_b200_host_plan_destroy(prism_b200_host_plan* plan);
+
 #ifdef __cplusplus
 }
 #endif

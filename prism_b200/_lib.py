@@ -40,6 +40,14 @@ SIGNATURES = {
     "prism_b200_scan_seeded_peers": (c_int, [c_size_t, c_void_p, c_void_p, c_void_p, c_int, c_int, ctypes.c_uint32, c_void_p]),
     "prism_b200_scan_static": (c_int, [c_size_t, c_void_p, c_void_p]),
     "prism_b200_gemm_bf16": (c_int, [c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "prism_b200_host_gemm_bf16_create": (c_int, [c_int, c_int, c_int, c_int, POINTER(c_void_p)]),
+    "prism_b200_host_gemm_bf16_run": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "prism_b200_host_sgemm_create": (c_int, [c_int, c_int, c_int, c_int, c_int, POINTER(c_void_p)]),
+    "prism_b200_host_sgemm_run": (c_int, [c_void_p, c_float, c_void_p, c_void_p, c_float, c_void_p, c_void_p]),
+    "prism_b200_host_scan_create": (c_int, [c_size_t, c_size_t, POINTER(c_void_p)]),
+    "prism_b200_host_scan_run": (c_int, [c_void_p, c_void_p, c_void_p]),
+    "prism_b200_host_plan_blocks": (c_int, [c_void_p]),
+    "prism_b200_host_plan_destroy": (None, [c_void_p]),
 }
 
 

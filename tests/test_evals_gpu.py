@@ -75,3 +75,10 @@ def test_reference_sgemm_sweep_relinked_against_this_library():
     assert sizes == [256, 512, 1024, 2048, 4096, 8192]
     vals = re.findall(r"performance:\s+\(\s*([\d.]+)\)\s+GFLOPS.*size:\s+\((\d+)\)", perf)
     assert len(vals) == 36 and all(float(v) > 0 for v, _ in vals)
+
+
+def test_host_e2e_program_through_the_c_abi_alone(binaries):
+    """Host plans driven from C++ with cudaHostAlloc'ed arrays (no Python on the data path), small sizes."""
+    out = _run([binaries / "host_e2e", 1024, 512, 23])
+    assert out.strip().endswith("PASSED") and "mismatch" not in out
+    assert len(re.findall(r"^host (bf16 GEMM|SGEMM|scan) .* end to end", out, re.M)) == 3

@@ -234,7 +234,8 @@ my_sgemm_kernel_4(int M, int N, int K, float alpha, float* A, float* B, float be
 //     A values are prepared first and the FMAs go column pair by column pair, so that
 //     consecutive instructions share their B operand.
 //   Measured on a B200 at 4096^3 / 8192^3 (TFLOP/s): this form 63.1 / 64.5; the same with
-//     B register-staged 55.9 / 57.3; with A through 4-byte cp.async 54.0 / 55.4; k-slices
+//     B register-staged 55.9 / 57.3; with B rows brought in by the bulk-copy (TMA) engine onto an
+//     mbarrier 57.6 / 59.9; with A through 4-byte cp.async 54.0 / 55.4; k-slices
 //     of 8 or 32: 58.9 / 60.4 and 57.9 / 61.5; A loaded one row per lane 56.3 / 57.6; a
 //     256-thread form with 8 x 8 outputs per lane 60.5 / 61.8; 256 x 128 tiles with one CTA per
 //     SM 52.2 / 60.4.  An earlier form that staged row-major A with cp.async.bulk through a

@@ -114,6 +114,15 @@ int prism_b200_scan_workspace_size(size_t n, size_t* bytes);
 int prism_b200_scan(size_t n, uint32_t* x, void* workspace, void* stream);
 
 /*
+ * fp32 flavour of the same single-pass kernel (no counterpart in the reference, whose scan is
+ * uint32 only): in-place inclusive prefix sum of n floats, same workspace, same limits.  Sums
+ * are formed in fp32, 4 elements serially per thread, then by warp shuffles, then across tiles
+ * through the look-back; how the tile sums are grouped follows the look-back windows, which
+ * depend on timing, so two runs may differ in the last bits (compare with a tolerance).
+ */
+int prism_b200_scan_f32(size_t n, float* x, void* workspace, void* stream);
+
+/*
  * Sharded scan helpers (no counterpart in the reference, which is single-GPU).
  * A rank that owns the r-th contiguous chunk of a longer array
  *   1. prism_b200_reduce_u32: total of its chunk -> *total (device),

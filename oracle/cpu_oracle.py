@@ -41,6 +41,13 @@ def scan_cpu(x: np.ndarray) -> np.ndarray:
     return np.cumsum(x, dtype=np.uint32)
 
 
+def scan_f32_cpu(x: np.ndarray) -> np.ndarray:
+    """fp64 running sum of float32 values: the value an fp32 scan approximates.  The reference has no
+    floating-point scan (its kernel and its CPU loop are uint32, evals/4090_scan/scan_harness.cuh:30-36);
+    this is the checker of the library's fp32 flavour, compared with a tolerance."""
+    return np.cumsum(np.ascontiguousarray(x, dtype=np.float32).astype(np.float64))
+
+
 def scan_cpu_loop(x: np.ndarray) -> np.ndarray:
     """The same thing as a literal loop (small inputs only); used to pin `scan_cpu`."""
     x = np.ascontiguousarray(x).view(np.uint32)

@@ -121,6 +121,19 @@ def scan_(x: torch.Tensor, workspace: torch.Tensor | None = None) -> torch.Tenso
     return launch_scan(n, x, workspace)
 
 
+def scan_f32_(x: torch.Tensor, workspace: torch.Tensor | None = None) -> torch.Tensor:
+    """In-place inclusive prefix sum of a float32 tensor (fp32 adds; last bits may vary between runs)."""
+    _require_cuda("x", x, (torch.float32,))
+    if workspace is None:
+        workspace = scan_workspace(x.numel(), x.device)
+    _require_cuda("workspace", workspace)
+    if workspace.numel() * workspace.element_size() < get_workspace_size(x.numel()):
+        raise ValueError("workspace too small; see get_workspace_size(n)")
+    with torch.cuda.device(x.device):
+        _lib.check(load().prism_b200_scan_f32(x.numel(), x.data_ptr(), workspace.data_ptr(), _stream(x)))
+    return x
+
+
 def scan_static_(x: torch.Tensor) -> torch.Tensor:
     """In-place scan that allocates nothing: the look-back records live in a fixed array inside the
     library (at most 2^28 elements; calls that overlap on the GPU race -- see include/prism_b200.h)."""

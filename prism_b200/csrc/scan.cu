@@ -82,9 +82,18 @@ __device__ __forceinline__ uint32_t ld_flag(const uint32_t* p) {
     return v;
 }
 
+// Element arithmetic on 32-bit containers: wrap-around uint32 adds, or fp32 adds on the bit patterns
+// (F32).  The all-zero pattern is the identity of both.
+template <bool F32>
+__device__ __forceinline__ uint32_t eadd(uint32_t a, uint32_t b) {
+    if constexpr (F32) return __float_as_uint(__fadd_rn(__uint_as_float(a), __uint_as_float(b)));
+    else return a + b;
+}
+
+template <bool F32 = false>
 __device__ __forceinline__ uint32_t warp_sum(uint32_t v) {
 #pragma unroll
-    for (int d = 16; d > 0; d >>= 1) v += __shfl_xor_sync(0xffffffffu, v, d);
+    for (int d = 16; d > 0; d >>= 1) v = eadd<F32>(v, __shfl_xor_sync(0xffffffffu, v, d));
     return v;
 }
 
@@ -110,6 +119,7 @@ __device__ unsigned long long g_trace[8 * 65536];
 // lookback_to_prev_blocks, generated/lookback_to_prev_blocks.cu:8-25, done by a warp
 // instead of a thread and with bounded spins).  *failed is set if a poll ran out or
 // an abort was seen.
+template <bool F32>
 __device__ __forceinline__ uint32_t lookback(uint32_t tile, const uint64_t* desc, const uint32_t* abort_flag,
                                              bool* failed) {
     const int lane = threadIdx.x & 31;
@@ -144,10 +154,10 @@ __device__ __forceinline__ uint32_t lookback(uint32_t tile, const uint64_t* desc
         const unsigned has_prefix = __ballot_sync(0xffffffffu, state == kStatePrefix);
         if (has_prefix) {
             const int first = __ffs(has_prefix) - 1;  // nearest predecessor with a prefix
-            exclusive += warp_sum(lane <= first ? value : 0u);
+            exclusive = eadd<F32>(exclusive, warp_sum<F32>(lane <= first ? value : 0u));
             return exclusive;
         }
-        exclusive += warp_sum(value);
+        exclusive = eadd<F32>(exclusive, warp_sum<F32>(value));
         idx -= 32;
     }
 }
@@ -158,7 +168,7 @@ __device__ __forceinline__ uint32_t lookback(uint32_t tile, const uint64_t* desc
 //   kSeedPeers   the same sum, but each total arrives as a {epoch, total} word that the owning rank stores
 //                straight into this GPU's memory over NVLink; the look-back warp waits (bounded) until every
 //                rank's word carries this call's epoch
-enum { kSeedNone = 0, kSeedTotals = 1, kSeedPeers = 2 };
+enum { kSeedNone = 0, kSeedTotals = 1, kSeedPeers = 2, kSeedNoneF32 = 3 /* host-side selector of the fp32 kernel */ };
 
 __device__ __forceinline__ uint64_t ld_sys_u64(const uint64_t* p) {
     uint64_t v;
@@ -166,9 +176,10 @@ __device__ __forceinline__ uint64_t ld_sys_u64(const uint64_t* p) {
     return v;
 }
 
-template <int SEED>
+template <int SEED, bool F32 = false>
 __device__ __forceinline__ void scan_body(uint32_t n, uint32_t* x, uint32_t* header, uint64_t* desc,
                                           const void* seed_src, int rank, int world, uint32_t epoch) {
+    static_assert(!F32 || SEED == kSeedNone, "the sharded forms are uint32 only");
     constexpr int S = kSlots;
     extern __shared__ __align__(128) unsigned char p_smem[];
     uint32_t* slots = reinterpret_cast<uint32_t*>(p_smem);
@@ -280,7 +291,7 @@ __device__ __forceinline__ void scan_body(uint32_t n, uint32_t* x, uint32_t* hea
                     exclusive = warp_sum(lane < rank ? static_cast<uint32_t>(w >> 32) : 0u);
                 }
             } else {
-                exclusive = lookback(t, desc, header + 1, &failed);
+                exclusive = lookback<F32>(t, desc, header + 1, &failed);
             }
             if (lane == 0) {
                 if (failed) {
@@ -288,7 +299,7 @@ __device__ __forceinline__ void scan_body(uint32_t n, uint32_t* x, uint32_t* hea
                     atomicExch(header + 1, 1u);
                     raise_device_status(DEV_SCAN_LOOKBACK_TIMEOUT);
                 }
-                st_desc(desc + static_cast<size_t>(t) * kRecStride, kStatePrefix, exclusive + agg);  // as write_block_prefix.cu:8-10
+                st_desc(desc + static_cast<size_t>(t) * kRecStride, kStatePrefix, eadd<F32>(exclusive, agg));  // as write_block_prefix.cu:8-10
                 PRISM_TRACE(t, 4);   // prefix published
                 s_excl[s] = exclusive;
                 mbar_arrive(&pre_bar[s]);
@@ -379,9 +390,9 @@ __device__ __forceinline__ void scan_body(uint32_t n, uint32_t* x, uint32_t* hea
             uint32_t sum[kVecs], inc[kVecs];
 #pragma unroll
             for (int q = 0; q < kVecs; ++q) {
-                v[q].y += v[q].x;
-                v[q].z += v[q].y;
-                v[q].w += v[q].z;
+                v[q].y = eadd<F32>(v[q].y, v[q].x);
+                v[q].z = eadd<F32>(v[q].z, v[q].y);
+                v[q].w = eadd<F32>(v[q].w, v[q].z);
                 sum[q] = v[q].w;
                 inc[q] = sum[q];
             }
@@ -390,14 +401,19 @@ __device__ __forceinline__ void scan_body(uint32_t n, uint32_t* x, uint32_t* hea
 #pragma unroll
                 for (int q = 0; q < kVecs; ++q) {
                     const uint32_t up = __shfl_up_sync(0xffffffffu, inc[q], d);
-                    if (lane >= d) inc[q] += up;
+                    if (lane >= d) inc[q] = eadd<F32>(inc[q], up);
                 }
             }
             uint32_t chunk_off = 0, excl[kVecs];
 #pragma unroll
             for (int q = 0; q < kVecs; ++q) {
-                excl[q] = chunk_off + inc[q] - sum[q];
-                chunk_off += __shfl_sync(0xffffffffu, inc[q], 31);
+                if constexpr (F32) {   // no subtraction in floating point: the lane below's inclusive value
+                    const uint32_t below = __shfl_up_sync(0xffffffffu, inc[q], 1);
+                    excl[q] = eadd<F32>(chunk_off, lane == 0 ? 0u : below);
+                } else {
+                    excl[q] = chunk_off + inc[q] - sum[q];
+                }
+                chunk_off = eadd<F32>(chunk_off, __shfl_sync(0xffffffffu, inc[q], 31));
             }
             uint32_t* wt = s_warp_total + (i & 1u) * 8;
             if (lane == 0) wt[warp] = chunk_off;
@@ -406,8 +422,8 @@ __device__ __forceinline__ void scan_body(uint32_t n, uint32_t* x, uint32_t* hea
 #pragma unroll
             for (int w = 0; w < kScanThreads / 32; ++w) {
                 const uint32_t tot = wt[w];
-                if (w < warp) warp_off += tot;
-                aggregate += tot;
+                if (w < warp) warp_off = eadd<F32>(warp_off, tot);
+                aggregate = eadd<F32>(aggregate, tot);
             }
             if (tid == 0) {
                 if (t != 0) st_desc(desc + static_cast<size_t>(t) * kRecStride, kStateAggregate, aggregate);  // as write_block_aggregate.cu:8-10
@@ -418,8 +434,9 @@ __device__ __forceinline__ void scan_body(uint32_t n, uint32_t* x, uint32_t* hea
             // Tile-local inclusive scan back into the slot; the same lane reads it again in phase B.
 #pragma unroll
             for (int q = 0; q < kVecs; ++q) {
-                const uint32_t a = warp_off + excl[q];
-                v[q].x += a; v[q].y += a; v[q].z += a; v[q].w += a;
+                const uint32_t a = eadd<F32>(warp_off, excl[q]);
+                v[q].x = eadd<F32>(v[q].x, a); v[q].y = eadd<F32>(v[q].y, a);
+                v[q].z = eadd<F32>(v[q].z, a); v[q].w = eadd<F32>(v[q].w, a);
                 *reinterpret_cast<uint4*>(slot + vec0 + q * 128) = v[q];
             }
             ++i;
@@ -438,7 +455,8 @@ __device__ __forceinline__ void scan_body(uint32_t n, uint32_t* x, uint32_t* hea
             for (int q = 0; q < kVecs; ++q) {
                 const uint32_t e = vec0 + q * 128;
                 uint4 v = *reinterpret_cast<const uint4*>(slot + e);
-                v.x += add; v.y += add; v.z += add; v.w += add;
+                v.x = eadd<F32>(v.x, add); v.y = eadd<F32>(v.y, add);
+                v.z = eadd<F32>(v.z, add); v.w = eadd<F32>(v.w, add);
                 if (e + 4 <= cnt) {
                     __stcg(reinterpret_cast<uint4*>(x + base + e), v);
                 } else {
@@ -467,6 +485,15 @@ constexpr int kCtasPerSm = static_cast<int>((227 * 1024) / (kSmemBytes + 1024));
 __global__ void __launch_bounds__(kThreads, kCtasPerSm)
 scan_kernel(uint32_t n, uint32_t* x, uint32_t* block_idx_counter, int* block_infos) {
     scan_body<kSeedNone>(n, x, block_idx_counter, reinterpret_cast<uint64_t*>(block_infos), nullptr, 0, 1, 0);
+}
+
+// fp32 flavour of the same kernel (the reference scans uint32 only): same pipeline, fp32 adds.  The
+// grouping of the partial sums follows the look-back windows, which depend on timing, so results can
+// differ from run to run in the last bits, as with any floating-point decoupled look-back scan.
+__global__ void __launch_bounds__(kThreads, kCtasPerSm)
+scan_kernel_f32(uint32_t n, float* x, uint32_t* block_idx_counter, int* block_infos) {
+    scan_body<kSeedNone, true>(n, reinterpret_cast<uint32_t*>(x), block_idx_counter,
+                               reinterpret_cast<uint64_t*>(block_infos), nullptr, 0, 1, 0);
 }
 
 // Sharded form: tile 0 starts from totals[0] + ... + totals[rank-1].
@@ -561,6 +588,8 @@ int persistent_grid(unsigned* out) {
                                         static_cast<int>(kSmemBytes)));
     PRISM_CUDA_TRY(cudaFuncSetAttribute(scan_kernel_seeded, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         static_cast<int>(kSmemBytes)));
+    PRISM_CUDA_TRY(cudaFuncSetAttribute(scan_kernel_f32, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        static_cast<int>(kSmemBytes)));
     PRISM_CUDA_TRY(cudaFuncSetAttribute(scan_kernel_seeded_peers, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         static_cast<int>(kSmemBytes)));
     PRISM_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, scan_kernel, kThreads, kSmemBytes));
@@ -589,6 +618,9 @@ int scan_enqueue(size_t n, uint32_t* x, void* scratch, const void* seed_src, int
         scan_kernel_seeded<<<grid, kThreads, kSmemBytes, stream>>>(static_cast<uint32_t>(n), x, header,
                                                                    reinterpret_cast<int*>(desc),
                                                                    static_cast<const uint32_t*>(seed_src), rank);
+    else if (seed_mode == kSeedNoneF32)
+        scan_kernel_f32<<<grid, kThreads, kSmemBytes, stream>>>(static_cast<uint32_t>(n), reinterpret_cast<float*>(x), header,
+                                                                reinterpret_cast<int*>(desc));
     else
         scan_kernel<<<grid, kThreads, kSmemBytes, stream>>>(static_cast<uint32_t>(n), x, header,
                                                             reinterpret_cast<int*>(desc));
@@ -704,6 +736,11 @@ extern "C" int prism_b200_scan_workspace_size(size_t n, size_t* bytes) {
 
 extern "C" int prism_b200_scan(size_t n, uint32_t* x, void* workspace, void* stream) {
     return scan_launch(n, x, workspace, nullptr, 0, kSeedNone, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int prism_b200_scan_f32(size_t n, float* x, void* workspace, void* stream) {
+    return scan_launch(n, reinterpret_cast<uint32_t*>(x), workspace, nullptr, 0, kSeedNoneF32,
+                       static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int prism_b200_scan_seeded(size_t n, uint32_t* x, void* workspace, const uint32_t* totals, int rank,

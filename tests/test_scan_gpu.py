@@ -150,6 +150,36 @@ def test_sharded_pieces_compose(pb):
         assert np.array_equal(b.cpu().numpy().view(np.uint32), expect[cuts[r]:cuts[r + 1]]), r
 
 
+@pytest.mark.parametrize("n", [1, 5, 4096, 4097, 100003, 1 << 22])
+def test_scan_f32_exact_on_small_integers(pb, n):
+    """fp32 flavour on integer-valued data whose partial sums all stay below 2^24: every fp32 add is exact,
+    whatever the grouping, so the result must equal the running sum bit for bit."""
+    rng = np.random.default_rng(n)
+    x = rng.integers(0, 4, n).astype(np.float32)
+    t = torch.from_numpy(x.copy()).to(DEV)
+    pb.scan_f32_(t)
+    torch.cuda.synchronize()
+    assert np.array_equal(t.cpu().numpy().astype(np.float64), O.scan_f32_cpu(x))
+
+
+@pytest.mark.parametrize("n,signed", [(1000003, False), (1 << 20, True), (1 << 24, False)])
+def test_scan_f32_against_fp64(pb, n, signed):
+    """Random data against the fp64 running sum.  An output is reached through at most 24 fp32 adds inside its
+    tile (3 in a thread, 5 shuffle steps, 4 + 8 hand-offs, 2 offsets, the prefix) plus at most 2 per preceding tile
+    along the chain of look-backs (when every look-back finds its prefix one tile back); each add rounds by at
+    most 2^-24 of the running sum of |x|.  That worst case is the bound; typical errors are far below it."""
+    rng = np.random.default_rng(n + signed)
+    x = (rng.uniform(-1.0, 1.0, n) if signed else rng.uniform(0.0, 1.0, n)).astype(np.float32)
+    t = torch.from_numpy(x.copy()).to(DEV)
+    pb.scan_f32_(t)
+    torch.cuda.synchronize()
+    ref = O.scan_f32_cpu(x)
+    scale = np.cumsum(np.abs(x).astype(np.float64))
+    err = np.abs(t.cpu().numpy().astype(np.float64) - ref) / np.maximum(scale, 1.0)
+    tiles = -(-n // 4096)
+    assert err.max() <= (24 + 2 * tiles) * 2.0 ** -24, err.max()
+
+
 def test_scan_rejects_misaligned(pb):
     x = torch.zeros(1024, dtype=torch.int32, device=DEV)
     with pytest.raises(pb.PrismB200Error) as e:

@@ -120,6 +120,15 @@ int end_run(prism_b200_host_plan* p, cudaStream_t caller) {
     return PRISM_B200_OK;
 }
 
+// A kernel entry point refused mid-run: the copies already queued still run, so the caller's stream
+// is tied to the lanes as at the end of a normal run before the error goes back (the error state
+// keeps the kernel's message).
+int abandon_run(prism_b200_host_plan* p, cudaStream_t caller, int rc) {
+    for (int i = 0; i < 3; ++i)
+        if (cudaEventRecord(p->done[i], p->lane[i]) == cudaSuccess) cudaStreamWaitEvent(caller, p->done[i], 0);
+    return rc;
+}
+
 }  // namespace
 
 extern "C" int prism_b200_host_gemm_bf16_create(int M, int N, int K, int block_rows, prism_b200_host_plan** plan) {
@@ -153,7 +162,7 @@ extern "C" int prism_b200_host_gemm_bf16_run(prism_b200_host_plan* p, const uint
         if (int rc = prism_b200_gemm_bf16(p->M, static_cast<int>(rows), p->K, static_cast<const uint16_t*>(p->a),
                                           reinterpret_cast<const uint16_t*>(b_dev), reinterpret_cast<uint16_t*>(c_dev),
                                           p->lane[1]))
-            return rc;
+            return abandon_run(p, caller, rc);
         PRISM_CUDA_TRY(cudaEventRecord(p->computed[j], p->lane[1]));
         PRISM_CUDA_TRY(cudaStreamWaitEvent(p->lane[2], p->computed[j], 0));
         PRISM_CUDA_TRY(cudaMemcpyAsync(reinterpret_cast<char*>(C_host) + lo * row_c, c_dev, rows * row_c, cudaMemcpyDeviceToHost,
@@ -193,7 +202,7 @@ extern "C" int prism_b200_host_sgemm_run(prism_b200_host_plan* p, float alpha, c
         PRISM_CUDA_TRY(cudaStreamWaitEvent(p->lane[1], p->uploaded[j], 0));
         if (int rc = prism_b200_sgemm(p->kernel_id, static_cast<int>(rows), p->N, p->K, alpha, a_dev,
                                       static_cast<const float*>(p->b), beta, c_dev, p->lane[1]))
-            return rc;
+            return abandon_run(p, caller, rc);
         PRISM_CUDA_TRY(cudaEventRecord(p->computed[j], p->lane[1]));
         PRISM_CUDA_TRY(cudaStreamWaitEvent(p->lane[2], p->computed[j], 0));
         PRISM_CUDA_TRY(cudaMemcpyAsync(C_host + lo * N, c_dev, rows * N * 4, cudaMemcpyDeviceToHost, p->lane[2]));
@@ -234,7 +243,7 @@ extern "C" int prism_b200_host_scan_run(prism_b200_host_plan* p, uint32_t* x_hos
         PRISM_CUDA_TRY(cudaEventRecord(p->uploaded[j], p->lane[0]));
         PRISM_CUDA_TRY(cudaStreamWaitEvent(p->lane[1], p->uploaded[j], 0));
         // seed = totals[0] with rank 1: the carry word, i.e. the scanned last element of the block before
-        if (int rc = prism_b200_scan_seeded(hi - lo, x + lo, p->b, carry, 1, p->lane[1])) return rc;
+        if (int rc = prism_b200_scan_seeded(hi - lo, x + lo, p->b, carry, 1, p->lane[1])) return abandon_run(p, caller, rc);
         PRISM_CUDA_TRY(cudaMemcpyAsync(carry, x + hi - 1, 4, cudaMemcpyDeviceToDevice, p->lane[1]));
         PRISM_CUDA_TRY(cudaEventRecord(p->computed[j], p->lane[1]));
         PRISM_CUDA_TRY(cudaStreamWaitEvent(p->lane[2], p->computed[j], 0));

@@ -123,6 +123,16 @@ int prism_b200_scan(size_t n, uint32_t* x, void* workspace, void* stream);
 int prism_b200_scan_f32(size_t n, float* x, void* workspace, void* stream);
 
 /*
+ * The other flavours of the same kernel (no counterpart in the reference): separate input and
+ * output (in == out is allowed, partial overlap is not), inclusive or exclusive, uint32 or fp32
+ * adds.  Exclusive: out[0] = 0, out[i] = in[0] + ... + in[i-1].  Same workspace, limits and
+ * alignment as prism_b200_scan; flags = 0 with in == out is prism_b200_scan.
+ */
+#define PRISM_B200_SCAN_EXCLUSIVE 1
+#define PRISM_B200_SCAN_F32 2
+int prism_b200_scan_general(size_t n, const void* in, void* out, void* workspace, int flags, void* stream);
+
+/*
  * Sharded scan helpers (no counterpart in the reference, which is single-GPU).
  * A rank that owns the r-th contiguous chunk of a longer array
  *   1. prism_b200_reduce_u32: total of its chunk -> *total (device),

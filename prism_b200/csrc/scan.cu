@@ -176,8 +176,10 @@ __device__ __forceinline__ uint64_t ld_sys_u64(const uint64_t* p) {
     return v;
 }
 
-template <int SEED, bool F32 = false>
-__device__ __forceinline__ void scan_body(uint32_t n, uint32_t* x, uint32_t* header, uint64_t* desc,
+// `src` is read, `x` is written (the same pointer for the in-place entry points).  EXCL shifts the
+// result by one element: out[i] = in[0] + ... + in[i-1], out[0] = the seed.
+template <int SEED, bool F32 = false, bool EXCL = false>
+__device__ __forceinline__ void scan_body(uint32_t n, const uint32_t* src, uint32_t* x, uint32_t* header, uint64_t* desc,
                                           const void* seed_src, int rank, int world, uint32_t epoch) {
     static_assert(!F32 || SEED == kSeedNone, "the sharded forms are uint32 only");
     constexpr int S = kSlots;
@@ -240,7 +242,7 @@ __device__ __forceinline__ void scan_body(uint32_t n, uint32_t* x, uint32_t* hea
                 const uint32_t bytes = (cnt * 4u) & ~15u;  // whole 16-byte vectors; a ragged end is read by its owner
                 if (bytes) {
                     mbar_arrive_expect_tx(&full_bar[s], bytes);
-                    bulk_load_tile(slots + s * kTile, x + base, bytes, &full_bar[s]);
+                    bulk_load_tile(slots + s * kTile, src + base, bytes, &full_bar[s]);
                 } else {
                     mbar_arrive(&full_bar[s]);
                 }
@@ -379,10 +381,10 @@ __device__ __forceinline__ void scan_body(uint32_t n, uint32_t* x, uint32_t* hea
                 if (e + 4 <= (cnt & ~3u)) {
                     v[q] = *reinterpret_cast<const uint4*>(slot + e);
                 } else {  // the ragged end of the last tile: straight from global memory, zero beyond n
-                    v[q].x = (e + 0 < cnt) ? x[base + e + 0] : 0u;
-                    v[q].y = (e + 1 < cnt) ? x[base + e + 1] : 0u;
-                    v[q].z = (e + 2 < cnt) ? x[base + e + 2] : 0u;
-                    v[q].w = (e + 3 < cnt) ? x[base + e + 3] : 0u;
+                    v[q].x = (e + 0 < cnt) ? src[base + e + 0] : 0u;
+                    v[q].y = (e + 1 < cnt) ? src[base + e + 1] : 0u;
+                    v[q].z = (e + 2 < cnt) ? src[base + e + 2] : 0u;
+                    v[q].w = (e + 3 < cnt) ? src[base + e + 3] : 0u;
                 }
             }
             // Inside each 16-byte group, then across the 32 lanes of each of the four chunks
@@ -435,8 +437,13 @@ __device__ __forceinline__ void scan_body(uint32_t n, uint32_t* x, uint32_t* hea
 #pragma unroll
             for (int q = 0; q < kVecs; ++q) {
                 const uint32_t a = eadd<F32>(warp_off, excl[q]);
-                v[q].x = eadd<F32>(v[q].x, a); v[q].y = eadd<F32>(v[q].y, a);
-                v[q].z = eadd<F32>(v[q].z, a); v[q].w = eadd<F32>(v[q].w, a);
+                if constexpr (EXCL) {   // each element gets the sum of the ones before it
+                    v[q].w = eadd<F32>(v[q].z, a); v[q].z = eadd<F32>(v[q].y, a);
+                    v[q].y = eadd<F32>(v[q].x, a); v[q].x = a;
+                } else {
+                    v[q].x = eadd<F32>(v[q].x, a); v[q].y = eadd<F32>(v[q].y, a);
+                    v[q].z = eadd<F32>(v[q].z, a); v[q].w = eadd<F32>(v[q].w, a);
+                }
                 *reinterpret_cast<uint4*>(slot + vec0 + q * 128) = v[q];
             }
             ++i;
@@ -484,7 +491,7 @@ constexpr int kCtasPerSm = static_cast<int>((227 * 1024) / (kSmemBytes + 1024));
 
 __global__ void __launch_bounds__(kThreads, kCtasPerSm)
 scan_kernel(uint32_t n, uint32_t* x, uint32_t* block_idx_counter, int* block_infos) {
-    scan_body<kSeedNone>(n, x, block_idx_counter, reinterpret_cast<uint64_t*>(block_infos), nullptr, 0, 1, 0);
+    scan_body<kSeedNone>(n, x, x, block_idx_counter, reinterpret_cast<uint64_t*>(block_infos), nullptr, 0, 1, 0);
 }
 
 // fp32 flavour of the same kernel (the reference scans uint32 only): same pipeline, fp32 adds.  The
@@ -492,22 +499,30 @@ scan_kernel(uint32_t n, uint32_t* x, uint32_t* block_idx_counter, int* block_inf
 // differ from run to run in the last bits, as with any floating-point decoupled look-back scan.
 __global__ void __launch_bounds__(kThreads, kCtasPerSm)
 scan_kernel_f32(uint32_t n, float* x, uint32_t* block_idx_counter, int* block_infos) {
-    scan_body<kSeedNone, true>(n, reinterpret_cast<uint32_t*>(x), block_idx_counter,
+    scan_body<kSeedNone, true>(n, reinterpret_cast<uint32_t*>(x), reinterpret_cast<uint32_t*>(x), block_idx_counter,
                                reinterpret_cast<uint64_t*>(block_infos), nullptr, 0, 1, 0);
+}
+
+// General flavour (no counterpart in the reference): separate input and output, inclusive or exclusive,
+// uint32 or fp32 adds.  in == out is allowed.
+template <bool F32, bool EXCL>
+__global__ void __launch_bounds__(kThreads, kCtasPerSm)
+scan_kernel_general(uint32_t n, const uint32_t* in, uint32_t* out, uint32_t* block_idx_counter, int* block_infos) {
+    scan_body<kSeedNone, F32, EXCL>(n, in, out, block_idx_counter, reinterpret_cast<uint64_t*>(block_infos), nullptr, 0, 1, 0);
 }
 
 // Sharded form: tile 0 starts from totals[0] + ... + totals[rank-1].
 __global__ void __launch_bounds__(kThreads, kCtasPerSm)
 scan_kernel_seeded(uint32_t n, uint32_t* x, uint32_t* block_idx_counter, int* block_infos, const uint32_t* totals,
                    int rank) {
-    scan_body<kSeedTotals>(n, x, block_idx_counter, reinterpret_cast<uint64_t*>(block_infos), totals, rank, 1, 0);
+    scan_body<kSeedTotals>(n, x, x, block_idx_counter, reinterpret_cast<uint64_t*>(block_infos), totals, rank, 1, 0);
 }
 
 // Sharded form without a collective call: the totals arrive as {epoch, total} words stored by the peers.
 __global__ void __launch_bounds__(kThreads, kCtasPerSm)
 scan_kernel_seeded_peers(uint32_t n, uint32_t* x, uint32_t* block_idx_counter, int* block_infos,
                          const uint64_t* slots, int rank, int world, uint32_t epoch) {
-    scan_body<kSeedPeers>(n, x, block_idx_counter, reinterpret_cast<uint64_t*>(block_infos), slots, rank, world, epoch);
+    scan_body<kSeedPeers>(n, x, x, block_idx_counter, reinterpret_cast<uint64_t*>(block_infos), slots, rank, world, epoch);
 }
 
 // Stores this rank's {epoch, total} word into every rank's slot array (its own included) with one
@@ -590,6 +605,14 @@ int persistent_grid(unsigned* out) {
                                         static_cast<int>(kSmemBytes)));
     PRISM_CUDA_TRY(cudaFuncSetAttribute(scan_kernel_f32, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         static_cast<int>(kSmemBytes)));
+    PRISM_CUDA_TRY(cudaFuncSetAttribute(scan_kernel_general<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        static_cast<int>(kSmemBytes)));
+    PRISM_CUDA_TRY(cudaFuncSetAttribute(scan_kernel_general<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        static_cast<int>(kSmemBytes)));
+    PRISM_CUDA_TRY(cudaFuncSetAttribute(scan_kernel_general<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        static_cast<int>(kSmemBytes)));
+    PRISM_CUDA_TRY(cudaFuncSetAttribute(scan_kernel_general<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        static_cast<int>(kSmemBytes)));
     PRISM_CUDA_TRY(cudaFuncSetAttribute(scan_kernel_seeded_peers, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         static_cast<int>(kSmemBytes)));
     PRISM_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, scan_kernel, kThreads, kSmemBytes));
@@ -643,6 +666,40 @@ int scan_launch(size_t n, uint32_t* x, void* workspace, const void* seed_src, in
         return set_error(PRISM_B200_ERR_INVALID_ARGUMENT, "scan_seeded_peers: need slots, 1 <= world <= 32, a rank below world and a non-zero epoch");
     if (int rc = bind_status_word()) return rc;
     return scan_enqueue(n, x, workspace, seed_src, rank, seed_mode, stream, world, epoch);
+}
+
+// The general flavour: same re-arming and grid as scan_enqueue.
+int scan_general_launch(size_t n, const uint32_t* in, uint32_t* out, void* workspace, int flags, cudaStream_t stream) {
+    if (flags & ~(PRISM_B200_SCAN_EXCLUSIVE | PRISM_B200_SCAN_F32))
+        return set_error(PRISM_B200_ERR_INVALID_ARGUMENT, "scan_general: unknown flag bits 0x%x", flags);
+    if (n == 0) return PRISM_B200_OK;
+    if (!in || !out || !workspace) return set_error(PRISM_B200_ERR_INVALID_ARGUMENT, "scan_general: null pointer");
+    if (n >= (1ull << 32)) return set_error(PRISM_B200_ERR_TOO_LARGE, "scan_general: n=%zu must be below 2^32", n);
+    if ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(workspace)) & 15u)
+        return set_error(PRISM_B200_ERR_MISALIGNED, "scan_general: in, out and workspace must be 16-byte aligned");
+    if (in != out) {
+        const uintptr_t a = reinterpret_cast<uintptr_t>(in), b = reinterpret_cast<uintptr_t>(out);
+        if (a < b + n * 4 && b < a + n * 4)
+            return set_error(PRISM_B200_ERR_INVALID_ARGUMENT, "scan_general: in and out overlap without being equal");
+    }
+    if (int rc = bind_status_word()) return rc;
+    const uint32_t tiles = static_cast<uint32_t>(scan_tiles(n));
+    uint32_t* header = static_cast<uint32_t*>(workspace);
+    int* desc = reinterpret_cast<int*>(static_cast<char*>(workspace) + kHeaderBytes);
+    unsigned grid = 0;
+    if (int rc = persistent_grid(&grid)) return rc;
+    if (grid > tiles) grid = tiles;
+    PRISM_CUDA_TRY(cudaMemsetAsync(workspace, 0, kHeaderBytes + static_cast<size_t>(tiles) * kRecStride * sizeof(uint64_t), stream));
+    const uint32_t n32 = static_cast<uint32_t>(n);
+    switch (flags) {
+    case 0: scan_kernel_general<false, false><<<grid, kThreads, kSmemBytes, stream>>>(n32, in, out, header, desc); break;
+    case PRISM_B200_SCAN_EXCLUSIVE: scan_kernel_general<false, true><<<grid, kThreads, kSmemBytes, stream>>>(n32, in, out, header, desc); break;
+    case PRISM_B200_SCAN_F32: scan_kernel_general<true, false><<<grid, kThreads, kSmemBytes, stream>>>(n32, in, out, header, desc); break;
+    default: scan_kernel_general<true, true><<<grid, kThreads, kSmemBytes, stream>>>(n32, in, out, header, desc); break;
+    }
+    PRISM_CUDA_TRY(cudaGetLastError());
+    count_launch();
+    return PRISM_B200_OK;
 }
 
 unsigned streaming_grid(size_t n4) {
@@ -741,6 +798,11 @@ extern "C" int prism_b200_scan(size_t n, uint32_t* x, void* workspace, void* str
 extern "C" int prism_b200_scan_f32(size_t n, float* x, void* workspace, void* stream) {
     return scan_launch(n, reinterpret_cast<uint32_t*>(x), workspace, nullptr, 0, kSeedNoneF32,
                        static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int prism_b200_scan_general(size_t n, const void* in, void* out, void* workspace, int flags, void* stream) {
+    return scan_general_launch(n, static_cast<const uint32_t*>(in), static_cast<uint32_t*>(out), workspace, flags,
+                               static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int prism_b200_scan_seeded(size_t n, uint32_t* x, void* workspace, const uint32_t* totals, int rank,

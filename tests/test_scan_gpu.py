@@ -180,6 +180,42 @@ def test_scan_f32_against_fp64(pb, n, signed):
     assert err.max() <= (24 + 2 * tiles) * 2.0 ** -24, err.max()
 
 
+@pytest.mark.parametrize("n", [1, 4, 4097, 100003, 1 << 22])
+@pytest.mark.parametrize("exclusive", [False, True])
+def test_scan_general_out_of_place_and_exclusive(pb, n, exclusive):
+    """Separate output and the exclusive form, uint32: bit-exact against the oracle (exclusive = inclusive shifted
+    by one element with a leading zero); the input is left untouched; in == out works as well."""
+    x = O.scan_inputs(n, seed=n + exclusive, high=1 << 30)
+    inc = O.scan_cpu(x)
+    want = np.concatenate([np.zeros(1, np.uint32), inc[:-1]]) if exclusive else inc
+    t = torch.from_numpy(x.view(np.int32).copy()).to(DEV)
+    out = pb.scan(t, exclusive=exclusive)
+    torch.cuda.synchronize()
+    assert np.array_equal(out.cpu().numpy().view(np.uint32), want)
+    assert np.array_equal(t.cpu().numpy().view(np.uint32), x)
+    pb.scan(t, out=t, exclusive=exclusive)
+    torch.cuda.synchronize()
+    assert np.array_equal(t.cpu().numpy().view(np.uint32), want)
+
+
+def test_scan_general_f32_exclusive(pb):
+    n = 300007
+    x = np.random.default_rng(3).integers(0, 4, n).astype(np.float32)     # exact in fp32
+    out = pb.scan(torch.from_numpy(x).to(DEV), exclusive=True)
+    torch.cuda.synchronize()
+    want = np.concatenate([[0.0], O.scan_f32_cpu(x)[:-1]])
+    assert np.array_equal(out.cpu().numpy().astype(np.float64), want)
+
+
+def test_scan_general_rejects_partial_overlap(pb):
+    buf = torch.zeros(4096 + 8, dtype=torch.int32, device=DEV)
+    ws = pb.scan_workspace(4096, DEV)
+    import prism_b200._lib as L
+    rc = L.load().prism_b200_scan_general(4096, buf.data_ptr(), buf.data_ptr() + 16, ws.data_ptr(), 0, None)
+    assert rc == 1 and "overlap" in pb.last_error()[1]
+    pb.clear_error()
+
+
 def test_scan_rejects_misaligned(pb):
     x = torch.zeros(1024, dtype=torch.int32, device=DEV)
     with pytest.raises(pb.PrismB200Error) as e:

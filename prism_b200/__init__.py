@@ -24,7 +24,7 @@ from ._lib import PrismB200Error, last_error, load  # noqa: F401
 
 __all__ = [
     "run_my_kernel", "get_workspace_size", "launch_scan", "runmyh100",
-    "sgemm", "scan_", "scan_static_", "scan_workspace", "gemm_bf16", "reduce_u32", "scan_seeded_", "scan_add_carry_",
+    "sgemm", "scan_", "scan", "scan_f32_", "scan_static_", "scan_workspace", "gemm_bf16", "reduce_u32", "scan_seeded_", "scan_add_carry_",
     "scan_publish_total", "scan_seeded_peers_",
     "launch_count", "last_error", "clear_error", "version", "PrismB200Error",
 ]
@@ -241,15 +241,22 @@ def runmyh100(M: int, N: int, K: int, A: torch.Tensor, B: torch.Tensor, C: torch
                                                _stream(C)))
 
 
-def gemm_bf16(A: torch.Tensor, B: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
-    """Returns C^T as an (N, M) row-major tensor, i.e. the reference's column-major M x N C.
+def gemm_bf16(A: torch.Tensor, B: torch.Tensor, out: torch.Tensor | None = None, row_major: bool = False) -> torch.Tensor:
+    """A @ B.T for A (M, K) and B (N, K), bf16 with fp32 accumulation.
 
-    `out.t()` is the M x N product A @ B.T.
+    By default returns C^T as an (N, M) row-major tensor, i.e. the reference's column-major M x N C
+    (`out.t()` is the product).  row_major=True returns the (M, N) row-major product itself: the same
+    kernel with the two operands exchanged.
     """
     M, K = A.shape
     N, K2 = B.shape
     if K2 != K:
         raise ValueError(f"K mismatch: A {tuple(A.shape)}, B {tuple(B.shape)}")
+    if row_major:
+        if out is None:
+            out = torch.empty((M, N), dtype=torch.bfloat16, device=A.device)
+        runmyh100(N, M, K, B, A, out)
+        return out
     if out is None:
         out = torch.empty((N, M), dtype=torch.bfloat16, device=A.device)
     runmyh100(M, N, K, A, B, out)

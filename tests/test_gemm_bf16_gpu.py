@@ -111,6 +111,20 @@ def test_many_tiles_per_cta_4096(pb):
     assert np.all(np.abs(out[rows] - ref) <= 1e-2 * np.abs(ref) + 1e-2 * rms)
 
 
+def test_row_major_output_is_the_exchanged_call(pb):
+    M, N, K = 384, 640, 192
+    A, B = O.gemm_bf16_inputs(M, N, K, seed=21)
+    a = torch.from_numpy(A.view(np.int16)).view(torch.bfloat16).to(DEV)
+    b = torch.from_numpy(B.view(np.int16)).view(torch.bfloat16).to(DEV)
+    col = pb.gemm_bf16(a, b)                     # (N, M): the reference's column-major C
+    row = pb.gemm_bf16(a, b, row_major=True)     # (M, N)
+    torch.cuda.synchronize()
+    assert row.shape == (M, N) and torch.equal(row, col.t())
+    ref = O.gemm_bf16_cpu(A, B).T
+    rms = float(np.sqrt(np.mean(ref * ref)))
+    assert np.all(np.abs(row.float().cpu().numpy() - ref) <= 1e-2 * np.abs(ref) + 1e-2 * rms)
+
+
 def test_benchmark_size_8192(pb):
     """8192^3, the headline configuration (512 x 256 two-CTA tiles, 6.9 waves): sampled rows against fp64
     and the full-size symmetry C(A, B)^T == C(B, A), which the swapped call computes with the roles of the

@@ -24,3 +24,14 @@ def test_reference_arm_prints_one_json_line(workload):
     assert d["cpu_baseline"]["kind"] in ("port", "reference") and d["cpu_baseline"]["cores"] >= 1
     assert d["e2e"]["h2d_bytes_per_step"] == 0 and d["e2e"]["d2h_bytes_per_step"] == 0
     assert "workload" in d["config"]
+
+
+def test_own_arm_fails_loudly_without_a_gpu():
+    """There is no CPU path: without a CUDA device the kernel arm must exit non-zero and say why."""
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a CUDA device is present")
+    r = subprocess.run([sys.executable, str(ROOT / "bench.py"), "--steps", "1", "--warmup", "1"], capture_output=True,
+                       text=True, timeout=300)
+    assert r.returncode != 0
+    assert "no CPU path" in r.stdout

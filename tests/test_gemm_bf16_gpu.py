@@ -64,6 +64,16 @@ print('ok', worst)
 """
 
 
+def test_random_shapes_match_fp64_oracle(pb):
+    """Twelve seeded random shapes (M, N multiples of 128, K of 64, up to 1536 x 1536 x 1024)."""
+    rng = np.random.default_rng(2718)
+    for _ in range(12):
+        M, N, K = (int(rng.integers(1, 13)) * 128, int(rng.integers(1, 13)) * 128, int(rng.integers(1, 17)) * 64)
+        A, B = O.gemm_bf16_inputs(M, N, K, seed=M + 13 * N + 131 * K)
+        ok, worst = O.gemm_bf16_check(_run(pb, A, B), O.gemm_bf16_cpu(A, B))
+        assert ok, f"{(M, N, K)}: worst error / bound = {worst}"
+
+
 @pytest.mark.parametrize("mode,shapes", [
     # one-CTA kernels only
     ("0", [(256, 256, 128), (1024, 1024, 512), (2048, 4096, 256)]),

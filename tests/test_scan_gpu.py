@@ -216,6 +216,23 @@ def test_scan_general_rejects_partial_overlap(pb):
     pb.clear_error()
 
 
+def test_scan_random_sizes_all_flavours(pb):
+    """Thirty seeded random sizes up to 2^21 with full-range values: in place, separate output, exclusive."""
+    rng = np.random.default_rng(57721)
+    for _ in range(30):
+        n = int(rng.integers(1, 1 << 21))
+        x = rng.integers(0, 1 << 32, n, dtype=np.uint64).astype(np.uint32)
+        inc = O.scan_cpu(x)
+        t = torch.from_numpy(x.view(np.int32).copy()).to(DEV)
+        ex = pb.scan(t, exclusive=True)
+        out = pb.scan(t)
+        pb.scan_(t)
+        torch.cuda.synchronize()
+        assert np.array_equal(t.cpu().numpy().view(np.uint32), inc), n
+        assert np.array_equal(out.cpu().numpy().view(np.uint32), inc), n
+        assert np.array_equal(ex.cpu().numpy().view(np.uint32), np.concatenate([np.zeros(1, np.uint32), inc[:-1]])), n
+
+
 def test_scan_rejects_misaligned(pb):
     x = torch.zeros(1024, dtype=torch.int32, device=DEV)
     with pytest.raises(pb.PrismB200Error) as e:

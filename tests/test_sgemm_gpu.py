@@ -107,6 +107,29 @@ def test_ragged_shapes_every_kernel(pb, k, shape):
     assert O.sgemm_rel_error(out, O.sgemm_cpu(1.5, A, B, 0.5, C)) <= O.SGEMM_TOL
 
 
+def test_random_ragged_shapes(pb):
+    """Twenty seeded random shapes up to 400 x 400 x 300, every kernel id, random alpha and beta."""
+    rng = np.random.default_rng(31415)
+    for it in range(20):
+        M, N, K = (int(v) for v in rng.integers(1, (401, 401, 301)))
+        alpha, beta = float(rng.uniform(-2, 2)), float(rng.uniform(-2, 2))
+        A, B, C = O.sgemm_inputs(M, N, K, seed=1000 + it)
+        ref = O.sgemm_cpu(alpha, A, B, beta, C)
+        for k in KERNELS:
+            out = _run(pb, k, alpha, A, B, beta, C)
+            assert O.sgemm_rel_error(out, ref) <= O.SGEMM_TOL, (k, M, N, K)
+
+
+def test_kernel5_random_tiled_shapes(pb):
+    """Shapes that kernel 5's tiled forms take (M, N multiples of 128, K of 16), both tile forms."""
+    rng = np.random.default_rng(1618)
+    for it in range(8):
+        M, N, K = int(rng.integers(1, 12)) * 128, int(rng.integers(1, 12)) * 128, int(rng.integers(1, 20)) * 16
+        A, B, C = O.sgemm_inputs(M, N, K, seed=2000 + it)
+        out = _run(pb, 5, 1.5, A, B, 0.5, C)
+        assert O.sgemm_rel_error(out, O.sgemm_cpu(1.5, A, B, 0.5, C)) <= O.SGEMM_TOL, (M, N, K)
+
+
 def test_linearity_at_4096(pb):
     """Benchmark size, checked without an fp64 4096^3 product: rows sampled against fp64, plus
     C(alpha=2, beta=0) == 2 * C(alpha=1, beta=0) exactly (scaling by 2 is exact in fp32)."""

@@ -626,9 +626,11 @@ cutlass_my_h100_match_no_tail_pair(int M, int N, int K, __nv_bfloat16* C, const 
 // MACs per CTA, against 32 KB for half of that in the form above).  Shared-memory and
 // L2 traffic per flop drop by a quarter, which is what lets the tensor pipe stay busy.
 // The two accumulators take all 512 tensor-memory columns, so they cannot be
-// double-buffered: the epilogue of a tile is not hidden behind the next main loop.  It
-// is kept short instead -- eight epilogue warps, two per lane quarter, one accumulator
-// each -- and the producer already prefetches the next tile's stages while it runs.
+// double-buffered.  Instead the part of the epilogue that holds tensor memory is kept
+// short: eight epilogue warps, two per lane quarter, one accumulator each, first move
+// their rows into registers as packed bf16 (128 registers per lane) and hand tensor
+// memory back; the next tile's MMAs then run while the rows go through shared memory to
+// global memory.  The producer prefetches the next tile's stages throughout.
 // Barriers and pairing are as in the kernel above.
 // ============================================================================
 namespace g16 {
@@ -801,19 +803,30 @@ cutlass_my_h100_match_no_tail_pair_wide(int M, int N, int K, __nv_bfloat16* C,
             __nv_bfloat16* c_warp = C + n_warp * static_cast<size_t>(M) + static_cast<size_t>(tm) * W_::TILE_M;
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(block * 256);
             unsigned char* stage_buf = epi_smem + (warp - 2) * W_::EPI_WARP_BYTES;
-            for (int c0 = 0; c0 < W_::TILE_M; c0 += 64) {
-                uint32_t r0[32], r1[32];
-                tmem_ld_32cols(t_row + c0, r0);
-                tmem_ld_32cols(t_row + c0 + 32, r1);
+            // The whole accumulator row first goes into registers as packed bf16 (256 columns = 128
+            // registers), so that tensor memory can be handed back and the next tile's MMAs start
+            // while this tile is still on its way to global memory.
+            uint32_t packed[W_::TILE_M / 2];
+#pragma unroll
+            for (int c0 = 0; c0 < W_::TILE_M; c0 += 32) {
+                uint32_t r[32];
+                tmem_ld_32cols(t_row + c0, r);
                 tmem_ld_wait();
 #pragma unroll
+                for (int e = 0; e < 16; ++e) packed[c0 / 2 + e] = pack_bf16(r[2 * e], r[2 * e + 1]);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(cluster_addr(acc_empty_bar, 0));
+#pragma unroll
+            for (int c0 = 0; c0 < W_::TILE_M; c0 += 64) {
+#pragma unroll
                 for (int ch = 0; ch < 8; ++ch) {
-                    const uint32_t* r = ch < 4 ? &r0[8 * ch] : &r1[8 * (ch - 4)];
                     uint4 o;
-                    o.x = pack_bf16(r[0], r[1]);
-                    o.y = pack_bf16(r[2], r[3]);
-                    o.z = pack_bf16(r[4], r[5]);
-                    o.w = pack_bf16(r[6], r[7]);
+                    o.x = packed[c0 / 2 + 4 * ch + 0];
+                    o.y = packed[c0 / 2 + 4 * ch + 1];
+                    o.z = packed[c0 / 2 + 4 * ch + 2];
+                    o.w = packed[c0 / 2 + 4 * ch + 3];
                     *reinterpret_cast<uint4*>(stage_buf + lane * 128 + ((ch ^ (lane & 7)) << 4)) = o;
                 }
                 __syncwarp();
@@ -826,9 +839,6 @@ cutlass_my_h100_match_no_tail_pair_wide(int M, int N, int K, __nv_bfloat16* C,
                 }
                 __syncwarp();
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(cluster_addr(acc_empty_bar, 0));
             tile_phase ^= 1u;
         }
     }

@@ -42,7 +42,7 @@ SCAN_NG = 1 << 30
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel,
 # from the ncu captures whose summaries sit in the profiles/ folder (None = not captured).
 NCU_TRAFFIC_BYTES = {
-    "gemm_bf16": 970.5e6,   # 8192^3: 850.5 MB read + 120.0 MB written
+    "gemm_bf16": 1007.4e6,  # 8192^3: 880.4 MB read + 127.0 MB written
     "sgemm": 640.5e6,       # 4096^3: 579.5 MB read + 61.0 MB written
     "scan": 1919.3e6,       # 2^28: 4 x the 479.8 MB captured at 2^26
 }

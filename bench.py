@@ -282,7 +282,9 @@ def run_gemm_bf16(args, world, rank, peaks):
     kernel_ms = sum(per) / len(per)     # this rank's kernel: rows x S x S
     achieved = 2.0 * rows * S * S / (kernel_ms * 1e-3) / 1e12
     peak = peaks["bf16_tflops"]
-    roofline = {"bound": "tensor", "kernel": "cutlass_my_h100_match_no_tail<256> (tcgen05)", "achieved": achieved,
+    roofline = {"bound": "tensor", "kernel": ("cutlass_my_h100_match_no_tail_pair_wide<16> (tcgen05, cta_group::2, 512 x 256 tiles)"
+                           if (rows % 256 == 0 and S % 512 == 0 and rows * S * S >= 2 ** 35)
+                           else "cutlass_my_h100_match_no_tail family (tcgen05), form chosen by shape"), "achieved": achieved,
                 "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                 "peak_source": f"{peaks['source']} cuBLAS bf16 burst", "frac_of_sustained": achieved / peaks["bf16_tflops_sustained"],
                 "frac_of_nominal_2250": achieved / 2250.0,

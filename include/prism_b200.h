@@ -151,18 +151,34 @@ int prism_b200_scan_add_carry(size_t n, uint32_t* x, const uint32_t* totals,
 /*
  * The same exchange without a collective call, over peer memory (NVLink / NVSwitch).  Every rank
  * owns an array `slots` of 2 * world 64-bit words that all ranks can write (peer-mapped or
- * symmetric memory, zeroed once).  Per call, with a non-zero `epoch` that changes from call to call
- * (1, 2, 3, ...) and is the same on every rank:
- *   1. prism_b200_reduce_u32: total of the chunk,
- *   2. prism_b200_scan_publish_total: stores {epoch, total} into slot (epoch & 1) * world + rank of
- *      EVERY rank's array; peer_slots is a device array of the world base addresses,
- *   3. prism_b200_scan_seeded_peers: scans the chunk; the first tile waits (bounded, 1 s) until all
- *      world words of this epoch have arrived in its own array and starts from the sum of the lower
- *      ranks' totals.
+ * symmetric memory, zeroed once); `peer_slots` is a device array of the `world` base addresses of
+ * these arrays, in rank order.  `epoch` is non-zero, the same on every rank, and changes from call
+ * to call (1, 2, 3, ...).
+ *
+ * prism_b200_scan_sharded does the whole step in ONE launch.  phases = 3:
+ *   reduce   the CTAs add up the chunk slice by slice (last slice first, so that the start of the
+ *            chunk is what remains in L2); whoever finishes the last slice stores {epoch, total}
+ *            into slot (epoch & 1) * world + rank of EVERY rank's array, one 64-bit store each;
+ *   scan     the chunk is scanned in place; its first tile waits until all `world` words of this
+ *            epoch have arrived in this rank's own array and starts from the sum of the lower
+ *            ranks' totals.
+ * phases = 1 or 2 runs one of the two alone (a reduce-only launch on every rank, then a scan-only
+ * launch on every rank, is the same computation in two launches).
+ * The wait for the words is bounded by wait_limit_ns (0 = 1 s, at most 600 s): ranks that enter the
+ * call further apart than that give up, set PRISM_B200_ERR_DEVICE_TIMEOUT (see prism_b200_last_error,
+ * after synchronising) and leave x undefined, where a collective would have waited.  Pick the limit
+ * for the skew the job can have.  An empty chunk (n = 0) still publishes a zero total and waits.
  * Waiting for every rank's word, together with the two alternating halves of the array, is what
- * makes it safe for a rank to run a whole call ahead of another.  world <= 32.  No counterpart in
- * the reference.
+ * makes it safe for a rank to run a whole call ahead of another.  world <= 32.
+ * The pieces are also exported on their own: prism_b200_scan_publish_total stores the word for a
+ * total computed elsewhere (prism_b200_reduce_u32), prism_b200_scan_seeded_peers is phases = 2
+ * with the default limit.  No counterpart in the reference.
  */
+#define PRISM_B200_SHARD_REDUCE 1
+#define PRISM_B200_SHARD_SCAN 2
+int prism_b200_scan_sharded(size_t n, uint32_t* x, void* workspace, const uint64_t* slots,
+                            uint64_t* const* peer_slots, int rank, int world, uint32_t epoch, int phases,
+                            unsigned long long wait_limit_ns, void* stream);
 int prism_b200_scan_publish_total(const uint32_t* total, uint64_t* const* peer_slots, int world,
                                   int rank, uint32_t epoch, void* stream);
 int prism_b200_scan_seeded_peers(size_t n, uint32_t* x, void* workspace, const uint64_t* slots,
@@ -201,7 +217,7 @@ int prism_b200_scan_static(size_t n, uint32_t* x, void* stream);
  * A is M x K and B is N x K, both K-major (row-major) bf16; C is M x N bf16 stored
  * COLUMN-major, C[n * M + m], as the reference kernel writes it
  * (generated/cutlass_my_h100_match_no_tail.cu:313,347-354).  fp32 accumulation,
- * round-to-nearest-even on store.  Requires M % 128 == 0, N % 128 == 0, K % 64 == 0
+ * round-to-nearest-even on store.  Requires M % 128 == 0, N % 128 == 0, K % 64 == 0, K > 0
  * (the reference needs M % 2048 == 0, N % 2048 == 0, K % 256 == 0).
  * Tensor maps are cached on (device, pointer, rows, K) so a new buffer never reuses a
  * stale map (the reference caches on M alone, utils.cuh:512-518).

@@ -25,7 +25,7 @@ from ._lib import PrismB200Error, last_error, load  # noqa: F401
 __all__ = [
     "run_my_kernel", "get_workspace_size", "launch_scan", "runmyh100",
     "sgemm", "scan_", "scan", "scan_f32_", "scan_static_", "scan_workspace", "gemm_bf16", "reduce_u32", "scan_seeded_", "scan_add_carry_",
-    "scan_publish_total", "scan_seeded_peers_",
+    "scan_publish_total", "scan_seeded_peers_", "scan_sharded_",
     "launch_count", "last_error", "clear_error", "version", "PrismB200Error",
 ]
 
@@ -212,6 +212,26 @@ def scan_seeded_peers_(x: torch.Tensor, workspace: torch.Tensor, slots: torch.Te
     with torch.cuda.device(x.device):
         _lib.check(load().prism_b200_scan_seeded_peers(x.numel(), x.data_ptr(), workspace.data_ptr(), slots.data_ptr(),
                                                        int(rank), int(world), int(epoch), _stream(x)))
+    return x
+
+
+def scan_sharded_(x: torch.Tensor, workspace: torch.Tensor, slots: torch.Tensor, peer_slots_dev: int, rank: int,
+                  world: int, epoch: int, phases: int = 3, wait_limit_s: float = 0.0) -> torch.Tensor:
+    """One launch of the sharded scan over peer memory: reduce the chunk and store its {epoch, total} word into
+    every rank's `slots` (phases & 1), scan it in place starting from the lower ranks' totals (phases & 2).
+    `wait_limit_s` bounds the wait for the other ranks' words (0 = the library's default of 1 s).  An empty
+    chunk is allowed: it still publishes and waits."""
+    _require_cuda("x", x, _SCAN_DTYPES)
+    _require_cuda("workspace", workspace)
+    _require_cuda("slots", slots, torch.int64)
+    if slots.numel() < 2 * world:
+        raise ValueError("slots must hold 2 * world words")
+    if workspace.numel() * workspace.element_size() < get_workspace_size(x.numel()):
+        raise ValueError("workspace too small; see get_workspace_size(n)")
+    with torch.cuda.device(x.device):
+        _lib.check(load().prism_b200_scan_sharded(x.numel(), x.data_ptr() if x.numel() else None, workspace.data_ptr(),
+                                                  slots.data_ptr(), ctypes.c_void_p(int(peer_slots_dev)), int(rank),
+                                                  int(world), int(epoch), int(phases), int(wait_limit_s * 1e9), _stream(x)))
     return x
 
 

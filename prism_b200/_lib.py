@@ -40,6 +40,8 @@ SIGNATURES = {
     "prism_b200_scan_add_carry": (c_int, [c_size_t, c_void_p, c_void_p, c_int, c_void_p]),
     "prism_b200_scan_publish_total": (c_int, [c_void_p, c_void_p, c_int, c_int, ctypes.c_uint32, c_void_p]),
     "prism_b200_scan_seeded_peers": (c_int, [c_size_t, c_void_p, c_void_p, c_void_p, c_int, c_int, ctypes.c_uint32, c_void_p]),
+    "prism_b200_scan_sharded": (c_int, [c_size_t, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, ctypes.c_uint32, c_int,
+                                        c_ulonglong, c_void_p]),
     "prism_b200_scan_static": (c_int, [c_size_t, c_void_p, c_void_p]),
     "prism_b200_gemm_bf16": (c_int, [c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     "prism_b200_host_gemm_bf16_create": (c_int, [c_int, c_int, c_int, c_int, POINTER(c_void_p)]),
@@ -73,9 +75,10 @@ def load(build_if_missing: bool = True) -> ctypes.CDLL:
     if _lib is not None:
         return _lib
     path = _build.LIB_PATH
-    if not path.exists():
+    if _build.stale():
+        # A library built from other sources than the ones in the tree is never loaded silently.
         if not build_if_missing:
-            raise FileNotFoundError(f"{path} is missing; run `python -m prism_b200.build`")
+            raise FileNotFoundError(f"{path} is missing or older than its sources; run `python -m prism_b200.build`")
         _build.build_library()
     lib = ctypes.CDLL(str(path))
     for name, (res, args) in SIGNATURES.items():

@@ -39,17 +39,33 @@ def sources() -> list[Path]:
     return [CSRC / s for s in SOURCES if (CSRC / s).exists()]
 
 
-def _stale() -> bool:
-    if not LIB_PATH.exists():
+STAMP_PATH = PKG_DIR / "libprism_b200.stamp"
+
+
+def _source_digest() -> str:
+    """Hash of everything the library is compiled from (contents, not time stamps: a copied tree keeps
+    its contents but not necessarily the order of its modification times)."""
+    import hashlib
+    h = hashlib.sha256()
+    deps = sorted(CSRC.glob("*.cu")) + sorted(CSRC.glob("*.cuh")) + [PKG_DIR.parent / "include" / "prism_b200.h"]
+    for d in deps:
+        if d.exists():
+            h.update(d.name.encode())
+            h.update(d.read_bytes())
+    h.update(" ".join(NVCC_FLAGS).encode())
+    return h.hexdigest()
+
+
+def stale() -> bool:
+    """True if the library is missing or was built from other sources than the ones in the tree."""
+    if not LIB_PATH.exists() or not STAMP_PATH.exists():
         return True
-    t = LIB_PATH.stat().st_mtime
-    deps = list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + [PKG_DIR.parent / "include" / "prism_b200.h"]
-    return any(d.stat().st_mtime > t for d in deps if d.exists())
+    return STAMP_PATH.read_text().strip() != _source_digest()
 
 
 def build_library(force: bool = False, verbose: bool = False) -> Path:
     """Compile every kernel source into one shared library; returns its path."""
-    if not force and not _stale():
+    if not force and not stale():
         return LIB_PATH
     objdir = PKG_DIR / "build"
     objdir.mkdir(exist_ok=True)
@@ -81,6 +97,7 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
         sys.stdout.write(r.stdout)
         raise RuntimeError("libprism_b200.so: link failed")
     os.replace(tmp, LIB_PATH)
+    STAMP_PATH.write_text(_source_digest() + "\n")
     return LIB_PATH
 
 

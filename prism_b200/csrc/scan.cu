@@ -41,6 +41,8 @@
 // unwind and the kernel returns.
 #include "common.cuh"
 
+#include <mutex>
+
 namespace prism_b200 {
 
 namespace {
@@ -48,7 +50,6 @@ namespace {
 constexpr uint32_t kStateInvalid = 0u;
 constexpr uint32_t kStateAggregate = 1u;
 constexpr uint32_t kStatePrefix = 2u;
-constexpr uint32_t kMaxPolls = 1u << 20;
 constexpr size_t kHeaderBytes = 128;  // [0] ticket, [1] abort flag; the records follow
 // 64-bit words between consecutive tiles' records: one 32-byte sector per record.  Packed records
 // (16 to a 128-byte line) cost 11 % of the throughput: up to 32 look-back warps poll each record
@@ -104,16 +105,6 @@ __device__ __forceinline__ void bulk_load_tile(void* dst_smem, const void* src, 
                  : "memory");
 }
 
-// TUNING ONLY (-DPRISM_SCAN_TRACE): per-tile timestamps of the pipeline stages.
-#ifdef PRISM_SCAN_TRACE
-__device__ unsigned long long g_trace[8 * 65536];
-#define PRISM_TRACE(tile, k) do { if ((tile) < 65536u) g_trace[8 * (tile) + (k)] = global_timer_ns(); } while (0)
-#define PRISM_TRACE_VAL(tile, k, v) do { if ((tile) < 65536u) g_trace[8 * (tile) + (k)] = (v); } while (0)
-#else
-#define PRISM_TRACE(tile, k) do { } while (0)
-#define PRISM_TRACE_VAL(tile, k, v) do { } while (0)
-#endif
-
 // Sum of the tiles before `tile`, found by walking the records backwards 32 at a
 // time until one that already carries an inclusive prefix (the job of the reference's
 // lookback_to_prev_blocks, generated/lookback_to_prev_blocks.cu:8-25, done by a warp
@@ -121,27 +112,23 @@ __device__ unsigned long long g_trace[8 * 65536];
 // an abort was seen.
 template <bool F32>
 __device__ __forceinline__ uint32_t lookback(uint32_t tile, const uint64_t* desc, const uint32_t* abort_flag,
-                                             bool* failed) {
+                                             unsigned long long limit_ns, bool* failed) {
     const int lane = threadIdx.x & 31;
     uint32_t exclusive = 0;
     long long idx = static_cast<long long>(tile) - 1 - lane;
     *failed = false;
-#ifdef PRISM_SCAN_TRACE
-    unsigned long long rounds = 0;
-#endif
     while (true) {
-#ifdef PRISM_SCAN_TRACE
-        ++rounds;
-        if (lane == 0) PRISM_TRACE_VAL(tile, 6, rounds);
-#endif
         // A slot before tile 0 behaves like a finished tile with prefix 0.
         uint64_t d = kStatePrefix;
         if (idx >= 0) {
             uint32_t polls = 0;
+            unsigned long long t0 = 0;
             d = ld_desc(desc + idx * kRecStride);
             while (static_cast<uint32_t>(d) == kStateInvalid) {
-                if (++polls >= kMaxPolls) break;
-                if ((polls & 1023u) == 0u && ld_flag(abort_flag) != 0u) break;
+                if ((++polls & 1023u) == 0u) {
+                    if (t0 == 0) t0 = global_timer_ns();
+                    if (ld_flag(abort_flag) != 0u || global_timer_ns() - t0 > limit_ns) break;
+                }
                 d = ld_desc(desc + idx * kRecStride);
             }
         }
@@ -175,13 +162,111 @@ __device__ __forceinline__ uint64_t ld_sys_u64(const uint64_t* p) {
     asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
     return v;
 }
+__device__ __forceinline__ void st_sys_u64(uint64_t* p, uint64_t v) {
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+
+// What the sharded kernel needs beyond the plain scan's arguments.
+struct ShardArgs {
+    const uint64_t* slots;         // this rank's 2 * world words, written by every rank
+    uint64_t* const* peer_slots;   // base address of every rank's word array (device array of `world` pointers)
+    int rank, world;
+    uint32_t epoch;                // non-zero, the same on every rank, changes from call to call
+    uint32_t phases;               // kPhaseReduce | kPhaseScan
+    unsigned long long wait_ns;    // longest wait for the other ranks' words
+};
+enum : uint32_t { kPhaseReduce = 1u, kPhaseScan = 2u };
+
+// Header words of the scratch: [0] scan ticket, [1] abort flag, and for the sharded kernel
+// [2] reduce ticket, [3] reduce slices finished, [4] running total of the chunk.
+constexpr uint32_t kSliceElems = 1u << 15;   // elements per reduce ticket (128 KB)
+
+// First phase of the sharded kernel: the CTAs draw slices of the chunk, LAST slice first (what is still
+// in L2 afterwards is then the part the scan reads first), add them up, and whoever finishes the last
+// slice stores {epoch, total} into every rank's word array, one 64-bit system-scope store each, over
+// NVLink for the peers.  Slices are handed out by ticket, so a CTA that is not resident yet holds
+// nobody up.  All threads of the CTA take part; `s_ticket` and `s_part` are shared-memory scratch.
+__device__ __forceinline__ void reduce_and_publish(uint32_t n, const uint32_t* src, uint32_t* header, const ShardArgs& sh,
+                                                   volatile uint32_t* s_ticket, volatile uint32_t* s_part) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t slices = static_cast<uint32_t>((static_cast<unsigned long long>(n) + kSliceElems - 1) / kSliceElems);
+    auto publish = [&](uint32_t total) {
+        const uint64_t w = static_cast<uint64_t>(sh.epoch) | (static_cast<uint64_t>(total) << 32);
+        for (int p = 0; p < sh.world; ++p) st_sys_u64(sh.peer_slots[p] + (sh.epoch & 1u) * sh.world + sh.rank, w);
+    };
+    if (slices == 0) {   // an empty chunk still announces itself: the others wait for every rank's word
+        if (blockIdx.x == 0 && tid == 0) publish(0u);
+        return;
+    }
+    for (;;) {
+        if (tid == 0) *s_ticket = atomicAdd(header + 2, 1u);
+        __syncthreads();
+        const uint32_t t = *s_ticket;
+        if (t >= slices) break;
+        const unsigned long long lo = static_cast<unsigned long long>(slices - 1 - t) * kSliceElems;
+        const uint32_t cnt = n - lo < kSliceElems ? static_cast<uint32_t>(n - lo) : kSliceElems;
+        const uint4* p4 = reinterpret_cast<const uint4*>(src + lo);
+        const uint32_t nv = cnt / 4;
+        uint32_t acc = 0;
+        uint32_t v = tid;
+        for (; v + 3 * kThreads < nv; v += 4 * kThreads) {
+            const uint4 a = __ldcg(p4 + v), b = __ldcg(p4 + v + kThreads), c = __ldcg(p4 + v + 2 * kThreads),
+                        d = __ldcg(p4 + v + 3 * kThreads);
+            acc += (a.x + a.y) + (a.z + a.w) + (b.x + b.y) + (b.z + b.w) + (c.x + c.y) + (c.z + c.w) + (d.x + d.y) +
+                   (d.z + d.w);
+        }
+        for (; v < nv; v += kThreads) {
+            const uint4 a = __ldcg(p4 + v);
+            acc += (a.x + a.y) + (a.z + a.w);
+        }
+        if (static_cast<uint32_t>(tid) < (cnt & 3u)) acc += src[lo + nv * 4 + tid];
+        acc = warp_sum(acc);
+        if (lane == 0) s_part[warp] = acc;
+        __syncthreads();
+        if (tid == 0) {
+            uint32_t tot = 0;
+            for (int w = 0; w < kThreads / 32; ++w) tot += s_part[w];
+            atomicAdd(header + 4, tot);
+            __threadfence();
+            if (atomicAdd(header + 3, 1u) == slices - 1) {   // every slice has been added
+                __threadfence();
+                publish(atomicAdd(header + 4, 0u));
+            }
+        }
+    }
+}
+
+// Waits (at most sh.wait_ns) until every rank's word in this rank's array carries this call's epoch and
+// returns the sum of the lower ranks' totals.  Every rank's word is awaited, not only the lower ones:
+// that a rank has seen all words of epoch e is what allows the others to overwrite that half of the
+// array at epoch e + 2, and this rank's own word says that its reduce phase has read the whole chunk,
+// which the scan is about to overwrite.  Called by one whole warp; lane r watches rank r.
+__device__ __forceinline__ uint32_t wait_peer_words(const ShardArgs& sh, volatile uint32_t* abort_flag, bool* failed) {
+    const int lane = threadIdx.x & 31;
+    const uint64_t* words = sh.slots + (sh.epoch & 1u) * sh.world;
+    uint64_t w = static_cast<uint64_t>(sh.epoch);
+    if (lane < sh.world) {
+        const unsigned long long t0 = global_timer_ns();
+        w = ld_sys_u64(words + lane);
+        for (uint32_t spin = 1; static_cast<uint32_t>(w) != sh.epoch; ++spin) {
+            if ((spin & 63u) == 0u && (*abort_flag || global_timer_ns() - t0 > sh.wait_ns)) break;
+            __nanosleep(100);
+            w = ld_sys_u64(words + lane);
+        }
+    }
+    *failed = !__all_sync(0xffffffffu, static_cast<uint32_t>(w) == sh.epoch);
+    return warp_sum(lane < sh.rank ? static_cast<uint32_t>(w >> 32) : 0u);
+}
 
 // `src` is read, `x` is written (the same pointer for the in-place entry points).  EXCL shifts the
 // result by one element: out[i] = in[0] + ... + in[i-1], out[0] = the seed.
 template <int SEED, bool F32 = false, bool EXCL = false>
 __device__ __forceinline__ void scan_body(uint32_t n, const uint32_t* src, uint32_t* x, uint32_t* header, uint64_t* desc,
-                                          const void* seed_src, int rank, int world, uint32_t epoch) {
+                                          const void* seed_src, int rank, const ShardArgs* shard = nullptr) {
     static_assert(!F32 || SEED == kSeedNone, "the sharded forms are uint32 only");
+    // Longest single wait inside this kernel.  The sharded form may be told to wait longer for its peers;
+    // every other wait then gets twice that, so that the wait for the peers is the one that gives up first.
+    const unsigned long long limit_ns = SEED == kSeedPeers ? 2ull * shard->wait_ns : kWaitLimitNs;
     constexpr int S = kSlots;
     extern __shared__ __align__(128) unsigned char p_smem[];
     uint32_t* slots = reinterpret_cast<uint32_t*>(p_smem);
@@ -215,12 +300,18 @@ __device__ __forceinline__ void scan_body(uint32_t n, const uint32_t* src, uint3
     }
     __syncthreads();
 
+    if constexpr (SEED == kSeedPeers) {
+        if (shard->phases & kPhaseReduce) reduce_and_publish(n, src, header, *shard, s_tile, s_warp_total);
+        if (!(shard->phases & kPhaseScan)) return;
+        __syncthreads();
+    }
+
     if (warp == kScanThreads / 32) {
         // ------------------------------ producer ------------------------------
         if (lane == 0) {
             for (uint32_t i = 0;; ++i) {
                 const int s = i % S;
-                if (!mbar_wait_bounded(&empty_bar[s], ((i / S) & 1u) ^ 1u, abort_flag)) {
+                if (!mbar_wait_bounded(&empty_bar[s], ((i / S) & 1u) ^ 1u, abort_flag, limit_ns)) {
                     *abort_flag = 1;
                     atomicExch(header + 1, 1u);
                     raise_device_status(DEV_SCAN_LOOKBACK_TIMEOUT);
@@ -235,7 +326,6 @@ __device__ __forceinline__ void scan_body(uint32_t n, const uint32_t* src, uint3
                     break;
                 }
                 s_tile[s] = t;
-                PRISM_TRACE(t, 0);   // ticket drawn, load issued
                 const unsigned long long base = static_cast<unsigned long long>(t) * kTile;
                 const unsigned long long left = n - base;
                 const uint32_t cnt = left < kTile ? static_cast<uint32_t>(left) : kTile;
@@ -254,9 +344,21 @@ __device__ __forceinline__ void scan_body(uint32_t n, const uint32_t* src, uint3
     if (warp > kScanThreads / 32) {
         // ------------------------------ look-back ------------------------------
         static_assert(kLookbackWarps >= 1 && kLookbackWarps <= kSlots, "one look-back warp per slot at most");
+        if constexpr (SEED == kSeedPeers) {
+            // An empty chunk has no tile 0 to do the waiting, but the protocol still needs this rank to have seen
+            // every word of this epoch before it moves on to the next one.
+            if (tiles == 0 && blockIdx.x == 0) {
+                bool failed = false;
+                (void)wait_peer_words(*shard, abort_flag, &failed);
+                if (failed && lane == 0) {
+                    atomicExch(header + 1, 1u);
+                    raise_device_status(DEV_SCAN_LOOKBACK_TIMEOUT);
+                }
+            }
+        }
         for (uint32_t k = static_cast<uint32_t>(warp - kScanThreads / 32 - 1);; k += kLookbackWarps) {
             const int s = k % S;
-            const bool ready = mbar_wait_bounded(&agg_bar[s], (k / S) & 1u, abort_flag);
+            const bool ready = mbar_wait_bounded(&agg_bar[s], (k / S) & 1u, abort_flag, limit_ns);
             if (!__all_sync(0xffffffffu, ready)) {
                 if (lane == 0) {
                     *abort_flag = 1;
@@ -270,30 +372,15 @@ __device__ __forceinline__ void scan_body(uint32_t n, const uint32_t* src, uint3
             const uint32_t agg = s_agg[s];
             uint32_t exclusive = 0;
             bool failed = false;
-            if (lane == 0) PRISM_TRACE(t, 3);   // look-back starts
             if (t == 0) {
                 if (SEED == kSeedTotals) {
                     const uint32_t* totals = static_cast<const uint32_t*>(seed_src);
                     for (int r = 0; r < rank; ++r) exclusive += totals[r];
                 } else if (SEED == kSeedPeers) {
-                    // Lane r waits for rank r's word of this epoch (every rank's, not only the lower
-                    // ones: that is what keeps a fast rank from overwriting a word nobody has read yet).
-                    const uint64_t* slots = static_cast<const uint64_t*>(seed_src) + (epoch & 1u) * world;
-                    uint64_t w = static_cast<uint64_t>(epoch);
-                    if (lane < world) {
-                        const unsigned long long t0 = global_timer_ns();
-                        w = ld_sys_u64(slots + lane);
-                        for (uint32_t spin = 1; static_cast<uint32_t>(w) != epoch; ++spin) {
-                            if ((spin & 63u) == 0u && (*abort_flag || global_timer_ns() - t0 > kWaitLimitNs)) break;
-                            __nanosleep(100);
-                            w = ld_sys_u64(slots + lane);
-                        }
-                    }
-                    failed = !__all_sync(0xffffffffu, static_cast<uint32_t>(w) == epoch);
-                    exclusive = warp_sum(lane < rank ? static_cast<uint32_t>(w >> 32) : 0u);
+                    exclusive = wait_peer_words(*shard, abort_flag, &failed);
                 }
             } else {
-                exclusive = lookback<F32>(t, desc, header + 1, &failed);
+                exclusive = lookback<F32>(t, desc, header + 1, limit_ns, &failed);
             }
             if (lane == 0) {
                 if (failed) {
@@ -302,7 +389,6 @@ __device__ __forceinline__ void scan_body(uint32_t n, const uint32_t* src, uint3
                     raise_device_status(DEV_SCAN_LOOKBACK_TIMEOUT);
                 }
                 st_desc(desc + static_cast<size_t>(t) * kRecStride, kStatePrefix, eadd<F32>(exclusive, agg));  // as write_block_prefix.cu:8-10
-                PRISM_TRACE(t, 4);   // prefix published
                 s_excl[s] = exclusive;
                 mbar_arrive(&pre_bar[s]);
             }
@@ -338,7 +424,7 @@ __device__ __forceinline__ void scan_body(uint32_t n, const uint32_t* src, uint3
                 for (uint32_t spin = 0;; ++spin) {
                     if (can_a && mbar_try_wait(&full_bar[i % S], (i / S) & 1u)) { what = 1; break; }
                     if (can_b && mbar_try_wait(&pre_bar[j % S], (j / S) & 1u)) { what = 2; break; }
-                    if ((spin & 63u) == 63u && (*abort_flag || global_timer_ns() - t0 > kWaitLimitNs)) break;
+                    if ((spin & 63u) == 63u && (*abort_flag || global_timer_ns() - t0 > limit_ns)) break;
                 }
                 if (what == 0) {
                     *abort_flag = 1;
@@ -370,7 +456,6 @@ __device__ __forceinline__ void scan_body(uint32_t n, const uint32_t* src, uint3
                 continue;
             }
             uint32_t* slot = slots + s * kTile;
-            if (tid == 0) PRISM_TRACE(t, 1);   // phase A starts (data landed and scan warps free)
             const unsigned long long base = static_cast<unsigned long long>(t) * kTile;
             const unsigned long long left = n - base;
             const uint32_t cnt = left < kTile ? static_cast<uint32_t>(left) : kTile;
@@ -430,7 +515,6 @@ __device__ __forceinline__ void scan_body(uint32_t n, const uint32_t* src, uint3
             if (tid == 0) {
                 if (t != 0) st_desc(desc + static_cast<size_t>(t) * kRecStride, kStateAggregate, aggregate);  // as write_block_aggregate.cu:8-10
                 s_agg[s] = aggregate;
-                PRISM_TRACE(t, 2);   // aggregate published
                 mbar_arrive(&agg_bar[s]);
             }
             // Tile-local inclusive scan back into the slot; the same lane reads it again in phase B.
@@ -452,7 +536,6 @@ __device__ __forceinline__ void scan_body(uint32_t n, const uint32_t* src, uint3
             const int s = j % S;
             (void)mbar_try_wait(&pre_bar[s], (j / S) & 1u);
             const uint32_t t = s_tile[s];
-            if (tid == 0) PRISM_TRACE(t, 5);   // phase B starts
             const uint32_t add = s_excl[s];
             const uint32_t* slot = slots + s * kTile;
             const unsigned long long base = static_cast<unsigned long long>(t) * kTile;
@@ -491,7 +574,7 @@ constexpr int kCtasPerSm = static_cast<int>((227 * 1024) / (kSmemBytes + 1024));
 
 __global__ void __launch_bounds__(kThreads, kCtasPerSm)
 scan_kernel(uint32_t n, uint32_t* x, uint32_t* block_idx_counter, int* block_infos) {
-    scan_body<kSeedNone>(n, x, x, block_idx_counter, reinterpret_cast<uint64_t*>(block_infos), nullptr, 0, 1, 0);
+    scan_body<kSeedNone>(n, x, x, block_idx_counter, reinterpret_cast<uint64_t*>(block_infos), nullptr, 0);
 }
 
 // fp32 flavour of the same kernel (the reference scans uint32 only): same pipeline, fp32 adds.  The
@@ -500,7 +583,7 @@ scan_kernel(uint32_t n, uint32_t* x, uint32_t* block_idx_counter, int* block_inf
 __global__ void __launch_bounds__(kThreads, kCtasPerSm)
 scan_kernel_f32(uint32_t n, float* x, uint32_t* block_idx_counter, int* block_infos) {
     scan_body<kSeedNone, true>(n, reinterpret_cast<uint32_t*>(x), reinterpret_cast<uint32_t*>(x), block_idx_counter,
-                               reinterpret_cast<uint64_t*>(block_infos), nullptr, 0, 1, 0);
+                               reinterpret_cast<uint64_t*>(block_infos), nullptr, 0);
 }
 
 // General flavour (no counterpart in the reference): separate input and output, inclusive or exclusive,
@@ -508,21 +591,24 @@ scan_kernel_f32(uint32_t n, float* x, uint32_t* block_idx_counter, int* block_in
 template <bool F32, bool EXCL>
 __global__ void __launch_bounds__(kThreads, kCtasPerSm)
 scan_kernel_general(uint32_t n, const uint32_t* in, uint32_t* out, uint32_t* block_idx_counter, int* block_infos) {
-    scan_body<kSeedNone, F32, EXCL>(n, in, out, block_idx_counter, reinterpret_cast<uint64_t*>(block_infos), nullptr, 0, 1, 0);
+    scan_body<kSeedNone, F32, EXCL>(n, in, out, block_idx_counter, reinterpret_cast<uint64_t*>(block_infos), nullptr, 0);
 }
 
 // Sharded form: tile 0 starts from totals[0] + ... + totals[rank-1].
 __global__ void __launch_bounds__(kThreads, kCtasPerSm)
 scan_kernel_seeded(uint32_t n, uint32_t* x, uint32_t* block_idx_counter, int* block_infos, const uint32_t* totals,
                    int rank) {
-    scan_body<kSeedTotals>(n, x, x, block_idx_counter, reinterpret_cast<uint64_t*>(block_infos), totals, rank, 1, 0);
+    scan_body<kSeedTotals>(n, x, x, block_idx_counter, reinterpret_cast<uint64_t*>(block_infos), totals, rank);
 }
 
-// Sharded form without a collective call: the totals arrive as {epoch, total} words stored by the peers.
+// Sharded form without a collective call, in one launch: (1) the chunk's total, stored as an {epoch, total}
+// word into every rank's memory by whichever CTA finishes the last slice, (2) the scan, whose first tile
+// waits for all ranks' words and starts from the sum of the lower ranks' totals.  Either phase can be
+// switched off (the two-launch form, and the emulation of several ranks on one GPU, where a launch
+// that waits for a later launch's word would never see it).
 __global__ void __launch_bounds__(kThreads, kCtasPerSm)
-scan_kernel_seeded_peers(uint32_t n, uint32_t* x, uint32_t* block_idx_counter, int* block_infos,
-                         const uint64_t* slots, int rank, int world, uint32_t epoch) {
-    scan_body<kSeedPeers>(n, x, x, block_idx_counter, reinterpret_cast<uint64_t*>(block_infos), slots, rank, world, epoch);
+scan_kernel_sharded(uint32_t n, uint32_t* x, uint32_t* block_idx_counter, int* block_infos, const ShardArgs shard) {
+    scan_body<kSeedPeers>(n, x, x, block_idx_counter, reinterpret_cast<uint64_t*>(block_infos), nullptr, shard.rank, &shard);
 }
 
 // Stores this rank's {epoch, total} word into every rank's slot array (its own included) with one
@@ -590,6 +676,8 @@ size_t scan_tiles(size_t n) { return (n + kTile - 1) / kTile; }
 // once per device; also raises the kernels' dynamic shared-memory limit.
 int persistent_grid(unsigned* out) {
     static unsigned cached[64] = {};
+    static std::mutex mu;   // entry points may be called from several host threads
+    std::lock_guard<std::mutex> lk(mu);
     int dev = 0;
     PRISM_CUDA_TRY(cudaGetDevice(&dev));
     const bool cacheable = dev >= 0 && dev < 64;
@@ -613,7 +701,7 @@ int persistent_grid(unsigned* out) {
                                         static_cast<int>(kSmemBytes)));
     PRISM_CUDA_TRY(cudaFuncSetAttribute(scan_kernel_general<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         static_cast<int>(kSmemBytes)));
-    PRISM_CUDA_TRY(cudaFuncSetAttribute(scan_kernel_seeded_peers, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    PRISM_CUDA_TRY(cudaFuncSetAttribute(scan_kernel_sharded, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         static_cast<int>(kSmemBytes)));
     PRISM_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, scan_kernel, kThreads, kSmemBytes));
     if (per_sm < 1 || sms < 1) return set_error(PRISM_B200_ERR_CUDA, "scan: the kernel does not fit on an SM");
@@ -625,18 +713,17 @@ int persistent_grid(unsigned* out) {
 // Re-arms the scratch (ticket, abort flag, every record: one memset where the reference
 // issues two, evals/4090_scan/main.cu:81-82) and launches the kernel.
 int scan_enqueue(size_t n, uint32_t* x, void* scratch, const void* seed_src, int rank, int seed_mode,
-                 cudaStream_t stream, int world = 1, uint32_t epoch = 0) {
+                 cudaStream_t stream, const ShardArgs* shard = nullptr) {
     const uint32_t tiles = static_cast<uint32_t>(scan_tiles(n));
     uint32_t* header = static_cast<uint32_t*>(scratch);
     uint64_t* desc = reinterpret_cast<uint64_t*>(static_cast<char*>(scratch) + kHeaderBytes);
     unsigned grid = 0;
     if (int rc = persistent_grid(&grid)) return rc;
-    if (grid > tiles) grid = tiles;
+    if (grid > tiles) grid = tiles > 0 ? tiles : 1;   // tiles == 0 only in the sharded form (an empty chunk)
     PRISM_CUDA_TRY(cudaMemsetAsync(scratch, 0, kHeaderBytes + static_cast<size_t>(tiles) * kRecStride * sizeof(uint64_t), stream));
     if (seed_mode == kSeedPeers)
-        scan_kernel_seeded_peers<<<grid, kThreads, kSmemBytes, stream>>>(
-            static_cast<uint32_t>(n), x, header, reinterpret_cast<int*>(desc), static_cast<const uint64_t*>(seed_src),
-            rank, world, epoch);
+        scan_kernel_sharded<<<grid, kThreads, kSmemBytes, stream>>>(static_cast<uint32_t>(n), x, header,
+                                                                    reinterpret_cast<int*>(desc), *shard);
     else if (seed_mode == kSeedTotals)
         scan_kernel_seeded<<<grid, kThreads, kSmemBytes, stream>>>(static_cast<uint32_t>(n), x, header,
                                                                    reinterpret_cast<int*>(desc),
@@ -653,7 +740,7 @@ int scan_enqueue(size_t n, uint32_t* x, void* scratch, const void* seed_src, int
 }
 
 int scan_launch(size_t n, uint32_t* x, void* workspace, const void* seed_src, int rank, int seed_mode,
-                cudaStream_t stream, int world = 1, uint32_t epoch = 0) {
+                cudaStream_t stream) {
     if (n == 0) return PRISM_B200_OK;
     if (!x || !workspace) return set_error(PRISM_B200_ERR_INVALID_ARGUMENT, "scan: null pointer");
     if (n >= (1ull << 32)) return set_error(PRISM_B200_ERR_TOO_LARGE, "scan: n=%zu must be below 2^32", n);
@@ -662,10 +749,30 @@ int scan_launch(size_t n, uint32_t* x, void* workspace, const void* seed_src, in
         return set_error(PRISM_B200_ERR_MISALIGNED, "scan: workspace not 16-byte aligned");
     if (seed_mode == kSeedTotals && (rank < 0 || (rank > 0 && !seed_src)))
         return set_error(PRISM_B200_ERR_INVALID_ARGUMENT, "scan_seeded: bad rank/totals");
-    if (seed_mode == kSeedPeers && (!seed_src || world < 1 || world > 32 || rank < 0 || rank >= world || epoch == 0))
-        return set_error(PRISM_B200_ERR_INVALID_ARGUMENT, "scan_seeded_peers: need slots, 1 <= world <= 32, a rank below world and a non-zero epoch");
     if (int rc = bind_status_word()) return rc;
-    return scan_enqueue(n, x, workspace, seed_src, rank, seed_mode, stream, world, epoch);
+    return scan_enqueue(n, x, workspace, seed_src, rank, seed_mode, stream);
+}
+
+// The sharded form.  Unlike the others it runs for n == 0 too: an empty chunk still has to publish its
+// word and to wait for the others'.
+int scan_sharded_launch(size_t n, uint32_t* x, void* workspace, const uint64_t* slots, uint64_t* const* peer_slots,
+                        int rank, int world, uint32_t epoch, int phases, unsigned long long wait_limit_ns,
+                        cudaStream_t stream) {
+    if (world < 1 || world > 32 || rank < 0 || rank >= world || epoch == 0)
+        return set_error(PRISM_B200_ERR_INVALID_ARGUMENT,
+                         "scan_sharded: need 1 <= world <= 32, a rank below world and a non-zero epoch");
+    if (phases < 1 || phases > 3) return set_error(PRISM_B200_ERR_INVALID_ARGUMENT, "scan_sharded: phases must be 1, 2 or 3");
+    if (((phases & kPhaseReduce) && !peer_slots) || ((phases & kPhaseScan) && !slots) || !workspace || (n && !x))
+        return set_error(PRISM_B200_ERR_INVALID_ARGUMENT, "scan_sharded: null pointer");
+    if (n >= (1ull << 32)) return set_error(PRISM_B200_ERR_TOO_LARGE, "scan_sharded: n=%zu must be below 2^32", n);
+    if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(workspace)) & 15u)
+        return set_error(PRISM_B200_ERR_MISALIGNED, "scan_sharded: x and workspace must be 16-byte aligned");
+    if (wait_limit_ns == 0) wait_limit_ns = kWaitLimitNs;
+    if (wait_limit_ns > 600ull * kWaitLimitNs)
+        return set_error(PRISM_B200_ERR_INVALID_ARGUMENT, "scan_sharded: wait limit above 600 s");
+    if (int rc = bind_status_word()) return rc;
+    const ShardArgs shard{slots, peer_slots, rank, world, epoch, static_cast<uint32_t>(phases), wait_limit_ns};
+    return scan_enqueue(n, x, workspace, nullptr, rank, kSeedPeers, stream, &shard);
 }
 
 // The general flavour: same re-arming and grid as scan_enqueue.
@@ -743,6 +850,8 @@ void* g_static_scratch_addr[64] = {};
 
 // Device address of the built-in scratch on the current device, looked up once per device.
 int static_scratch_address(void** out) {
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lk(mu);
     int dev = 0;
     PRISM_CUDA_TRY(cudaGetDevice(&dev));
     const bool cacheable = dev >= 0 && dev < 64;
@@ -778,11 +887,6 @@ extern "C" int prism_b200_scan_static(size_t n, uint32_t* x, void* stream) {
     return scan_enqueue(n, x, scratch, nullptr, 0, kSeedNone, static_cast<cudaStream_t>(stream));
 }
 
-#ifdef PRISM_SCAN_TRACE
-extern "C" int prism_b200_scan_trace(unsigned long long* out) {
-    return cudaMemcpyFromSymbol(out, g_trace, sizeof(unsigned long long) * 8 * 65536) == cudaSuccess ? 0 : 4;
-}
-#endif
 
 extern "C" int prism_b200_scan_workspace_size(size_t n, size_t* bytes) {
     if (!bytes) return set_error(PRISM_B200_ERR_INVALID_ARGUMENT, "scan_workspace_size: null bytes");
@@ -822,7 +926,15 @@ extern "C" int prism_b200_scan_publish_total(const uint32_t* total, uint64_t* co
 
 extern "C" int prism_b200_scan_seeded_peers(size_t n, uint32_t* x, void* workspace, const uint64_t* slots, int rank,
                                             int world, uint32_t epoch, void* stream) {
-    return scan_launch(n, x, workspace, slots, rank, kSeedPeers, static_cast<cudaStream_t>(stream), world, epoch);
+    return scan_sharded_launch(n, x, workspace, slots, nullptr, rank, world, epoch, kPhaseScan, 0,
+                               static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int prism_b200_scan_sharded(size_t n, uint32_t* x, void* workspace, const uint64_t* slots,
+                                       uint64_t* const* peer_slots, int rank, int world, uint32_t epoch, int phases,
+                                       unsigned long long wait_limit_ns, void* stream) {
+    return scan_sharded_launch(n, x, workspace, slots, peer_slots, rank, world, epoch, phases, wait_limit_ns,
+                               static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int prism_b200_reduce_u32(size_t n, const uint32_t* x, uint32_t* total, void* stream) {

@@ -5,13 +5,20 @@
   collective on the data path.
 * scan: rank r owns the r-th contiguous chunk.  The only exchange is one uint32
   total per rank.  Three schedules are offered:
-    "peer_words"        total of the chunk (4 B/element read); the total is stored as an
-                        {epoch, total} word straight into every rank's memory over NVLink
-                        (symmetric memory, no collective call, no host involvement); ONE scan
-                        pass whose first tile waits for the words and starts from the sum of
-                        the lower ranks' totals (8 B/element): 12 B/element per rank.  Default
-                        on CUDA with more than one rank.
-    "reduce_then_scan"  the same with an NCCL all-gather of the totals between the passes.
+    "peer_words"        ONE launch per rank: the CTAs add up the chunk (4 B/element read) and the
+                        total is stored as an {epoch, total} word straight into every rank's memory
+                        over NVLink (symmetric memory, no collective call, no host involvement);
+                        then the scan, whose first tile waits for the words and starts from the sum
+                        of the lower ranks' totals (8 B/element): 12 B/element per rank.  Default on
+                        CUDA with more than one rank; if the symmetric-memory rendezvous is not
+                        available (no peer access, several nodes) the constructor falls back to
+                        "reduce_then_scan".  The wait for the other ranks is bounded
+                        (`wait_limit_s`): ranks that enter the call further apart than that get a
+                        device time-out instead of a result -- `checked=True` makes the call
+                        synchronise and raise in that case; otherwise consult `last_error()` after
+                        synchronising.
+    "reduce_then_scan"  the same in two launches with an NCCL all-gather of the totals in between
+                        (waits as long as NCCL does).
     "scan_then_carry"   local scan (8 B/element), all-gather of the last elements,
                         carry-add pass (8 B/element): 16 B/element per rank.
   All produce the scan of the concatenated array, bit for bit.
@@ -69,11 +76,32 @@ class _CudaOps:
     def scan_add_carry_(self, x, totals, rank):
         self._pb.scan_add_carry_(x, totals, rank)
 
-    def publish_total(self, total, peer_slots_dev, world, rank, epoch):
-        self._pb.scan_publish_total(total, peer_slots_dev, world, rank, epoch)
+    def scan_sharded_(self, x, workspace, slots, peer_slots_dev, rank, world, epoch, wait_limit_s):
+        self._pb.scan_sharded_(x, workspace, slots, peer_slots_dev, rank, world, epoch, 3, wait_limit_s)
 
-    def scan_seeded_peers_(self, x, workspace, slots, rank, world, epoch):
-        self._pb.scan_seeded_peers_(x, workspace, slots, rank, world, epoch)
+    def check(self, device):
+        """Synchronise and raise if a device-side wait ran out."""
+        import torch as _t
+        _t.cuda.synchronize(device)
+        code, msg = self._pb.last_error()
+        if code:
+            self._pb.clear_error()
+            raise self._pb.PrismB200Error(code, msg)
+
+
+def _symmetric_words(n_words: int, device, group):
+    """`n_words` int64 words on this rank that every rank of the group can write, plus the device address of
+    the table of all ranks' base addresses; None if torch's symmetric memory cannot provide them."""
+    try:
+        import torch.distributed._symmetric_memory as symm
+        words = symm.empty(n_words, dtype=torch.int64, device=device)
+        words.zero_()
+        handle = symm.rendezvous(words, group if group is not None else dist.group.WORLD)
+        return words, handle, int(handle.buffer_ptrs_dev)
+    except Exception as e:   # no peer access, several nodes, or a torch build without the module
+        import warnings
+        warnings.warn(f"peer_words schedule unavailable ({type(e).__name__}: {e}); using reduce_then_scan")
+        return None
 
 
 class ShardedScan:
@@ -82,36 +110,47 @@ class ShardedScan:
     SCHEDULES = ("reduce_then_scan", "scan_then_carry")       # run anywhere a process group runs
     PEER_SCHEDULE = "peer_words"                               # needs CUDA peer access (one node)
 
-    def __init__(self, n_local: int, device, group: Any = None, schedule: str | None = None, ops: Any = None):
+    def __init__(self, n_local: int, device, group: Any = None, schedule: str | None = None, ops: Any = None,
+                 wait_limit_s: float = 0.0, checked: bool = False, symmetric_words: Any = _symmetric_words):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         on_cuda = torch.device(device).type == "cuda"
+        asked = schedule
         if schedule is None:
             schedule = self.PEER_SCHEDULE if (on_cuda and self.world > 1 and ops is None) else "reduce_then_scan"
         if schedule not in self.SCHEDULES + (self.PEER_SCHEDULE,):
             raise ValueError(f"schedule must be one of {self.SCHEDULES + (self.PEER_SCHEDULE,)}")
-        if schedule == self.PEER_SCHEDULE and (self.world > 32 or not on_cuda):
-            raise ValueError("the peer_words schedule needs CUDA devices and at most 32 ranks")
-        self.schedule = schedule
+        if schedule == self.PEER_SCHEDULE and self.world > 32:
+            raise ValueError("the peer_words schedule handles at most 32 ranks")
+        if schedule == self.PEER_SCHEDULE and not on_cuda and ops is None:
+            raise ValueError("the peer_words schedule needs CUDA devices")
         self.epoch = 0
         self.slots = None
         self.peer_slots_dev = 0
+        self.wait_limit_s = float(wait_limit_s)
+        self.checked = bool(checked)
+        self.device = device
         self.ops = ops if ops is not None else _CudaOps()
         self.n_local = n_local
         self.workspace = self.ops.workspace(n_local, device)
         self.total = torch.zeros(1, dtype=torch.int32, device=device)
         self.totals = torch.zeros(self.world, dtype=torch.int32, device=device)
-        if self.schedule == self.PEER_SCHEDULE and self.world > 1:
-            # 2 * world words per rank, writable by every rank: torch's symmetric memory gives each
-            # rank the device addresses of all the peers' buffers.
-            import torch.distributed._symmetric_memory as symm
-            self.slots = symm.empty(2 * self.world, dtype=torch.int64, device=device)
-            self.slots.zero_()
-            self._symm = symm.rendezvous(self.slots, group if group is not None else dist.group.WORLD)
-            self.peer_slots_dev = int(self._symm.buffer_ptrs_dev)
-            torch.cuda.synchronize(device)
-            dist.barrier(group)   # every rank's words are zero before anyone publishes
+        if schedule == self.PEER_SCHEDULE and self.world > 1:
+            # 2 * world words per rank, writable by every rank.  All ranks must agree on the outcome,
+            # hence the all-reduce of "it worked here".
+            got = symmetric_words(2 * self.world, device, group)
+            ok = torch.tensor([1 if got is not None else 0], dtype=torch.int32, device=device)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+            if int(ok.item()) == 1:
+                self.slots, self._symm, self.peer_slots_dev = got
+                if on_cuda:
+                    torch.cuda.synchronize(device)
+                dist.barrier(group)   # every rank's words are zero before anyone publishes
+            else:
+                schedule = "reduce_then_scan"
+        self.schedule = schedule
+        self.fell_back = asked in (None, self.PEER_SCHEDULE) and schedule != self.PEER_SCHEDULE and on_cuda and self.world > 1
 
     def _exchange(self, total: torch.Tensor) -> None:
         if self.world == 1:
@@ -124,9 +163,10 @@ class ShardedScan:
             raise ValueError(f"shard has {x_local.numel()} elements, planned for {self.n_local}")
         if self.schedule == self.PEER_SCHEDULE and self.world > 1:
             self.epoch += 1
-            self.ops.reduce_u32(x_local, self.total)
-            self.ops.publish_total(self.total, self.peer_slots_dev, self.world, self.rank, self.epoch)
-            self.ops.scan_seeded_peers_(x_local, self.workspace, self.slots, self.rank, self.world, self.epoch)
+            self.ops.scan_sharded_(x_local, self.workspace, self.slots, self.peer_slots_dev, self.rank, self.world,
+                                   self.epoch, self.wait_limit_s)
+            if self.checked:
+                self.ops.check(self.device)
         elif self.schedule in ("reduce_then_scan", self.PEER_SCHEDULE):
             if self.world > 1:
                 self.ops.reduce_u32(x_local, self.total)

@@ -156,6 +156,28 @@ def test_benchmark_size_8192(pb):
     assert np.all(np.abs(got - ref) <= 1e-2 * np.abs(ref) + 1e-2 * rms)
 
 
+@pytest.mark.parametrize("shape", [(6144, 6144, 6144), (12288, 12288, 12288), (12288, 6144, 2048), (16384, 16384, 1024)])
+def test_sweep_sizes_of_the_reference_harness(pb, shape):
+    """Sizes of the reference's sweep (evals/run_h100.sh:12) that are not powers of two, and the largest one:
+    tile counts that leave a partly filled last wave.  Sampled rows of both CTA ranks and both row blocks of a
+    512-row tile against fp64, plus the full-size symmetry C(A, B)^T == C(B, A)."""
+    M, N, K = shape
+    g = torch.Generator(device=DEV).manual_seed(M + N + K)
+    a = (torch.randn((M, K), device=DEV, generator=g) * 0.1).to(torch.bfloat16)
+    b = (torch.randn((N, K), device=DEV, generator=g) * 0.1).to(torch.bfloat16)
+    c = torch.full((N, M), float("nan"), dtype=torch.bfloat16, device=DEV)
+    c2 = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    pb.runmyh100(M, N, K, a, b, c)      # c[n, m]
+    pb.runmyh100(N, M, K, b, a, c2)     # c2[m, n]
+    torch.cuda.synchronize()
+    assert torch.equal(c, c2.t())
+    rows = [0, 127, 128, 255, 256, 383, 384, 511, 512, N // 2 - 1, N // 2, N - 129, N - 1]
+    ref = (b[rows].double() @ a.double().t()).cpu().numpy()         # [n in rows, m]
+    got = c[rows].double().cpu().numpy()
+    rms = float(np.sqrt(np.mean(ref * ref)))
+    assert np.all(np.abs(got - ref) <= 1e-2 * np.abs(ref) + 1e-2 * rms)
+
+
 def test_agrees_with_cublas_like_the_reference_harness(pb):
     """The reference harness accepts |kernel - cuBLAS| <= 0.1 (evals/h100_bench/main.cu:43-55); same check here."""
     M, N, K = 1024, 1024, 1024

@@ -1,0 +1,118 @@
+"""The peer-memory schedule of the sharded scan on ONE GPU: k "virtual ranks" whose word arrays all live
+on the same device, with a device table of their k base addresses standing in for the peers' addresses.
+
+Kernels of different ranks cannot wait for one another on one GPU (a launch that waits for a word that a
+later launch stores would never see it), so each epoch first runs the reduce/publish step of every rank
+and then the scan step of every rank -- the two-launch form of prism_b200_scan_sharded, and the older
+three-piece form (reduce_u32, scan_publish_total, scan_seeded_peers).  Every word of the epoch is then in
+place when a scan starts, and the concatenation of the chunks must equal the scan of the whole array bit
+for bit, as the reference's harness checks element by element (evals/4090_scan/scan_harness.cuh:131-146).
+The fused single launch (phases = 3) needs one GPU per rank and is covered by tests/test_sharded_gpu.py.
+"""
+import ctypes
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+sys.path.insert(0, str(ROOT))
+from oracle import cpu_oracle as O  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _bounds(n, world):
+    from prism_b200 import sharded
+    return [sharded.chunk_bounds(n, world, r) for r in range(world)]
+
+
+def _setup(world):
+    """Per-rank word arrays (2 * world int64 each) in one allocation, and the device table of their addresses."""
+    words = torch.zeros((world, 2 * world), dtype=torch.int64, device=DEV)
+    table = torch.tensor([words[r].data_ptr() for r in range(world)], dtype=torch.int64, device=DEV)
+    return words, table
+
+
+@pytest.mark.parametrize("world,n,high", [(3, (1 << 22) + 12345, 1 << 20), (4, 3 * 4096 * 5 + 77, 0xFFFFFFFF),
+                                          (4, 10, 16)])
+@pytest.mark.parametrize("form", ["two_launch", "three_piece"])
+def test_virtual_ranks_on_one_gpu(pb, world, n, high, form):
+    lib = pb.load()
+    stream = ctypes.c_void_p(torch.cuda.current_stream(torch.device(DEV)).cuda_stream)
+    words, table = _setup(world)
+    spans = _bounds(n, world)           # n = 10 over 4 ranks: chunks of 4, 4, 2 and an empty one
+    ws = [pb.scan_workspace(hi - lo, DEV) for lo, hi in spans]
+    total = torch.zeros(1, dtype=torch.int32, device=DEV)
+    with torch.cuda.device(DEV):
+        for epoch in (1, 2, 3, 4):      # both halves of every word array, twice
+            full = O.scan_inputs(n, seed=100 * world + epoch, high=high)
+            expect = O.scan_cpu(full)
+            chunks = [torch.from_numpy(full[lo:hi].view(np.int32).copy()).to(DEV) for lo, hi in spans]
+            for r, x in enumerate(chunks):
+                if form == "two_launch":
+                    rc = lib.prism_b200_scan_sharded(x.numel(), x.data_ptr() if x.numel() else None, ws[r].data_ptr(),
+                                                     words[r].data_ptr(), table.data_ptr(), r, world, epoch, 1, 0, stream)
+                else:
+                    rc = lib.prism_b200_reduce_u32(x.numel(), x.data_ptr() if x.numel() else None, total.data_ptr(), stream)
+                    assert rc == 0, pb.last_error()
+                    rc = lib.prism_b200_scan_publish_total(total.data_ptr(), table.data_ptr(), world, r, epoch, stream)
+                assert rc == 0, pb.last_error()
+            for r, x in enumerate(chunks):
+                if form == "two_launch":
+                    rc = lib.prism_b200_scan_sharded(x.numel(), x.data_ptr() if x.numel() else None, ws[r].data_ptr(),
+                                                     words[r].data_ptr(), table.data_ptr(), r, world, epoch, 2, 0, stream)
+                elif x.numel():
+                    rc = lib.prism_b200_scan_seeded_peers(x.numel(), x.data_ptr(), ws[r].data_ptr(), words[r].data_ptr(),
+                                                          r, world, epoch, stream)
+                assert rc == 0, pb.last_error()
+            torch.cuda.synchronize()
+            assert pb.last_error()[0] == 0, pb.last_error()
+            got = np.concatenate([x.cpu().numpy().view(np.uint32) for x in chunks])
+            assert np.array_equal(got, expect), f"epoch {epoch}: first mismatch at {int(np.argmax(got != expect))}"
+            # every rank's array holds every rank's {epoch, total} word of this epoch
+            half = (epoch & 1) * world
+            w = words[:, half:half + world].cpu().numpy().view(np.uint64)
+            assert np.all((w & 0xFFFFFFFF) == epoch)
+            totals = [int(full[lo:hi].sum(dtype=np.uint64)) & 0xFFFFFFFF for lo, hi in spans]
+            assert np.all((w >> 32) == np.array(totals, dtype=np.uint64)[None, :])
+
+
+def test_scan_step_gives_up_when_a_word_never_arrives(pb):
+    """Nothing publishes rank 1's word: the scan step of rank 0 must come back after its (short) limit with
+    a device time-out recorded, and the context must stay usable."""
+    lib = pb.load()
+    stream = ctypes.c_void_p(torch.cuda.current_stream(torch.device(DEV)).cuda_stream)
+    world, n = 2, 3 * 4096 + 5
+    words, table = _setup(world)
+    x = torch.ones(n, dtype=torch.int32, device=DEV)
+    ws = pb.scan_workspace(n, DEV)
+    with torch.cuda.device(DEV):
+        assert lib.prism_b200_scan_sharded(n, x.data_ptr(), ws.data_ptr(), words[0].data_ptr(), table.data_ptr(), 0, world,
+                                           1, 1, 0, stream) == 0
+        assert lib.prism_b200_scan_sharded(n, x.data_ptr(), ws.data_ptr(), words[0].data_ptr(), table.data_ptr(), 0, world,
+                                           1, 2, 2_000_000, stream) == 0        # 2 ms for the peers
+        torch.cuda.synchronize()
+    code, msg = pb.last_error()
+    assert code == 5 and "scan" in msg
+    pb.clear_error()
+    y = torch.ones(n, dtype=torch.int32, device=DEV)
+    pb.scan_(y)
+    torch.cuda.synchronize()
+    assert int(y[-1]) == n and pb.last_error()[0] == 0
+
+
+def test_argument_checks(pb):
+    lib = pb.load()
+    words, table = _setup(2)
+    x = torch.zeros(16, dtype=torch.int32, device=DEV)
+    ws = pb.scan_workspace(16, DEV)
+    args = (16, x.data_ptr(), ws.data_ptr(), words[0].data_ptr(), table.data_ptr())
+    assert lib.prism_b200_scan_sharded(*args, 0, 2, 0, 3, 0, None) == 1      # epoch 0
+    assert lib.prism_b200_scan_sharded(*args, 2, 2, 1, 3, 0, None) == 1      # rank outside the world
+    assert lib.prism_b200_scan_sharded(*args, 0, 2, 1, 4, 0, None) == 1      # unknown phase bits
+    assert lib.prism_b200_scan_sharded(*args, 0, 33, 1, 3, 0, None) == 1     # more than 32 ranks
+    pb.clear_error()

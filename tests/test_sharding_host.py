@@ -51,6 +51,24 @@ class OracleOps:
         v = self._np(x)
         v[:] = (v.astype(np.uint64) + self._carry(totals, rank)).astype(np.uint32)
 
+    def scan_sharded_(self, x, workspace, slots, peer_slots_dev, rank, world, epoch, wait_limit_s):
+        """What the fused kernel does, with the peer stores replaced by an all-gather: every rank's
+        {epoch, total} word lands in slot (epoch & 1) * world + r of this rank's array."""
+        total = int(np.sum(self._np(x), dtype=np.uint64) & 0xFFFFFFFF)
+        w = (total << 32) | epoch
+        word = torch.tensor([w - (1 << 64) if w >= (1 << 63) else w], dtype=torch.int64)   # the same 64 bits
+        words = torch.zeros(world, dtype=torch.int64)
+        dist.all_gather_into_tensor(words, word)
+        half = (epoch & 1) * world
+        slots[half:half + world] = words
+        assert all((int(w) & 0xFFFFFFFF) == epoch for w in words.tolist())
+        carry = sum((int(w) >> 32) & 0xFFFFFFFF for w in words.tolist()[:rank]) & 0xFFFFFFFF
+        v = self._np(x)
+        v[:] = (O.scan_cpu(v).astype(np.uint64) + carry).astype(np.uint32)
+
+    def check(self, device):
+        pass
+
 
 def _free_port():
     with socket.socket() as s:
@@ -58,40 +76,67 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, n, schedule, high, q):
+def _local_words(n_words, device, group):
+    """Stand-in for symmetric memory on CPU: a private array (OracleOps fills it with an all-gather)."""
+    return torch.zeros(n_words, dtype=torch.int64), None, 0
+
+
+def _no_words(n_words, device, group):
+    return None   # what _symmetric_words returns when there is no peer access
+
+
+def _worker(rank, world, port, n, schedule, high, q, words="local"):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
         full = O.scan_inputs(n, seed=77, high=high)
         lo, hi = sharded.chunk_bounds(n, world, rank)
-        x = torch.from_numpy(full[lo:hi].copy().view(np.int32))
-        scan = sharded.ShardedScan(hi - lo, "cpu", schedule=schedule, ops=OracleOps())
-        scan(x)
+        scan = sharded.ShardedScan(hi - lo, "cpu", schedule=schedule, ops=OracleOps(),
+                                   symmetric_words=_local_words if words == "local" else _no_words)
         expect = O.scan_cpu(full)[lo:hi]
-        ok = np.array_equal(x.numpy().view(np.uint32), expect)
-        q.put((rank, ok, scan.totals_int64()))
+        ok = True
+        for _ in range(3):   # three epochs: both halves of the word array, and the first one again
+            x = torch.from_numpy(full[lo:hi].copy().view(np.int32))
+            scan(x)
+            ok = ok and np.array_equal(x.numpy().view(np.uint32), expect)
+        q.put((rank, ok, scan.totals_int64(), scan.schedule))
     finally:
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("schedule", sharded.ShardedScan.SCHEDULES)
-@pytest.mark.parametrize("n,high", [(100000, 16), (4099, 0xFFFFFFFF), (7, 2)])
-def test_sharded_scan_two_ranks(schedule, n, high):
+def _run_two_ranks(n, schedule, high, words="local"):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, n, schedule, high, q)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, n, schedule, high, q, words)) for r in range(2)]
     for p in procs:
         p.start()
     results = [q.get(timeout=120) for _ in procs]
     for p in procs:
         p.join(timeout=60)
         assert p.exitcode == 0
+    return results
+
+
+# n = 3 leaves the second rank with an empty chunk.
+@pytest.mark.parametrize("schedule", sharded.ShardedScan.SCHEDULES + (sharded.ShardedScan.PEER_SCHEDULE,))
+@pytest.mark.parametrize("n,high", [(100000, 16), (4099, 0xFFFFFFFF), (7, 2), (3, 9)])
+def test_sharded_scan_two_ranks(schedule, n, high):
+    results = _run_two_ranks(n, schedule, high)
     full = O.scan_inputs(n, seed=77, high=high)
-    for rank, ok, totals in results:
+    for rank, ok, totals, used in results:
+        assert used == schedule
         assert ok, f"rank {rank} shard differs from the scan of the whole array"
         lo0, hi0 = sharded.chunk_bounds(n, 2, 0)
         assert totals[0] == int(full[lo0:hi0].sum(dtype=np.uint64)) & 0xFFFFFFFF
+
+
+def test_peer_words_falls_back_when_there_is_no_symmetric_memory():
+    """Without peer-writable words (no peer access, several nodes) every rank must end up on the same
+    collective schedule and still produce the scan of the whole array."""
+    for rank, ok, totals, used in _run_two_ranks(5000, sharded.ShardedScan.PEER_SCHEDULE, 16, words="none"):
+        assert used == "reduce_then_scan"
+        assert ok
 
 
 def test_chunk_bounds_cover_and_align():

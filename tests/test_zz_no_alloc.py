@@ -6,19 +6,19 @@ block on the allocator, processes whose device memory is all handed out): its
 look-back records live in a fixed array inside the library instead of in
 caller-provided scratch.  The test drives it through the C ABI twice in a row --
 the second call finds the first call's records still in the array -- and requires
-the same bits as prism_b200_scan.  This file sorts last on purpose, so that a run
-that stops at the first failure has already run every other test; it also passes
-when run alone in a fresh process.
+the same bits as prism_b200_scan and as the CPU oracle.
 """
 import ctypes
 import sys
 from pathlib import Path
 
+import numpy as np
 import pytest
 import torch
 
 ROOT = Path(__file__).resolve().parent.parent
 sys.path.insert(0, str(ROOT))
+from oracle import cpu_oracle as O  # noqa: E402
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
@@ -53,6 +53,8 @@ def test_static_scan_matches_scan_on_two_calls_in_a_row():
             if call > 0:  # the first call may still trigger the runtime's own lazy set-up
                 assert free_after >= free_before, "device memory was allocated during the call"
             assert torch.equal(got, want), f"call {call}: built-in scratch result differs from prism_b200_scan"
+            assert np.array_equal(got.cpu().numpy().view(np.uint32), O.scan_cpu(src.cpu().numpy().view(np.uint32))), \
+                f"call {call}: built-in scratch result differs from the oracle"
         assert _lib.last_error()[0] == 0
 
 

@@ -48,6 +48,15 @@ NCU_TRAFFIC_BYTES = {
 }
 
 
+def use_all_host_threads() -> int:
+    """torch.distributed.run exports OMP_NUM_THREADS=1 to its workers; the CPU arm is meant to use every core the
+    process may run on.  Must be called before NumPy (and with it the BLAS library) is imported."""
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    for var in ("OMP_NUM_THREADS", "OPENBLAS_NUM_THREADS", "MKL_NUM_THREADS", "GOTO_NUM_THREADS"):
+        os.environ[var] = str(n)
+    return n
+
+
 def load_peaks() -> dict:
     p = ROOT / "MEASURED_PEAKS.json"
     if p.exists():
@@ -124,7 +133,9 @@ class ClockSampler:
         self.thread = threading.Thread(target=pump, daemon=True)
         self.thread.start()
 
-    def stop(self) -> dict:
+    def stop(self, all_samples: bool = False) -> dict:
+        """Median SM clock of the samples taken under load: the half with the highest power draw, or
+        (all_samples) every sample, for a window that is load from end to end."""
         reasons: set[str] = set()
         if self.nvml is not None:
             self.stop_flag.set()
@@ -162,7 +173,7 @@ class ClockSampler:
         # the samples with the highest power draw are the ones taken under load
         if self.nvml is not None and self.samples:
             by_power = sorted(self.samples, key=lambda t: t[1])
-            load = sorted(c for c, _, _ in by_power[len(by_power) // 2:])
+            load = sorted(c for c, _, _ in (by_power if all_samples else by_power[len(by_power) // 2:]))
         else:
             load = sm[: max(1, len(sm) // 2)] if sm else []
         return {"sm_mhz": (load[len(load) // 2] if load else None), "sm_max_mhz": smax,
@@ -223,6 +234,60 @@ def time_steps(step, steps: int, warmup: int, world: int, reset=None):
     return max_over_ranks(sum(per), world), per
 
 
+def measure_host_link(dev, mib: int = 256) -> dict:
+    """Pinned host <-> device copy rates of this GPU's link, each direction alone, best of 3 (GB/s)."""
+    import torch
+    n = mib << 20
+    h = torch.empty(n, dtype=torch.uint8).pin_memory()
+    d = torch.empty(n, dtype=torch.uint8, device=dev)
+    out = {}
+    for name, (dst, src) in (("h2d_gbs", (d, h)), ("d2h_gbs", (h, d))):
+        best = float("inf")
+        for _ in range(4):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            dst.copy_(src, non_blocking=True)
+            b.record()
+            b.synchronize()
+            best = min(best, a.elapsed_time(b))
+        out[name] = n / (best * 1e-3) / 1e9
+    out["sample_mib"] = mib
+    return out
+
+
+def link_fraction(e2e_ms: float, h2d_bytes: float, d2h_bytes: float, link: dict) -> float:
+    """Time the link needs for the step's copies at its measured rates (the two directions run at once)
+    divided by the measured end-to-end time: 1.0 = the step costs nothing beyond its copies."""
+    need_ms = max(h2d_bytes / link["h2d_gbs"], d2h_bytes / link["d2h_gbs"]) / 1e6
+    return need_ms / e2e_ms
+
+
+def sustained_run(step, flops_per_step: float, seconds: float, gpu_index: int, peak_sustained: float) -> dict:
+    """The same launch back to back for `seconds`, with the clock sampler running over the whole window
+    (hundreds of samples), so that what the kernel sustains under the power cap is visible."""
+    import torch
+    step()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record(); step(); b.record(); b.synchronize()
+    reps = max(50, int(seconds * 1e3 / max(a.elapsed_time(b), 1e-3)))
+    sampler = ClockSampler(gpu_index)
+    sampler.start()
+    a.record()
+    for _ in range(reps):
+        step()
+    b.record()
+    b.synchronize()
+    clocks = sampler.stop(all_samples=True)
+    ms = a.elapsed_time(b) / reps
+    value = flops_per_step / (ms * 1e-3) / 1e12
+    return {"value": value, "unit": "TFLOP/s", "launches": reps, "window_s": ms * reps * 1e-3, "ms_per_launch": ms,
+            "sm_mhz_median": clocks.get("sm_mhz"), "power_w_max": clocks.get("power_w_max"), "reasons": clocks.get("reasons"),
+            "samples": clocks.get("samples"), "frac": value / peak_sustained,
+            "peak": peak_sustained, "peak_source": "measured cuBLAS bf16, back to back for seconds",
+            "gflops_per_sm_mhz": (value * 1e3 / clocks["sm_mhz"]) if clocks.get("sm_mhz") else None}
+
+
 def ref_gpu_lib():
     p = ROOT / "oracle" / "_ref" / "libprism_ref.so"
     if not p.exists():
@@ -234,6 +299,31 @@ def ref_gpu_lib():
     lib.ref_scan_workspace_size.restype = ctypes.c_size_t
     lib.ref_scan.argtypes = [ctypes.c_size_t, ctypes.c_void_p, ctypes.c_void_p]
     return lib
+
+
+def gemm_bf16_config(S: int, world: int) -> dict:
+    """The `config` of the bf16 workload; both arms print this one dict."""
+    rows = S // world
+    return {"workload": "gemm_bf16 %dx%dx%d, A and B K-major, C column-major, values 0.1*normal bf16" % (S, S, S),
+            "M": S, "N": S, "K": S, "sharding": f"rows of M over {world} GPU(s), B replicated, no collective",
+            "rows_per_gpu": rows, "l2": "inputs larger than L2 (A+B = %d MiB per GPU)" % ((rows + S) * S * 2 >> 20)}
+
+
+def sgemm_config(S: int, world: int) -> dict:
+    return {"workload": "sgemm %dx%dx%d row-major, kernel 5, A/B/C uniform[-1,1)" % (S, S, S), "M": S, "N": S, "K": S,
+            "alpha": 1.5, "beta": 0.5, "sharding": f"rows of M over {world} GPU(s), B replicated, no collective",
+            "rows_per_gpu": S // world,
+            "l2": "C restored from a pristine copy before every step (untimed), which also displaces L2"}
+
+
+def scan_config(n_total: int, world: int, schedule: str) -> dict:
+    return {"workload": f"scan n=2^{n_total.bit_length() - 1} int32 values in {{0,1}}, in place", "n": n_total,
+            "sharding": f"contiguous chunks over {world} GPU(s); " +
+            ("single pass" if world == 1 else
+             f"{schedule}: " + ("one launch per GPU: chunk total stored into every peer's memory over NVLink, then the scan; "
+                                "no collective" if schedule == "peer_words" else "one all-gather of per-shard totals")),
+            "elements_per_gpu": -(-n_total // world),
+            "l2": "input restored from a pristine copy before every step (untimed); array larger than L2"}
 
 
 # --------------------------------------------------------------------------- workloads (ours)
@@ -261,40 +351,61 @@ def run_gemm_bf16(args, world, rank, peaks):
     flops = 2.0 * S * S * S
     value = flops / (ms * 1e-3) / 1e12
 
-    # spot check of this rank's result against fp64 on a few rows/columns (bf16-rounded inputs)
-    n_idx = [0, 1, S // 2 - 1, S - 1]
-    ref = (B[n_idx].double() @ A.double().t()).cpu()
-    got = C[n_idx].double().cpu()
-    rms = float(ref.pow(2).mean().sqrt())
-    ok = bool(((got - ref).abs() <= 1e-2 * ref.abs() + 1e-2 * rms).all())
+    # spot check of this rank's result against fp64 on rows of C^T (= rows of B) that cover both CTAs of a pair and
+    # both row blocks of a 512-row tile, the middle and the end (bf16-rounded inputs)
+    n_idx = sorted({0, 127, 128, 255, 256, 383, 384, 511, S // 2 - 1, S // 2, S - 1})
+    A64 = A.double()
 
-    # end to end through the host-buffer operator
-    op = host.HostGemmBF16(rows, S, S, dev)
-    Ah = A.cpu().pin_memory(); Bh = B.cpu().pin_memory()
-    Ch = torch.empty((S, rows), dtype=torch.bfloat16).pin_memory()
+    def rows_ok(c_rows):
+        ref = (B[n_idx].double() @ A64.t()).cpu()
+        got = c_rows.double().cpu()
+        rms = float(ref.pow(2).mean().sqrt())
+        return bool(((got - ref).abs() <= 1e-2 * ref.abs() + 1e-2 * rms).all())
+
+    ok = rows_ok(C[n_idx])
+
+    # what the kernel sustains: back to back for seconds, clocks sampled over the whole window
+    sustained = sustained_run(lambda: plan(A, B, C), 2.0 * rows * S * S, 2.5, torch.cuda.current_device(),
+                              peaks["bf16_tflops_sustained"])
+
+    # end to end through the host-buffer operator: pinned host arrays in, pinned host array out
+    link = measure_host_link(dev)
+    op = sharded.ShardedHostGemmBF16(S, S, S, dev)
+    Ah = host.pinned_near(dev, (rows, S), torch.bfloat16); Ah.copy_(A)
+    Bh = host.pinned_near(dev, (S, S), torch.bfloat16); Bh.copy_(B)
+    Ch = host.pinned_near(dev, (S, rows), torch.bfloat16)
     e2e_steps = max(3, min(args.steps, 5))
-    e2e_total, _ = time_steps(lambda: op(Ah, Bh, Ch), e2e_steps, 1, world)
+    e2e_total, _ = time_steps(lambda: op(Ah, Bh, Ch), e2e_steps, 2, world)
     e2e_ms = e2e_total / e2e_steps
+    torch.cuda.synchronize()
+    e2e_ok = rows_ok(Ch[n_idx].to(dev))
+    del A64
     e2e = {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
            "h2d_bytes_per_step": op.h2d_bytes, "d2h_bytes_per_step": op.d2h_bytes,
-           "pipeline": "%d blocks of B rows, upload / kernel / download on three streams" % op.blocks}
+           "link_gbs": link, "frac_of_link": link_fraction(e2e_ms, op.h2d_bytes, op.d2h_bytes, link),
+           "spot_check_ok": e2e_ok,
+           "pipeline": ("%d blocks of B rows, upload / kernel / download on three streams" % op.steps) if world == 1 else
+                       ("per rank: its rows of A and 1/%d of B over PCIe; B completed by %d in-place NCCL all-gathers over "
+                        "NVLink into local HBM, each followed by the GEMM on that block of columns and its download"
+                        % (world, op.steps))}
 
     kernel_ms = sum(per) / len(per)     # this rank's kernel: rows x S x S
     achieved = 2.0 * rows * S * S / (kernel_ms * 1e-3) / 1e12
     peak = peaks["bf16_tflops"]
-    roofline = {"bound": "tensor", "kernel": ("cutlass_my_h100_match_no_tail_pair_wide<16> (tcgen05, cta_group::2, 512 x 256 tiles)"
+    roofline = {"bound": "tensor", "kernel": ("cutlass_my_h100_match_no_tail_pair_wide[_split]<16> (tcgen05, cta_group::2, 512 x 256 tiles; "
+                                               "a partly filled last wave is cut along K)"
                            if (rows % 256 == 0 and S % 512 == 0 and rows * S * S >= 2 ** 35)
                            else "cutlass_my_h100_match_no_tail family (tcgen05), form chosen by shape"), "achieved": achieved,
                 "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                "peak_source": f"{peaks['source']} cuBLAS bf16 burst", "frac_of_sustained": achieved / peaks["bf16_tflops_sustained"],
+                "peak_source": f"{peaks['source']} cuBLAS bf16 burst (the timed region is a burst of %d launches)" % args.steps,
                 "frac_of_nominal_2250": achieved / 2250.0,
                 "traffic": NCU_TRAFFIC_BYTES["gemm_bf16"] if (S == GEMM_S and world == 1) else None}
     line = {"metric": "bf16 GEMM TFLOP/s (D = A*B^T, M=N=K=%d, fp32 accumulate, bf16 out)" % S, "value": value,
             "unit": "TFLOP/s", "ms_per_step": ms, "scaling": "strong", "dtype": "bf16",
-            "config": {"workload": "gemm_bf16 %dx%dx%d, A and B K-major, C column-major, values 0.1*normal bf16" % (S, S, S),
-                       "M": S, "N": S, "K": S, "sharding": f"rows of M over {world} GPU(s), B replicated, no collective",
-                       "rows_per_gpu": rows, "l2": "inputs larger than L2 (A+B = %d MiB per GPU)" % ((rows + S) * S * 2 >> 20)},
-            "roofline": roofline, "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "spot_check_ok": ok}
+            "config": gemm_bf16_config(S, world),
+            "roofline": roofline, "sustained": sustained, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
+            "spot_check_ok": ok and e2e_ok, "parity": "fp64 NumPy/torch on the bf16-rounded inputs; unpinned by the reference "
+            "(its kernel is wgmma, sm_90a only)"}
     return line
 
 
@@ -340,9 +451,7 @@ def run_sgemm(args, world, rank, peaks, steps=None, warmup=None):
     peak_at_clock = 148 * 128 * 2 * sm_load * 1e6 / 1e12
     return {"metric": "FP32 SGEMM TFLOP/s (C = 1.5*A*B + 0.5*C, M=N=K=%d, pure FFMA)" % S,
             "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms, "scaling": "strong", "dtype": "f32",
-            "config": {"workload": "sgemm %dx%dx%d row-major, kernel 5, A/B/C uniform[-1,1)" % (S, S, S), "sharding":
-                       f"rows of M over {world} GPU(s), B replicated, no collective", "rows_per_gpu": rows,
-                       "l2": "C restored from a pristine copy before every step (untimed), which also displaces L2"},
+            "config": sgemm_config(S, world),
             "roofline": {"bound": "fp32_ffma", "kernel": "my_sgemm_kernel_5<packed>", "achieved": achieved,
                          "peak": peak_nominal, "unit": "TFLOP/s", "frac": achieved / peak_nominal,
                          "peak_source": "148 SMs x 128 FMA/clk x 2 x %.0f MHz (max SM clock)" % sm_max,
@@ -372,7 +481,7 @@ def run_scan(args, world, rank, peaks, steps=None, warmup=None):
     sampler.start()
     l0 = pb.launch_count()
     total_ms, per = time_steps(lambda: scan(x), steps, warmup, world, reset=lambda: x.copy_(src))
-    per_step = 1 if world == 1 else (3 if scan.schedule == "peer_words" else 2)
+    per_step = 1 if (world == 1 or scan.schedule == "peer_words") else 2
     launches = (pb.launch_count() - l0) - warmup * per_step
     clocks = sampler.stop()
     ms = total_ms / steps
@@ -395,12 +504,7 @@ def run_scan(args, world, rank, peaks, steps=None, warmup=None):
     peak = peaks["hbm_gbs"]
     return {"metric": "uint32 inclusive scan GB/s (8 bytes per element)", "value": nbytes / (ms * 1e-3) / 1e9,
             "unit": "GB/s", "ms_per_step": ms, "scaling": "strong" if world > 1 else "weak", "dtype": "u32",
-            "config": {"workload": f"scan n=2^{n_total.bit_length() - 1} int32 values in {{0,1}}, in place",
-                       "sharding": f"contiguous chunks over {world} GPU(s); " +
-                       ("single pass" if world == 1 else
-                        f"{scan.schedule}: " + ("per-shard totals stored into peer memory over NVLink, no collective"
-                                                if scan.schedule == "peer_words" else "one all-gather of per-shard totals")),
-                       "elements_per_gpu": n, "l2": "input restored from a pristine copy before every step (untimed); array larger than L2"},
+            "config": scan_config(n_total, world, scan.schedule),
             "roofline": {"bound": "hbm", "kernel": "scan_kernel", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "peak_source": f"{peaks['source']} copy bandwidth",
                          "frac_of_nominal_8000": achieved / 8000.0,
@@ -470,16 +574,35 @@ def cpu_sgemm(sample_rows: int, reps: int):
     return 2.0 * sample_rows * S * S, times
 
 
+def ref_cpu_lib():
+    """The reference's own CPU scan loop (evals/4090_scan/scan_harness.cuh:30-36), compiled into oracle/_ref."""
+    p = ROOT / "oracle" / "_ref" / "libref_cpu.so"
+    if not p.exists():
+        return None
+    lib = ctypes.CDLL(str(p))
+    lib.ref_scan_cpu.argtypes = [ctypes.c_size_t, ctypes.c_void_p, ctypes.c_void_p]
+    lib.ref_scan_cpu.restype = None
+    return lib
+
+
 def cpu_scan(n: int, reps: int):
+    """Returns (bytes, times, kind): the reference's scan_cpu when it was built, else the NumPy port."""
     import numpy as np
     from oracle import cpu_oracle as O
     x = O.scan_inputs(n, seed=0, high=2)
+    lib = ref_cpu_lib()
+    out = np.empty_like(x)
     times = []
     for _ in range(reps):
         t0 = time.perf_counter()
-        O.scan_cpu(x)
+        if lib is not None:
+            lib.ref_scan_cpu(n, x.ctypes.data, out.ctypes.data)
+        else:
+            out = O.scan_cpu(x)
         times.append(time.perf_counter() - t0)
-    return 8.0 * n, times
+    if lib is not None:
+        assert np.array_equal(out, O.scan_cpu(x))
+    return 8.0 * n, times, ("reference" if lib is not None else "port")
 
 
 def cpu_threads() -> int:
@@ -507,41 +630,47 @@ def cpu_baseline(workload: str) -> dict:
         return {"value": work / min(times) / 1e12, "unit": "TFLOP/s", "cores": cpu_threads(), "kind": "port",
                 "sample": f"NumPy float32 1.5*A@B+0.5*C, {rows} of the 4096 rows of M, best of 3; os.cpu_count() = {os.cpu_count()}"}
     n = 1 << 26
-    work, times = cpu_scan(n, 3)
-    return {"value": work / min(times) / 1e9, "unit": "GB/s", "cores": 1, "kind": "port",
-            "sample": f"np.cumsum uint32 (single thread; the same loop as the reference's scan_cpu) on 2^26 of the 2^28 elements, best of 3"}
+    work, times, kind = cpu_scan(n, 3)
+    return {"value": work / min(times) / 1e9, "unit": "GB/s", "cores": 1, "kind": kind,
+            "sample": ("the reference's own scan_cpu loop (oracle/_ref/libref_cpu.so)" if kind == "reference" else
+                       "np.cumsum uint32 (the same loop as the reference's scan_cpu)") +
+                      ", single thread, on 2^26 of the 2^28 elements, best of 3"}
 
 
 def run_reference_arm(args):
-    """CPU implementation of the path on the host cores; each step is a bounded sample of the workload."""
-    world = int(os.environ.get("WORLD_SIZE", "1"))
+    """CPU implementation of the path on the host cores; each step is a bounded sample of the workload.
+    The line carries the same `config` as the GPU arm at this number of GPUs; what a step covers is in `sample`."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return None
+    threads = use_all_host_threads()      # before NumPy loads its BLAS: torchrun exports OMP_NUM_THREADS=1
+    world = max(1, args.gpus)
     steps, warmup = args.steps, args.warmup
+    kind = "port"
     if args.workload == "gemm_bf16":
         rows = 1024
         work, times = cpu_gemm_bf16(rows, steps + warmup)
         unit, scale = "TFLOP/s", 1e12
-        metric = "bf16 GEMM TFLOP/s (D = A*B^T, M=N=K=8192, fp32 accumulate, bf16 out)"
+        metric = "bf16 GEMM TFLOP/s (D = A*B^T, M=N=K=%d, fp32 accumulate, bf16 out)" % GEMM_S
         sample = f"NumPy float32 matmul on bf16-rounded values; each step = {rows} of the 8192 rows of M against all of B"
-        cfg = {"workload": "gemm_bf16 8192x8192x8192, A and B K-major, C column-major, values 0.1*normal bf16"}
+        cfg = gemm_bf16_config(GEMM_S, world)
         dtype, cores = "f32 on bf16-rounded inputs", cpu_threads()
     elif args.workload == "sgemm":
         rows = 1024
         work, times = cpu_sgemm(rows, steps + warmup)
         unit, scale = "TFLOP/s", 1e12
-        metric = "FP32 SGEMM TFLOP/s (C = 1.5*A*B + 0.5*C, M=N=K=4096, pure FFMA)"
+        metric = "FP32 SGEMM TFLOP/s (C = 1.5*A*B + 0.5*C, M=N=K=%d, pure FFMA)" % SGEMM_S
         sample = f"NumPy float32; each step = {rows} of the 4096 rows"
-        cfg = {"workload": "sgemm 4096x4096x4096 row-major"}
+        cfg = sgemm_config(SGEMM_S, world)
         dtype, cores = "f32", cpu_threads()
     else:
         n = 1 << 25
-        work, times = cpu_scan(n, steps + warmup)
+        work, times, kind = cpu_scan(n, steps + warmup)
         unit, scale = "GB/s", 1e9
         metric = "uint32 inclusive scan GB/s (8 bytes per element)"
-        sample = "np.cumsum uint32, single thread; each step = 2^25 elements"
-        cfg = {"workload": "scan int32 values in {0,1}, in place"}
+        sample = ("the reference's own scan_cpu loop" if kind == "reference" else "np.cumsum uint32") + \
+            ", single thread; each step = 2^25 elements"
+        cfg = scan_config(SCAN_N1 if world == 1 else SCAN_NG, world, args.scan_schedule or "peer_words")
         dtype, cores = "u32", 1
     timed = times[warmup:]
     ms = 1e3 * sum(timed) / len(timed)
@@ -549,9 +678,10 @@ def run_reference_arm(args):
     return {"impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": args.gpus, "steps": steps,
             "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": dtype, "data": "synthetic", "config": cfg,
-            "cpu_baseline": {"value": value, "unit": unit, "cores": cores, "kind": "port", "sample": sample +
-                             f"; os.cpu_count() = {os.cpu_count()}; the reference has no CPU GEMM and its bf16 kernel cannot "
-                             "run on sm_100, so the CPU path is NumPy as the benchmark definition prescribes"},
+            "cpu_baseline": {"value": value, "unit": unit, "cores": cores, "kind": kind, "sample": sample +
+                             f"; host threads offered to BLAS = {threads}, os.cpu_count() = {os.cpu_count()}; the reference has "
+                             "no CPU GEMM and its bf16 kernel cannot run on sm_100, so the CPU path of the GEMMs is NumPy as "
+                             "the benchmark definition prescribes"},
             "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
 

@@ -30,30 +30,37 @@
 
 extern "C" int ref_sgemm(int kernel_num, int M, int N, int K, float alpha, float* A, float* B, float beta, float* C) {
     const int cdiv128_m = (M + 127) / 128, cdiv128_n = (N + 127) / 128;
+    // The reference kernels have no bounds checks (kernel 2 excepted): a shape that does not divide the
+    // kernel's tile would read and write out of bounds, so it is refused here (return 2).
+    if (M <= 0 || N <= 0 || K <= 0) return 2;
     switch (kernel_num) {
     case 1:  // runner.cu:135-141
+        if ((static_cast<long long>(M) * N) % 256) return 2;
         my_sgemm_kernel_1<<<(M * N + 255) / 256, 256>>>(M, N, K, alpha, A, B, beta, C, 256);
         break;
     case 2:  // runner.cu:143-150
         my_sgemm_kernel_2<<<(M * N + 1023) / 1024, 1024>>>(M, N, K, alpha, A, B, beta, C, 32);
         break;
     case 3: {  // runner.cu:152-161 (the harness's "kernel 3" is the shared-memory block kernel)
+        if (M % 32 || N % 32 || K % 32) return 2;
         const int nbn = (N + 31) / 32;
         sgemm_shared_mem_block<32><<<((M + 31) / 32) * nbn, 32 * 32>>>(M, N, K, alpha, A, B, beta, C, nbn);
         break;
     }
     case 4:  // runner.cu:163-177 (the >= 128 branch)
-        if (M < 128 || N < 128) return 2;
+        if (M % 128 || N % 128 || K % 8) return 2;
         my_sgemm_kernel_4<128, 128, 8, 8, 8>
             <<<cdiv128_m * cdiv128_n, (128 * 128) / (8 * 8), (128 * 8 + 8 * 128) * sizeof(float)>>>(
                 M, N, K, alpha, A, B, beta, C, cdiv128_n);
         break;
     case 5:  // runner.cu:191-243
+        if (M % 128 || N % 128 || K % 16) return 2;
         my_sgemm_kernel_5<128, 128, 16, 64, 64, 4, 8, 4, 128>
             <<<cdiv128_m * cdiv128_n, 128, (128 * 16 + 16 * 128) * sizeof(float)>>>(M, N, K, alpha, A, B, beta, C,
                                                                                   cdiv128_n);
         break;
     case 6:  // generated/my_sgemm_kernel_3.cu, never launched by the harness; 64x64x8 tile, 8x8 per thread
+        if (M % 64 || N % 64 || K % 8) return 2;
         my_sgemm_kernel_3<64, 64, 8, 8, 8><<<((M + 63) / 64) * ((N + 63) / 64), 64, 2 * 1024 * sizeof(float)>>>(
             M, N, K, alpha, A, B, beta, C, (N + 63) / 64);
         break;

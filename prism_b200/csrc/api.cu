@@ -15,7 +15,9 @@ std::mutex g_mu;
 int g_code = 0;
 char g_msg[256] = "";
 std::atomic<unsigned long long> g_launches{0};
-uint32_t* g_status = nullptr;  // pinned + mapped; the same address is valid on every device (UVA)
+// One status word per device index, pinned + mapped; the same addresses are valid on every device (UVA).
+constexpr int kStatusWords = 64;
+uint32_t* g_status = nullptr;
 bool g_status_failed = false;
 }  // namespace
 
@@ -39,14 +41,14 @@ uint32_t* device_status_word() {
     std::lock_guard<std::mutex> lk(g_mu);
     if (g_status || g_status_failed) return g_status;
     void* p = nullptr;
-    cudaError_t e = cudaHostAlloc(&p, 64, cudaHostAllocPortable | cudaHostAllocMapped);
+    cudaError_t e = cudaHostAlloc(&p, kStatusWords * sizeof(uint32_t), cudaHostAllocPortable | cudaHostAllocMapped);
     if (e != cudaSuccess) {
         g_status_failed = true;
         g_code = PRISM_B200_ERR_CUDA;
         snprintf(g_msg, sizeof(g_msg), "cudaHostAlloc(status word): %s", cudaGetErrorString(e));
         return nullptr;
     }
-    memset(p, 0, 64);
+    memset(p, 0, kStatusWords * sizeof(uint32_t));
     g_status = static_cast<uint32_t*>(p);
     return g_status;
 }
@@ -86,16 +88,17 @@ extern "C" int prism_b200_version(void) { return 100; }
 
 extern "C" int prism_b200_last_error(int* code, char* msg, size_t len) {
     std::lock_guard<std::mutex> lk(g_mu);
-    if (g_status) {
-        uint32_t dev = *reinterpret_cast<volatile uint32_t*>(g_status);
-        if (dev != DEV_OK) {
+    for (int d = 0; g_status && d < kStatusWords; ++d) {
+        const uint32_t st = reinterpret_cast<volatile uint32_t*>(g_status)[d];
+        if (st != DEV_OK) {
             g_code = PRISM_B200_ERR_DEVICE_TIMEOUT;
-            const char* which = dev == DEV_SCAN_LOOKBACK_TIMEOUT ? "scan look-back"
-                              : dev == DEV_SGEMM_PIPE_TIMEOUT    ? "sgemm smem pipeline"
-                              : dev == DEV_GEMM_PIPE_TIMEOUT     ? "bf16 gemm pipeline"
-                              : dev == DEV_SELFTEST_TIMEOUT      ? "self-test (as requested)"
-                                                                  : "unknown";
-            snprintf(g_msg, sizeof(g_msg), "device-side wait ran out in %s (status 0x%08x)", which, dev);
+            const char* which = st == DEV_SCAN_LOOKBACK_TIMEOUT ? "scan look-back"
+                              : st == DEV_SGEMM_PIPE_TIMEOUT    ? "sgemm smem pipeline"
+                              : st == DEV_GEMM_PIPE_TIMEOUT     ? "bf16 gemm pipeline"
+                              : st == DEV_SELFTEST_TIMEOUT      ? "self-test (as requested)"
+                                                                 : "unknown";
+            snprintf(g_msg, sizeof(g_msg), "device %d: device-side wait ran out in %s (status 0x%08x)", d, which, st);
+            break;
         }
     }
     if (code) *code = g_code;
@@ -110,7 +113,7 @@ extern "C" void prism_b200_clear_error(void) {
     std::lock_guard<std::mutex> lk(g_mu);
     g_code = 0;
     g_msg[0] = '\0';
-    if (g_status) *reinterpret_cast<volatile uint32_t*>(g_status) = DEV_OK;
+    for (int d = 0; g_status && d < kStatusWords; ++d) reinterpret_cast<volatile uint32_t*>(g_status)[d] = DEV_OK;
 }
 
 extern "C" unsigned long long prism_b200_launch_count(void) {

@@ -6,6 +6,8 @@
 #include <stdint.h>
 #include <stddef.h>
 
+#include <mutex>
+
 #include "../../include/prism_b200.h"
 
 namespace prism_b200 {
@@ -15,10 +17,15 @@ int  set_error(int code, const char* fmt, ...);
 int  cuda_failed(cudaError_t e, const char* what);
 void count_launch(unsigned n = 1);
 
-// Device-visible status word in pinned, mapped host memory.  Kernels write a
-// non-zero code here when a bounded wait gives up; the host reads it without a
-// CUDA call.  Returns nullptr (and sets the error state) if it cannot be set up.
+// Device-visible status words in pinned, mapped host memory, one per device index (64).
+// Kernels write a non-zero code into their device's word when a bounded wait gives up;
+// the host reads them without a CUDA call.  Returns the first word's address, or nullptr
+// (and sets the error state) if the buffer cannot be set up.
 uint32_t* device_status_word();
+
+// Gives back the bf16 GEMM's split-K workspace of (current device, stream), if there is one
+// (called when a stream that the library owns is destroyed).
+void release_gemm_split_workspace(cudaStream_t stream);
 
 // Codes written into the status word by kernels.
 enum : uint32_t {
@@ -46,12 +53,15 @@ static __device__ uint32_t* d_status_word;
 
 static inline int bind_status_word() {
     static bool bound[64] = {};
+    static std::mutex mu;   // entry points may be called from several host threads
+    std::lock_guard<std::mutex> lk(mu);
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return cuda_failed(e, "cudaGetDevice");
     if (dev >= 0 && dev < 64 && bound[dev]) return PRISM_B200_OK;
     uint32_t* p = device_status_word();
     if (!p) return PRISM_B200_ERR_CUDA;
+    if (dev >= 0 && dev < 64) p += dev;   // this device's own word
     e = cudaMemcpyToSymbol(d_status_word, &p, sizeof(p));
     if (e != cudaSuccess) return cuda_failed(e, "cudaMemcpyToSymbol(status word)");
     if (dev >= 0 && dev < 64) bound[dev] = true;

@@ -414,6 +414,29 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t cluster_bar_addr) {
                  : "memory");
 }
 
+// Unwind path of the two-CTA kernels' producers: loads already issued must land before the CTA gives
+// its shared memory back.  All loads of a pair complete on the LEADER's "full" barriers, so the
+// leader waits for the armed ones (never_flag stays 0, so the wait is not cut short by the abort
+// flag); the other CTA cannot watch those barriers and instead lets the longest a load can take
+// pass.  Both are bounded.
+__device__ __forceinline__ void drain_pair_loads(uint64_t* full_bar, int stage, uint32_t phase, int armed, int stages,
+                                                 bool leader, volatile uint32_t* never_flag) {
+    if (leader) {
+        int s = stage;
+        uint32_t ph = phase;
+        for (int i = 0; i < armed; ++i) {
+            if (--s < 0) {
+                s = stages - 1;
+                ph ^= 1u;
+            }
+            mbar_wait_bounded(&full_bar[s], ph, never_flag, 2000000ull);
+        }
+    } else if (armed > 0) {
+        const unsigned long long t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+    }
+}
+
 template <int GROUP>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(g16::THREADS, 1)
 cutlass_my_h100_match_no_tail_pair(int M, int N, int K, __nv_bfloat16* C, const __grid_constant__ CUtensorMap tensorMapA,
@@ -480,6 +503,7 @@ cutlass_my_h100_match_no_tail_pair(int M, int N, int K, __nv_bfloat16* C, const 
             asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tensorMapB)) : "memory");
             int stage = 0;
             uint32_t phase = 0;
+            int armed = 0;   // stages loaded and not known to be consumed (for the unwind path)
             for (int t = pair; t < total_tiles && !timed_out; t += pairs) {
                 int tm, tn;
                 tile_coords(t, tiles_m, tiles_n, tm, tn, GROUP);
@@ -496,12 +520,14 @@ cutlass_my_h100_match_no_tail_pair(int M, int N, int K, __nv_bfloat16* C, const 
                     if (leader) mbar_arrive_expect_tx(&full_bar[stage], 2 * P_::STAGE_BYTES);  // both CTAs' bytes
                     tma_load_2d_pair(p_dst, &tensorMapB, kb * BLOCK_K, n_row, leader_full);
                     tma_load_2d_pair(q_dst, &tensorMapA, kb * BLOCK_K, m_row, leader_full);
+                    armed = armed < STAGES ? armed + 1 : STAGES;
                     if (++stage == STAGES) {
                         stage = 0;
                         phase ^= 1u;
                     }
                 }
             }
+            if (timed_out || *abort_flag) drain_pair_loads(full_bar, stage, phase, armed, STAGES, leader, never_flag);
         }
     } else if (warp == 1) {
         // ------------------------- MMA issuer (leader only) -------------------------
@@ -650,11 +676,84 @@ struct WideCfg {
 };
 }  // namespace g16
 
-template <int GROUP>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(g16::WideCfg::THREADS, 1)
-cutlass_my_h100_match_no_tail_pair_wide(int M, int N, int K, __nv_bfloat16* C,
-                                        const __grid_constant__ CUtensorMap tensorMapA,
-                                        const __grid_constant__ CUtensorMap tensorMapB) {
+// What the split form needs beyond the reference's parameter list.
+struct SplitArgs {
+    float* partials;      // one 512 x 256 fp32 slot per CTA pair
+    uint32_t* flags;      // 16 words per pair (one per epilogue warp of the pair); a slot is valid when they hold `epoch`
+    uint32_t epoch;       // differs from every earlier launch that used this workspace
+};
+
+// The work of one CTA pair: `full` whole tiles (tile = i * pairs + pair), then up to two segments of
+// the last, partly filled wave.  Without SPLIT a pair simply takes every pairs-th tile.  With SPLIT
+// the R = tiles mod pairs tiles of the last wave are cut along K into pairs equal ranges of
+// k-blocks (R * k_blocks / pairs each, less than one tile), so a pair gets the tail of one tile
+// and/or the head of the next:
+//   kb0 > 0   the pair contributes: it writes its fp32 accumulators to its slot and raises its flags;
+//   kb0 == 0  the pair finishes the tile: it adds the slots of the pairs that hold the rest of the
+//             tile, in pair order (so the result does not depend on timing), and stores bf16.
+// A pair contributes first and finishes last, and the pairs it waits for contribute first too, so
+// the wait is short; a pair never waits for a pair that waits for it.
+struct PairPlan {
+    int full;
+    int segs;
+    int tile0, kb0_0, kb1_0;               // first segment (tail or middle of a tile, or a head)
+    int tile1, kb1_1;                      // second segment: always the head of the next tile (kb0 = 0)
+    long long rem_units, rem_first_tile;   // k-blocks of the split wave; its first tile
+};
+
+template <bool SPLIT>
+__host__ __device__ __forceinline__ PairPlan make_pair_plan(int pair, int pairs, int total_tiles, int k_blocks) {
+    PairPlan p;
+    p.segs = 0;
+    p.tile0 = p.tile1 = p.kb0_0 = p.kb1_0 = p.kb1_1 = 0;
+    p.rem_units = 0;
+    p.rem_first_tile = total_tiles;
+    if constexpr (!SPLIT) {
+        p.full = pair < total_tiles ? (total_tiles - pair + pairs - 1) / pairs : 0;
+    } else {
+        p.full = total_tiles / pairs;
+        const int rem = total_tiles - p.full * pairs;
+        p.rem_first_tile = static_cast<long long>(p.full) * pairs;
+        p.rem_units = static_cast<long long>(rem) * k_blocks;
+        const long long r0 = p.rem_units * pair / pairs, r1 = p.rem_units * (pair + 1) / pairs;
+        if (r1 > r0) {
+            const int t0 = static_cast<int>(r0 / k_blocks), kb0 = static_cast<int>(r0 % k_blocks);
+            const long long len = r1 - r0;
+            const int first = static_cast<int>(len < k_blocks - kb0 ? len : k_blocks - kb0);
+            p.tile0 = static_cast<int>(p.rem_first_tile) + t0;
+            p.kb0_0 = kb0;
+            p.kb1_0 = kb0 + first;
+            p.segs = 1;
+            if (len > first) {   // less than one tile per pair, so the rest lies in the next tile
+                p.tile1 = p.tile0 + 1;
+                p.kb1_1 = static_cast<int>(len - first);
+                p.segs = 2;
+            }
+        }
+    }
+    return p;
+}
+
+__device__ __forceinline__ void plan_item(const PairPlan& p, int i, int pair, int pairs, int k_blocks, int& tile, int& kb0,
+                                          int& kb1) {
+    if (i < p.full) {
+        tile = i * pairs + pair;
+        kb0 = 0;
+        kb1 = k_blocks;
+    } else if (i == p.full) {
+        tile = p.tile0;
+        kb0 = p.kb0_0;
+        kb1 = p.kb1_0;
+    } else {
+        tile = p.tile1;
+        kb0 = 0;
+        kb1 = p.kb1_1;
+    }
+}
+
+template <int GROUP, bool SPLIT>
+__device__ __forceinline__ void pair_wide_body(int M, int N, int K, __nv_bfloat16* C, const CUtensorMap* tensorMapA,
+                                               const CUtensorMap* tensorMapB, const SplitArgs& split) {
     using namespace g16;
     using W_ = WideCfg;
     constexpr int STAGES = W_::STAGES;
@@ -669,6 +768,7 @@ cutlass_my_h100_match_no_tail_pair_wide(int M, int N, int K, __nv_bfloat16* C,
     uint64_t* acc_empty_bar = acc_full_bar + 1;    // [1], only the leader's is used
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty_bar + 1);
     volatile uint32_t* abort_flag = tmem_slot + 1;
+    volatile uint32_t* never_flag = tmem_slot + 2;  // stays 0: lets the unwind path wait although abort is set
     unsigned char* epi_smem = ring + STAGES * W_::STAGE_BYTES + W_::BAR_BYTES;   // 128-byte aligned
 
     const int warp = threadIdx.x >> 5;
@@ -681,6 +781,8 @@ cutlass_my_h100_match_no_tail_pair_wide(int M, int N, int K, __nv_bfloat16* C,
     const int tiles_n = N / W_::TILE_N;
     const int total_tiles = tiles_m * tiles_n;
     const int k_blocks = K / BLOCK_K;
+    const PairPlan plan = make_pair_plan<SPLIT>(pair, pairs, total_tiles, k_blocks);
+    const int items = plan.full + plan.segs;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -690,6 +792,7 @@ cutlass_my_h100_match_no_tail_pair_wide(int M, int N, int K, __nv_bfloat16* C,
         mbar_init(acc_full_bar, 1);
         mbar_init(acc_empty_bar, 2 * W_::EPI_WARPS);
         *abort_flag = 0;
+        *never_flag = 0;
         fence_barrier_init();
     }
     if (warp == 1) {
@@ -709,17 +812,19 @@ cutlass_my_h100_match_no_tail_pair_wide(int M, int N, int K, __nv_bfloat16* C,
     if (warp == 0) {
         // ------------------------- TMA producer (both CTAs) -------------------------
         if (lane == 0) {
-            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tensorMapA)) : "memory");
-            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tensorMapB)) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tensorMapA)) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tensorMapB)) : "memory");
             int stage = 0;
             uint32_t phase = 0;
-            for (int t = pair; t < total_tiles && !timed_out; t += pairs) {
-                int tm, tn;
+            int armed = 0;   // stages loaded and not known to be consumed (for the unwind path)
+            for (int i = 0; i < items && !timed_out; ++i) {
+                int t, kb0, kb1, tm, tn;
+                plan_item(plan, i, pair, pairs, k_blocks, t, kb0, kb1);
                 tile_coords(t, tiles_m, tiles_n, tm, tn, GROUP);
                 // This CTA's two n blocks and its half of the m rows.
                 const int n_row0 = tn * W_::TILE_N + static_cast<int>(rank) * 256;
                 const int m_row = tm * W_::TILE_M + static_cast<int>(rank) * W_::HALF;
-                for (int kb = 0; kb < k_blocks; ++kb) {
+                for (int kb = kb0; kb < kb1; ++kb) {
                     if (!mbar_wait_bounded_sleepy(&empty_bar[stage], phase ^ 1u, abort_flag, 40)) {
                         timed_out = true;
                         break;
@@ -727,15 +832,17 @@ cutlass_my_h100_match_no_tail_pair_wide(int M, int N, int K, __nv_bfloat16* C,
                     unsigned char* dst = ring + stage * W_::STAGE_BYTES;
                     const uint32_t leader_full = cluster_addr(&full_bar[stage], 0);
                     if (leader) mbar_arrive_expect_tx(&full_bar[stage], 2 * W_::STAGE_BYTES);
-                    tma_load_2d_pair(dst, &tensorMapB, kb * BLOCK_K, n_row0, leader_full);
-                    tma_load_2d_pair(dst + W_::BLOCK_BYTES, &tensorMapB, kb * BLOCK_K, n_row0 + W_::HALF, leader_full);
-                    tma_load_2d_pair(dst + 2 * W_::BLOCK_BYTES, &tensorMapA, kb * BLOCK_K, m_row, leader_full);
+                    tma_load_2d_pair(dst, tensorMapB, kb * BLOCK_K, n_row0, leader_full);
+                    tma_load_2d_pair(dst + W_::BLOCK_BYTES, tensorMapB, kb * BLOCK_K, n_row0 + W_::HALF, leader_full);
+                    tma_load_2d_pair(dst + 2 * W_::BLOCK_BYTES, tensorMapA, kb * BLOCK_K, m_row, leader_full);
+                    armed = armed < STAGES ? armed + 1 : STAGES;
                     if (++stage == STAGES) {
                         stage = 0;
                         phase ^= 1u;
                     }
                 }
             }
+            if (timed_out || *abort_flag) drain_pair_loads(full_bar, stage, phase, armed, STAGES, leader, never_flag);
         }
     } else if (warp == 1) {
         // ------------------------- MMA issuer (leader only) -------------------------
@@ -743,13 +850,15 @@ cutlass_my_h100_match_no_tail_pair_wide(int M, int N, int K, __nv_bfloat16* C,
             int stage = 0;
             uint32_t phase = 0;
             uint32_t tile_phase = 0;
-            for (int t = pair; t < total_tiles && !timed_out; t += pairs) {
+            for (int i = 0; i < items && !timed_out; ++i) {
+                int t, kb0, kb1;
+                plan_item(plan, i, pair, pairs, k_blocks, t, kb0, kb1);
                 if (!mbar_wait_bounded(acc_empty_bar, tile_phase ^ 1u, abort_flag)) {   // both CTAs drained both accumulators
                     timed_out = true;
                     break;
                 }
                 tc_fence_after();
-                for (int kb = 0; kb < k_blocks; ++kb) {
+                for (int kb = kb0; kb < kb1; ++kb) {
                     if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag)) {
                         timed_out = true;
                         break;
@@ -761,7 +870,7 @@ cutlass_my_h100_match_no_tail_pair_wide(int M, int N, int K, __nv_bfloat16* C,
                     const uint64_t q_desc = smem_desc_k_sw128(base + 2 * W_::BLOCK_BYTES);
 #pragma unroll
                     for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
-                        const uint32_t accumulate = (kb | k) != 0 ? 1u : 0u;
+                        const uint32_t accumulate = (kb != kb0 || k != 0) ? 1u : 0u;
                         umma_bf16_pair(tmem_base, p0_desc + 2u * k, q_desc + 2u * k, IDESC, accumulate);
                         umma_bf16_pair(tmem_base + 256u, p1_desc + 2u * k, q_desc + 2u * k, IDESC, accumulate);
                     }
@@ -785,8 +894,12 @@ cutlass_my_h100_match_no_tail_pair_wide(int M, int N, int K, __nv_bfloat16* C,
         const int quarter = warp & 3;
         const int block = (warp - 2) >> 2;
         uint32_t tile_phase = 0;
-        for (int t = pair; t < total_tiles; t += pairs) {
-            int tm, tn;
+        // Row of this lane inside the pair's 512-row tile, and this warp's flag inside a pair's 16.
+        const int tile_row = static_cast<int>(rank) * 256 + block * W_::HALF + quarter * 32 + lane;
+        const int flag_idx = static_cast<int>(rank) * W_::EPI_WARPS + (warp - 2);
+        for (int i = 0; i < items; ++i) {
+            int t, kb0, kb1, tm, tn;
+            plan_item(plan, i, pair, pairs, k_blocks, t, kb0, kb1);
             tile_coords(t, tiles_m, tiles_n, tm, tn, GROUP);
             const bool ready = lane != 0 || mbar_wait_bounded_sleepy(acc_full_bar, tile_phase, abort_flag, 200);
             if (!__all_sync(0xffffffffu, ready)) {
@@ -794,6 +907,59 @@ cutlass_my_h100_match_no_tail_pair_wide(int M, int N, int K, __nv_bfloat16* C,
                 break;
             }
             tc_fence_after();
+            const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(block * 256);
+            if (SPLIT && kb0 > 0) {
+                // Contributor: fp32 accumulators to this pair's slot, column by column so that the 32 lanes
+                // (32 consecutive rows) write one 128-byte line per store; then this warp's flag.
+                float* slot = split.partials + static_cast<size_t>(pair) * (W_::TILE_N * W_::TILE_M) + tile_row;
+#pragma unroll 1
+                for (int c0 = 0; c0 < W_::TILE_M; c0 += 32) {
+                    uint32_t r[32];
+                    tmem_ld_32cols(t_row + c0, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) __stcg(slot + static_cast<size_t>(c0 + e) * W_::TILE_N, __uint_as_float(r[e]));
+                }
+                tc_fence_before();
+                __threadfence();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive_cluster(cluster_addr(acc_empty_bar, 0));
+                    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(split.flags + pair * 16 + flag_idx), "r"(split.epoch)
+                                 : "memory");
+                }
+                tile_phase ^= 1u;
+                continue;
+            }
+            // Pairs whose slots complete this tile (none unless this pair holds only the head of the tile).
+            int q_end = pair + 1;
+            if (SPLIT && kb1 < k_blocks) {
+                const long long tile_end = (static_cast<long long>(t) - plan.rem_first_tile + 1) * k_blocks;
+                while (q_end < pairs && plan.rem_units * q_end / pairs < tile_end) ++q_end;
+                // This warp's rows of every contributing slot must have landed.
+                bool landed = true;
+                if (lane == 0) {
+                    for (int q = pair + 1; q < q_end && landed; ++q) {
+                        if (plan.rem_units * (q + 1) / pairs == plan.rem_units * q / pairs) continue;   // a pair without work
+                        const uint32_t* f = split.flags + q * 16 + flag_idx;
+                        const unsigned long long t0 = global_timer_ns();
+                        uint32_t v;
+                        for (uint32_t spin = 0;; ++spin) {
+                            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+                            if (v == split.epoch) break;
+                            if ((spin & 63u) == 63u && (*abort_flag || global_timer_ns() - t0 > kWaitLimitNs)) {
+                                landed = false;
+                                break;
+                            }
+                            __nanosleep(100);
+                        }
+                    }
+                }
+                if (!__all_sync(0xffffffffu, landed)) {
+                    timed_out = true;
+                    break;
+                }
+            }
             // A lane reads one accumulator row (one n, consecutive m).  Writing that row straight to
             // global memory would make every store instruction touch 32 different lines, 16 bytes
             // each; instead the warp passes 32 rows x 64 columns at a time through shared memory
@@ -801,7 +967,6 @@ cutlass_my_h100_match_no_tail_pair_wide(int M, int N, int K, __nv_bfloat16* C,
             // 128-byte lines: 4 rows per instruction.
             const size_t n_warp = static_cast<size_t>(tn) * W_::TILE_N + rank * 256 + block * W_::HALF + quarter * 32;
             __nv_bfloat16* c_warp = C + n_warp * static_cast<size_t>(M) + static_cast<size_t>(tm) * W_::TILE_M;
-            const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(block * 256);
             unsigned char* stage_buf = epi_smem + (warp - 2) * W_::EPI_WARP_BYTES;
             // The whole accumulator row first goes into registers as packed bf16 (256 columns = 128
             // registers), so that tensor memory can be handed back and the next tile's MMAs start
@@ -812,6 +977,15 @@ cutlass_my_h100_match_no_tail_pair_wide(int M, int N, int K, __nv_bfloat16* C,
                 uint32_t r[32];
                 tmem_ld_32cols(t_row + c0, r);
                 tmem_ld_wait();
+                if (SPLIT && q_end > pair + 1) {
+                    for (int q = pair + 1; q < q_end; ++q) {
+                        if (plan.rem_units * (q + 1) / pairs == plan.rem_units * q / pairs) continue;
+                        const float* slot = split.partials + static_cast<size_t>(q) * (W_::TILE_N * W_::TILE_M) + tile_row;
+#pragma unroll
+                        for (int e = 0; e < 32; ++e)
+                            r[e] = __float_as_uint(__uint_as_float(r[e]) + __ldcg(slot + static_cast<size_t>(c0 + e) * W_::TILE_N));
+                    }
+                }
 #pragma unroll
                 for (int e = 0; e < 16; ++e) packed[c0 / 2 + e] = pack_bf16(r[2 * e], r[2 * e + 1]);
             }
@@ -857,6 +1031,23 @@ cutlass_my_h100_match_no_tail_pair_wide(int M, int N, int K, __nv_bfloat16* C,
                      "r"(static_cast<uint32_t>(TMEM_COLS))
                      : "memory");
     }
+}
+
+template <int GROUP>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(g16::WideCfg::THREADS, 1)
+cutlass_my_h100_match_no_tail_pair_wide(int M, int N, int K, __nv_bfloat16* C,
+                                        const __grid_constant__ CUtensorMap tensorMapA,
+                                        const __grid_constant__ CUtensorMap tensorMapB) {
+    pair_wide_body<GROUP, false>(M, N, K, C, &tensorMapA, &tensorMapB, SplitArgs{nullptr, nullptr, 0u});
+}
+
+// The same kernel with the last, partly filled wave of tiles cut along K over all CTA pairs (see PairPlan).
+template <int GROUP>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(g16::WideCfg::THREADS, 1)
+cutlass_my_h100_match_no_tail_pair_wide_split(int M, int N, int K, __nv_bfloat16* C,
+                                              const __grid_constant__ CUtensorMap tensorMapA,
+                                              const __grid_constant__ CUtensorMap tensorMapB, const SplitArgs split) {
+    pair_wide_body<GROUP, true>(M, N, K, C, &tensorMapA, &tensorMapB, split);
 }
 
 namespace {
@@ -925,11 +1116,15 @@ int launch_gemm(int dev, int sms, int M, int N, int K, const void* A, const void
     if (int rc = get_tensor_map(dev, A, M, K, BLOCK_Q, &map_a)) return rc;
     if (int rc = get_tensor_map(dev, B, N, K, g16::BLOCK_P, &map_b)) return rc;
     auto kern = cutlass_my_h100_match_no_tail<BLOCK_Q>;
-    static bool attr_set[64] = {};
-    if (dev < 0 || dev >= 64 || !attr_set[dev]) {
-        PRISM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                            static_cast<int>(C_::SMEM_BYTES)));
-        if (dev >= 0 && dev < 64) attr_set[dev] = true;
+    {
+        static bool attr_set[64] = {};
+        static std::mutex mu;
+        std::lock_guard<std::mutex> lk(mu);
+        if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+            PRISM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                static_cast<int>(C_::SMEM_BYTES)));
+            if (dev >= 0 && dev < 64) attr_set[dev] = true;
+        }
     }
     const int tiles = (M / BLOCK_Q) * (N / g16::BLOCK_P);
     const int grid = tiles < sms ? tiles : sms;
@@ -940,33 +1135,56 @@ int launch_gemm(int dev, int sms, int M, int N, int K, const void* A, const void
 }
 
 using PairKernel = void (*)(int, int, int, __nv_bfloat16*, const CUtensorMap, const CUtensorMap);
+using PairSplitKernel = void (*)(int, int, int, __nv_bfloat16*, const CUtensorMap, const CUtensorMap, const SplitArgs);
 
-// Launches one of the two-CTA kernels: persistent, as many pairs as the device holds at once.
-int launch_pair_kernel(PairKernel kern, int* pairs_cache, int threads, size_t smem, int tiles, int dev, int M, int N,
-                       int K, const CUtensorMap& map_a, const CUtensorMap& map_b, void* C, cudaStream_t s) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.blockDim = dim3(static_cast<unsigned>(threads));
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = s;
-    cudaLaunchAttribute attr[1];
+std::mutex g_launch_mu;   // guards the per-device caches below; entry points may be called from several host threads
+
+void pair_launch_config(cudaLaunchConfig_t* cfg, cudaLaunchAttribute* attr, int threads, size_t smem, cudaStream_t s) {
+    *cfg = cudaLaunchConfig_t{};
+    cfg->blockDim = dim3(static_cast<unsigned>(threads));
+    cfg->dynamicSmemBytes = smem;
+    cfg->stream = s;
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    int pairs_cap = *pairs_cache;
-    if (pairs_cap == 0) {
-        PRISM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-        int sms = 0;
-        PRISM_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-        cfg.gridDim = dim3(static_cast<unsigned>(sms / 2 * 2));
-        int clusters = 0;
-        PRISM_CUDA_TRY(cudaOccupancyMaxActiveClusters(&clusters, kern, &cfg));
-        if (clusters < 1) return set_error(PRISM_B200_ERR_CUDA, "gemm_bf16: no 2-CTA cluster fits on this device");
-        pairs_cap = clusters;
-        *pairs_cache = clusters;
+    cfg->attrs = attr;
+    cfg->numAttrs = 1;
+}
+
+// CTA pairs of `kern` that the device holds at once, found once per device and kernel (`cache` is the
+// kernel's own table); also raises the kernel's dynamic shared-memory limit.
+template <typename Kernel>
+int pair_capacity(Kernel kern, int* cache, int threads, size_t smem, int dev, int* out) {
+    std::lock_guard<std::mutex> lk(g_launch_mu);
+    const bool cacheable = dev >= 0 && dev < 64;
+    if (cacheable && cache[dev]) {
+        *out = cache[dev];
+        return PRISM_B200_OK;
     }
+    cudaLaunchConfig_t cfg;
+    cudaLaunchAttribute attr[1];
+    pair_launch_config(&cfg, attr, threads, smem, nullptr);
+    PRISM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    int sms = 0;
+    PRISM_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    cfg.gridDim = dim3(static_cast<unsigned>(sms / 2 * 2));
+    int clusters = 0;
+    PRISM_CUDA_TRY(cudaOccupancyMaxActiveClusters(&clusters, kern, &cfg));
+    if (clusters < 1) return set_error(PRISM_B200_ERR_CUDA, "gemm_bf16: no 2-CTA cluster fits on this device");
+    if (cacheable) cache[dev] = clusters;
+    *out = clusters;
+    return PRISM_B200_OK;
+}
+
+// Launches one of the two-CTA kernels: persistent, as many pairs as the device holds at once.
+int launch_pair_kernel(PairKernel kern, int* cache, int threads, size_t smem, int tiles, int dev, int M, int N,
+                       int K, const CUtensorMap& map_a, const CUtensorMap& map_b, void* C, cudaStream_t s) {
+    int pairs_cap = 0;
+    if (int rc = pair_capacity(kern, cache, threads, smem, dev, &pairs_cap)) return rc;
+    cudaLaunchConfig_t cfg;
+    cudaLaunchAttribute attr[1];
+    pair_launch_config(&cfg, attr, threads, smem, s);
     const int pairs = tiles < pairs_cap ? tiles : pairs_cap;
     cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs));
     PRISM_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, M, N, K, static_cast<__nv_bfloat16*>(C), map_a, map_b));
@@ -982,28 +1200,148 @@ int launch_gemm_pair(int dev, int M, int N, int K, const void* A, const void* B,
     if (int rc = get_tensor_map(dev, A, M, K, P_::HALF, &map_a)) return rc;
     if (int rc = get_tensor_map(dev, B, N, K, P_::HALF, &map_b)) return rc;
     static int max_pairs[64] = {};
-    int uncached = 0;
-    int* cache = (dev >= 0 && dev < 64) ? &max_pairs[dev] : &uncached;
-    return launch_pair_kernel(cutlass_my_h100_match_no_tail_pair<8>, cache, g16::THREADS, P_::SMEM_BYTES,
+    return launch_pair_kernel(cutlass_my_h100_match_no_tail_pair<8>, max_pairs, g16::THREADS, P_::SMEM_BYTES,
                               (M / P_::BLOCK) * (N / P_::BLOCK), dev, M, N, K, map_a, map_b, C, s);
 }
+
+// ---- workspace of the split form -------------------------------------------------------------
+// One 512 x 256 fp32 slot per CTA pair plus 16 flag words per pair.  Launches on one stream run one
+// after the other and can share a workspace; launches on different streams may overlap and must not,
+// so there is one workspace per (device, stream), created at the first split launch on that stream
+// (a cudaMalloc, i.e. not during a stream capture) and kept until the process ends.  At most
+// kMaxSplitWorkspaces exist; a stream beyond that gets the unsplit kernel.
+struct SplitWorkspace {
+    int dev;
+    cudaStream_t stream;
+    float* partials;
+    uint32_t* flags;
+    uint32_t epoch;
+};
+constexpr int kMaxSplitWorkspaces = 16;
+constexpr size_t kSlotFloats = static_cast<size_t>(g16::WideCfg::TILE_N) * g16::WideCfg::TILE_M;
+SplitWorkspace g_split_ws[kMaxSplitWorkspaces];
+int g_split_ws_count = 0;
+
+// Fills `out` with the workspace of (dev, s) and a fresh epoch; *have = false if none can be had.
+int split_workspace(int dev, cudaStream_t s, int pairs, SplitArgs* out, bool* have) {
+    std::lock_guard<std::mutex> lk(g_launch_mu);
+    *have = false;
+    SplitWorkspace* w = nullptr;
+    for (int i = 0; i < g_split_ws_count; ++i)
+        if (g_split_ws[i].dev == dev && g_split_ws[i].stream == s) w = &g_split_ws[i];
+    if (!w) {
+        if (g_split_ws_count == kMaxSplitWorkspaces) return PRISM_B200_OK;
+        void* mem = nullptr;
+        const size_t flag_bytes = static_cast<size_t>(pairs) * 16 * sizeof(uint32_t);
+        const size_t bytes = static_cast<size_t>(pairs) * kSlotFloats * sizeof(float) + flag_bytes;
+        if (cudaMalloc(&mem, bytes) != cudaSuccess) {
+            (void)cudaGetLastError();   // out of memory is not an error of the call: the unsplit kernel runs instead
+            return PRISM_B200_OK;
+        }
+        w = &g_split_ws[g_split_ws_count];
+        w->dev = dev;
+        w->stream = s;
+        w->partials = static_cast<float*>(mem);
+        w->flags = reinterpret_cast<uint32_t*>(w->partials + static_cast<size_t>(pairs) * kSlotFloats);
+        w->epoch = 0;
+        cudaError_t e = cudaMemsetAsync(w->flags, 0, flag_bytes, s);   // epoch 0 is never used by a launch
+        if (e != cudaSuccess) {
+            cudaFree(mem);
+            return cuda_failed(e, "cudaMemsetAsync(split flags)");
+        }
+        ++g_split_ws_count;
+    }
+    if (++w->epoch == 0) w->epoch = 1;
+    out->partials = w->partials;
+    out->flags = w->flags;
+    out->epoch = w->epoch;
+    *have = true;
+    return PRISM_B200_OK;
+}
+
+}  // namespace
+
+void release_gemm_split_workspace(cudaStream_t stream) {
+    std::lock_guard<std::mutex> lk(g_launch_mu);
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return;
+    for (int i = 0; i < g_split_ws_count; ++i) {
+        if (g_split_ws[i].dev == dev && g_split_ws[i].stream == stream) {
+            cudaFree(g_split_ws[i].partials);   // flags live in the same allocation
+            g_split_ws[i] = g_split_ws[--g_split_ws_count];
+            return;
+        }
+    }
+}
+
+namespace {
+
+// k-blocks that the dump of a contribution and its addition cost, in units of main-loop k-blocks
+// (an estimate for the decision below, not a measured constant of the kernel).
+constexpr int kSplitOverheadKb = 8;
+
+// Time of the 512 x 256 form in k-blocks per pair, with and without the split of the last wave.
+void wide_estimate(long long tiles, int pairs, int k_blocks, double* unsplit, double* split) {
+    const long long full = tiles / pairs, rem = tiles % pairs;
+    *unsplit = static_cast<double>((full + (rem ? 1 : 0)) * k_blocks);
+    const double share = static_cast<double>(rem) * k_blocks / pairs;
+    *split = (rem && share >= 8.0 && share + kSplitOverheadKb < k_blocks)
+                 ? static_cast<double>(full * k_blocks) + share + kSplitOverheadKb
+                 : *unsplit;
+}
+
+int g_forced_split = -2;   // PRISM_B200_GEMM_SPLIT = 0 / 1 forces the unsplit / split kernel (tests)
 
 int launch_gemm_pair_wide(int dev, int M, int N, int K, const void* A, const void* B, void* C, cudaStream_t s) {
     using W_ = g16::WideCfg;
     CUtensorMap map_a, map_b;
     if (int rc = get_tensor_map(dev, A, M, K, W_::HALF, &map_a)) return rc;
     if (int rc = get_tensor_map(dev, B, N, K, W_::HALF, &map_b)) return rc;
-    static int max_pairs[64] = {};
-    int uncached = 0;
-    int* cache = (dev >= 0 && dev < 64) ? &max_pairs[dev] : &uncached;
-    return launch_pair_kernel(cutlass_my_h100_match_no_tail_pair_wide<16>, cache, W_::THREADS, W_::SMEM_BYTES,
-                              (M / W_::TILE_M) * (N / W_::TILE_N), dev, M, N, K, map_a, map_b, C, s);
+    static int max_pairs[64] = {}, max_pairs_split[64] = {};
+    const int tiles = (M / W_::TILE_M) * (N / W_::TILE_N);
+    const int k_blocks = K / g16::BLOCK_K;
+    int pairs_cap = 0;
+    if (int rc = pair_capacity(cutlass_my_h100_match_no_tail_pair_wide_split<16>, max_pairs_split, W_::THREADS,
+                               W_::SMEM_BYTES, dev, &pairs_cap))
+        return rc;
+    double t_unsplit, t_split;
+    wide_estimate(tiles, pairs_cap, k_blocks, &t_unsplit, &t_split);
+    bool want_split = t_split < t_unsplit;
+    if (g_forced_split == 0) want_split = false;
+    // Forced: any shape with a partly filled last wave whose pairs all get at least one k-block.
+    if (g_forced_split == 1) want_split = tiles % pairs_cap != 0 && static_cast<long long>(tiles % pairs_cap) * k_blocks >= pairs_cap;
+    if (want_split) {
+        SplitArgs split{};
+        bool have = false;
+        if (int rc = split_workspace(dev, s, pairs_cap, &split, &have)) return rc;
+        if (have) {
+            cudaLaunchConfig_t cfg;
+            cudaLaunchAttribute attr[1];
+            pair_launch_config(&cfg, attr, W_::THREADS, W_::SMEM_BYTES, s);
+            cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs_cap));   // every pair takes part in the split wave
+            PRISM_CUDA_TRY(cudaLaunchKernelEx(&cfg, cutlass_my_h100_match_no_tail_pair_wide_split<16>, M, N, K,
+                                              static_cast<__nv_bfloat16*>(C), map_a, map_b, split));
+            count_launch();
+            return PRISM_B200_OK;
+        }
+    }
+    return launch_pair_kernel(cutlass_my_h100_match_no_tail_pair_wide<16>, max_pairs, W_::THREADS, W_::SMEM_BYTES, tiles, dev,
+                              M, N, K, map_a, map_b, C, s);
 }
 
 }  // namespace
 }  // namespace prism_b200
 
 using namespace prism_b200;
+
+extern "C" int prism_b200_gemm_bf16_split_plan(int tiles, int pairs, int k_blocks, int pair, int* out7) {
+    if (!out7 || tiles < 0 || pairs < 1 || k_blocks < 1 || pair < 0 || pair >= pairs)
+        return set_error(PRISM_B200_ERR_INVALID_ARGUMENT, "gemm_bf16_split_plan: bad argument");
+    const PairPlan p = make_pair_plan<true>(pair, pairs, tiles, k_blocks);
+    out7[0] = p.full; out7[1] = p.segs; out7[2] = p.tile0; out7[3] = p.kb0_0; out7[4] = p.kb1_0; out7[5] = p.tile1;
+    out7[6] = p.kb1_1;
+    return PRISM_B200_OK;
+}
 
 extern "C" int prism_b200_gemm_bf16(int M, int N, int K, const uint16_t* A, const uint16_t* B, uint16_t* C,
                                     void* stream) {
@@ -1018,23 +1356,32 @@ extern "C" int prism_b200_gemm_bf16(int M, int N, int K, const uint16_t* A, cons
     if (int rc = bind_status_word()) return rc;
     int dev = 0;
     PRISM_CUDA_TRY(cudaGetDevice(&dev));
-    static int sm_count[64] = {};
-    int sms = (dev >= 0 && dev < 64) ? sm_count[dev] : 0;
-    if (sms == 0) {
-        PRISM_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-        if (dev >= 0 && dev < 64) sm_count[dev] = sms;
+    int sms = 0;
+    static int forced = -1;
+    {
+        static int sm_count[64] = {};
+        static bool env_read = false;
+        std::lock_guard<std::mutex> lk(g_launch_mu);
+        sms = (dev >= 0 && dev < 64) ? sm_count[dev] : 0;
+        if (sms == 0) {
+            PRISM_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+            if (dev >= 0 && dev < 64) sm_count[dev] = sms;
+        }
+        if (!env_read) {
+            // PRISM_B200_GEMM_PAIR = 0 / 1 / 2 forces one-CTA / 256 x 256 pair / 512 x 256 pair,
+            // PRISM_B200_GEMM_SPLIT = 0 / 1 forces the 512 x 256 form without / with the split last wave (tests).
+            const char* e = getenv("PRISM_B200_GEMM_PAIR");
+            forced = e ? atoi(e) : -1;
+            const char* sp = getenv("PRISM_B200_GEMM_SPLIT");
+            g_forced_split = sp ? atoi(sp) : -1;
+            env_read = true;
+        }
     }
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     {
         // Which form: estimated main-loop time in units of one 128 x 256 tile on one SM, waves x
         // tile size / (measured relative efficiency of the form).  Small problems (under 2^35
         // multiply-adds) stay with the one-CTA forms, whose launch costs less.
-        // PRISM_B200_GEMM_PAIR = 0 / 1 / 2 forces one-CTA / 256 x 256 pair / 512 x 256 pair (used by the tests).
-        static int forced = -2;
-        if (forced == -2) {
-            const char* e = getenv("PRISM_B200_GEMM_PAIR");
-            forced = e ? atoi(e) : -1;
-        }
         const bool pair_ok = M % 256 == 0 && N % 256 == 0;
         const bool wide_ok = M % 256 == 0 && N % 512 == 0;
         int form = 0;  // 0 one CTA, 1 pair, 2 wide pair
@@ -1054,7 +1401,10 @@ extern "C" int prism_b200_gemm_bf16(int M, int N, int K, const uint16_t* A, cons
                 if (t < best) { best = t; form = 1; }
             }
             if (wide_ok) {
-                const double t = waves(static_cast<long long>(M / 256) * (N / 512), pairs) * 2.0;
+                // with its last wave cut along K the 512 x 256 form has no partly filled wave to pay for
+                double t_unsplit, t_split;
+                wide_estimate(static_cast<long long>(M / 256) * (N / 512), pairs, K / g16::BLOCK_K, &t_unsplit, &t_split);
+                const double t = (g_forced_split == 0 ? t_unsplit : t_split) / (K / g16::BLOCK_K) * 2.0;
                 if (t <= best) { best = t; form = 2; }
             }
         }

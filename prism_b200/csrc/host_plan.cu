@@ -59,6 +59,13 @@ void destroy(prism_b200_host_plan* p) {
     cudaFree(p->a);
     cudaFree(p->b);
     cudaFree(p->c);
+    if (p->lane[1]) {   // the kernel lane may own a split-K workspace, on the plan's device
+        int cur = -1;
+        if (cudaGetDevice(&cur) == cudaSuccess && cudaSetDevice(p->device) == cudaSuccess) {
+            release_gemm_split_workspace(p->lane[1]);
+            cudaSetDevice(cur);
+        }
+    }
     for (auto& s : p->lane)
         if (s) cudaStreamDestroy(s);
     if (p->begin) cudaEventDestroy(p->begin);
@@ -129,6 +136,14 @@ int abandon_run(prism_b200_host_plan* p, cudaStream_t caller, int rc) {
     return rc;
 }
 
+// Inside a run: a CUDA call that fails after copies have been queued goes through abandon_run, so that the
+// caller's stream still waits for what is already in flight on the plan's lanes.
+#define PRISM_RUN_TRY(expr)                                                              \
+    do {                                                                                 \
+        cudaError_t _e = (expr);                                                         \
+        if (_e != cudaSuccess) return abandon_run(p, caller, ::prism_b200::cuda_failed(_e, #expr)); \
+    } while (0)
+
 }  // namespace
 
 extern "C" int prism_b200_host_gemm_bf16_create(int M, int N, int K, int block_rows, prism_b200_host_plan** plan) {
@@ -150,22 +165,22 @@ extern "C" int prism_b200_host_gemm_bf16_run(prism_b200_host_plan* p, const uint
     cudaStream_t caller = static_cast<cudaStream_t>(stream);
     if (int rc = begin_run(p, caller)) return rc;
     const size_t row_b = static_cast<size_t>(p->K) * 2, row_c = static_cast<size_t>(p->M) * 2;
-    PRISM_CUDA_TRY(cudaMemcpyAsync(p->a, A_host, static_cast<size_t>(p->M) * row_b, cudaMemcpyHostToDevice, p->lane[0]));
+    PRISM_RUN_TRY(cudaMemcpyAsync(p->a, A_host, static_cast<size_t>(p->M) * row_b, cudaMemcpyHostToDevice, p->lane[0]));
     for (size_t j = 0; j < p->blocks.size(); ++j) {
         const size_t lo = p->blocks[j].first, rows = p->blocks[j].second - lo;
         char* b_dev = static_cast<char*>(p->b) + lo * row_b;
         char* c_dev = static_cast<char*>(p->c) + lo * row_c;
-        PRISM_CUDA_TRY(cudaMemcpyAsync(b_dev, reinterpret_cast<const char*>(B_host) + lo * row_b, rows * row_b,
+        PRISM_RUN_TRY(cudaMemcpyAsync(b_dev, reinterpret_cast<const char*>(B_host) + lo * row_b, rows * row_b,
                                        cudaMemcpyHostToDevice, p->lane[0]));
-        PRISM_CUDA_TRY(cudaEventRecord(p->uploaded[j], p->lane[0]));
-        PRISM_CUDA_TRY(cudaStreamWaitEvent(p->lane[1], p->uploaded[j], 0));
+        PRISM_RUN_TRY(cudaEventRecord(p->uploaded[j], p->lane[0]));
+        PRISM_RUN_TRY(cudaStreamWaitEvent(p->lane[1], p->uploaded[j], 0));
         if (int rc = prism_b200_gemm_bf16(p->M, static_cast<int>(rows), p->K, static_cast<const uint16_t*>(p->a),
                                           reinterpret_cast<const uint16_t*>(b_dev), reinterpret_cast<uint16_t*>(c_dev),
                                           p->lane[1]))
             return abandon_run(p, caller, rc);
-        PRISM_CUDA_TRY(cudaEventRecord(p->computed[j], p->lane[1]));
-        PRISM_CUDA_TRY(cudaStreamWaitEvent(p->lane[2], p->computed[j], 0));
-        PRISM_CUDA_TRY(cudaMemcpyAsync(reinterpret_cast<char*>(C_host) + lo * row_c, c_dev, rows * row_c, cudaMemcpyDeviceToHost,
+        PRISM_RUN_TRY(cudaEventRecord(p->computed[j], p->lane[1]));
+        PRISM_RUN_TRY(cudaStreamWaitEvent(p->lane[2], p->computed[j], 0));
+        PRISM_RUN_TRY(cudaMemcpyAsync(reinterpret_cast<char*>(C_host) + lo * row_c, c_dev, rows * row_c, cudaMemcpyDeviceToHost,
                                        p->lane[2]));
     }
     return end_run(p, caller);
@@ -191,21 +206,21 @@ extern "C" int prism_b200_host_sgemm_run(prism_b200_host_plan* p, float alpha, c
     cudaStream_t caller = static_cast<cudaStream_t>(stream);
     if (int rc = begin_run(p, caller)) return rc;
     const size_t K = p->K, N = p->N;
-    PRISM_CUDA_TRY(cudaMemcpyAsync(p->b, B_host, K * N * 4, cudaMemcpyHostToDevice, p->lane[0]));
+    PRISM_RUN_TRY(cudaMemcpyAsync(p->b, B_host, K * N * 4, cudaMemcpyHostToDevice, p->lane[0]));
     for (size_t j = 0; j < p->blocks.size(); ++j) {
         const size_t lo = p->blocks[j].first, rows = p->blocks[j].second - lo;
         float* a_dev = static_cast<float*>(p->a) + lo * K;
         float* c_dev = static_cast<float*>(p->c) + lo * N;
-        PRISM_CUDA_TRY(cudaMemcpyAsync(a_dev, A_host + lo * K, rows * K * 4, cudaMemcpyHostToDevice, p->lane[0]));
-        PRISM_CUDA_TRY(cudaMemcpyAsync(c_dev, C_host + lo * N, rows * N * 4, cudaMemcpyHostToDevice, p->lane[0]));
-        PRISM_CUDA_TRY(cudaEventRecord(p->uploaded[j], p->lane[0]));
-        PRISM_CUDA_TRY(cudaStreamWaitEvent(p->lane[1], p->uploaded[j], 0));
+        PRISM_RUN_TRY(cudaMemcpyAsync(a_dev, A_host + lo * K, rows * K * 4, cudaMemcpyHostToDevice, p->lane[0]));
+        PRISM_RUN_TRY(cudaMemcpyAsync(c_dev, C_host + lo * N, rows * N * 4, cudaMemcpyHostToDevice, p->lane[0]));
+        PRISM_RUN_TRY(cudaEventRecord(p->uploaded[j], p->lane[0]));
+        PRISM_RUN_TRY(cudaStreamWaitEvent(p->lane[1], p->uploaded[j], 0));
         if (int rc = prism_b200_sgemm(p->kernel_id, static_cast<int>(rows), p->N, p->K, alpha, a_dev,
                                       static_cast<const float*>(p->b), beta, c_dev, p->lane[1]))
             return abandon_run(p, caller, rc);
-        PRISM_CUDA_TRY(cudaEventRecord(p->computed[j], p->lane[1]));
-        PRISM_CUDA_TRY(cudaStreamWaitEvent(p->lane[2], p->computed[j], 0));
-        PRISM_CUDA_TRY(cudaMemcpyAsync(C_host + lo * N, c_dev, rows * N * 4, cudaMemcpyDeviceToHost, p->lane[2]));
+        PRISM_RUN_TRY(cudaEventRecord(p->computed[j], p->lane[1]));
+        PRISM_RUN_TRY(cudaStreamWaitEvent(p->lane[2], p->computed[j], 0));
+        PRISM_RUN_TRY(cudaMemcpyAsync(C_host + lo * N, c_dev, rows * N * 4, cudaMemcpyDeviceToHost, p->lane[2]));
     }
     return end_run(p, caller);
 }
@@ -236,18 +251,18 @@ extern "C" int prism_b200_host_scan_run(prism_b200_host_plan* p, uint32_t* x_hos
     if (int rc = begin_run(p, caller)) return rc;
     uint32_t* x = static_cast<uint32_t*>(p->a);
     uint32_t* carry = static_cast<uint32_t*>(p->c);
-    PRISM_CUDA_TRY(cudaMemsetAsync(carry, 0, 4, p->lane[1]));
+    PRISM_RUN_TRY(cudaMemsetAsync(carry, 0, 4, p->lane[1]));
     for (size_t j = 0; j < p->blocks.size(); ++j) {
         const size_t lo = p->blocks[j].first, hi = p->blocks[j].second;
-        PRISM_CUDA_TRY(cudaMemcpyAsync(x + lo, x_host + lo, (hi - lo) * 4, cudaMemcpyHostToDevice, p->lane[0]));
-        PRISM_CUDA_TRY(cudaEventRecord(p->uploaded[j], p->lane[0]));
-        PRISM_CUDA_TRY(cudaStreamWaitEvent(p->lane[1], p->uploaded[j], 0));
+        PRISM_RUN_TRY(cudaMemcpyAsync(x + lo, x_host + lo, (hi - lo) * 4, cudaMemcpyHostToDevice, p->lane[0]));
+        PRISM_RUN_TRY(cudaEventRecord(p->uploaded[j], p->lane[0]));
+        PRISM_RUN_TRY(cudaStreamWaitEvent(p->lane[1], p->uploaded[j], 0));
         // seed = totals[0] with rank 1: the carry word, i.e. the scanned last element of the block before
         if (int rc = prism_b200_scan_seeded(hi - lo, x + lo, p->b, carry, 1, p->lane[1])) return abandon_run(p, caller, rc);
-        PRISM_CUDA_TRY(cudaMemcpyAsync(carry, x + hi - 1, 4, cudaMemcpyDeviceToDevice, p->lane[1]));
-        PRISM_CUDA_TRY(cudaEventRecord(p->computed[j], p->lane[1]));
-        PRISM_CUDA_TRY(cudaStreamWaitEvent(p->lane[2], p->computed[j], 0));
-        PRISM_CUDA_TRY(cudaMemcpyAsync(x_host + lo, x + lo, (hi - lo) * 4, cudaMemcpyDeviceToHost, p->lane[2]));
+        PRISM_RUN_TRY(cudaMemcpyAsync(carry, x + hi - 1, 4, cudaMemcpyDeviceToDevice, p->lane[1]));
+        PRISM_RUN_TRY(cudaEventRecord(p->computed[j], p->lane[1]));
+        PRISM_RUN_TRY(cudaStreamWaitEvent(p->lane[2], p->computed[j], 0));
+        PRISM_RUN_TRY(cudaMemcpyAsync(x_host + lo, x + lo, (hi - lo) * 4, cudaMemcpyDeviceToHost, p->lane[2]));
     }
     return end_run(p, caller);
 }

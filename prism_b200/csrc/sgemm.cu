@@ -14,6 +14,8 @@
 // four warps run an 8x16 register tile per lane on packed fma.rn.f32x2.
 #include "common.cuh"
 
+#include <mutex>
+
 namespace prism_b200 {
 
 // ============================================================================
@@ -424,8 +426,11 @@ namespace {
 
 inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
+std::mutex g_sgemm_mu;   // guards the caches below; entry points may be called from several host threads
+
 int sm_count() {
     static int n[64] = {};
+    std::lock_guard<std::mutex> lk(g_sgemm_mu);
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
     if (n[dev] == 0) {
@@ -507,10 +512,13 @@ extern "C" int prism_b200_sgemm(int kernel_id, int M, int N, int K, float alpha,
     }
     case 5: {
         if (M % k5::BM == 0 && N % k5::BN == 0 && K % k5::BK == 0 && K > 0 && vec_ok) {
-            if (!g_k5_env_read) {
-                const char* e = getenv("PRISM_B200_SGEMM_SCALAR");
-                g_k5_scalar = e && e[0] == '1';
-                g_k5_env_read = true;
+            {
+                std::lock_guard<std::mutex> lk(g_sgemm_mu);
+                if (!g_k5_env_read) {
+                    const char* e = getenv("PRISM_B200_SGEMM_SCALAR");
+                    g_k5_scalar = e && e[0] == '1';
+                    g_k5_env_read = true;
+                }
             }
             // Fewer 128 x 128 tiles than half the SMs: halve the tile's height so twice as many SMs work
             // (same k order per output element, so the same bits; 1024^3: 29 -> 37 TFLOP/s).

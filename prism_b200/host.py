@@ -114,3 +114,56 @@ class HostScan(_Plan):
         with torch.cuda.device(self.device):
             _lib.check(load().prism_b200_host_scan_run(self._plan, x_host.data_ptr(), self._stream()))
         return x_host
+
+
+# ---------------------------------------------------------------------------
+# Pinned host memory on the GPU's own NUMA node
+# ---------------------------------------------------------------------------
+def _gpu_numa_cpus(device) -> set[int] | None:
+    """CPUs of the NUMA node the GPU's PCIe link hangs off, from sysfs; None if the machine does not say."""
+    try:
+        p = torch.cuda.get_device_properties(device)
+        bdf = "%04x:%02x:%02x.0" % (p.pci_domain_id, p.pci_bus_id, p.pci_device_id)
+        with open(f"/sys/bus/pci/devices/{bdf}/numa_node") as f:
+            node = int(f.read().strip())
+        if node < 0:
+            return None
+        with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
+            text = f.read().strip()
+        cpus: set[int] = set()
+        for part in text.split(","):
+            if "-" in part:
+                lo, hi = part.split("-")
+                cpus.update(range(int(lo), int(hi) + 1))
+            elif part:
+                cpus.add(int(part))
+        return cpus or None
+    except (OSError, ValueError, AttributeError, RuntimeError):
+        return None
+
+
+def pinned_near(device, shape, dtype) -> torch.Tensor:
+    """A pinned host tensor whose pages lie on the NUMA node of `device`'s PCIe link (where the machine exposes
+    that): the allocating thread is confined to that node's CPUs while the pages are allocated and touched, then
+    gets its CPU set back.  Several GPUs uploading at once then read from their own memory controllers instead of
+    all from the node the process happened to start on.  Falls back to an ordinary pinned tensor."""
+    import os
+    cpus = _gpu_numa_cpus(device)
+    old = None
+    if cpus and hasattr(os, "sched_setaffinity"):
+        try:
+            old = os.sched_getaffinity(0)
+            allowed = cpus & old
+            if allowed:
+                os.sched_setaffinity(0, allowed)
+            else:
+                old = None
+        except OSError:
+            old = None
+    try:
+        t = torch.empty(shape, dtype=dtype, pin_memory=True)
+        t.view(torch.uint8).reshape(-1)[:: 4096].fill_(0)   # touch every page from this node
+    finally:
+        if old is not None:
+            os.sched_setaffinity(0, old)
+    return t

@@ -230,3 +230,114 @@ class RowShardedSgemm:
         import prism_b200 as pb
         pb.run_my_kernel(self.kernel, self.rows, self.N, self.K, alpha, A_local, B, beta, C_local)
         return C_local
+
+
+class ShardedHostGemmBF16:
+    """C = A @ B.T for operands in HOST memory on g GPUs (one process each), rows of M sharded.
+
+    Every rank holds its rows of A, all of B and its (N, M / g) block of the column-major C in pinned host
+    memory.  B is the same on every rank, so no rank uploads all of it: per step each rank sends 1/g of a
+    block of B's rows over its own PCIe link, the ranks all-gather the block over NVLink into their OWN memory
+    (an NCCL all-gather in place; the kernel only ever reads local HBM), and the GEMM on that block of columns
+    of C runs while the next block is uploaded and gathered and the previous block of C goes back to the host:
+
+        upload stream    piece 0 | A rows | piece 1 | piece 2 | ...
+        gather stream             gather 0          | gather 1 | ...
+        kernel stream                      GEMM 0            | GEMM 1 | ...
+        download stream                               C block 0      | C block 1 | ...
+
+    Per rank and call the host link carries (M / g + N / g) * K * 2 bytes up and N * M / g * 2 bytes down,
+    against (M / g + N) * K * 2 up when every rank uploads all of B.  With one rank this is
+    prism_b200.host.HostGemmBF16 (the library's host plan).  The reference's harness copies everything in,
+    launches and copies everything out on one GPU (evals/h100_bench/main.cu:105-130).
+    """
+
+    def __init__(self, M: int, N: int, K: int, device, group: Any = None, steps: int = 0, gemm: Any = None):
+        """`gemm(rows, n, K, A, B_block, C_block)` replaces the kernel call; the tests of the host-side
+        logic pass a CPU stand-in together with device="cpu" (then there are no streams either)."""
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.device = torch.device(device)
+        self.on_cuda = self.device.type == "cuda"
+        self.lo, self.hi = row_shard(M, self.world, self.rank)
+        self.M, self.N, self.K = M, N, K
+        self.rows = self.hi - self.lo
+        self.single = None
+        self._gemm = gemm
+        if self.world == 1 and gemm is None:
+            from . import host
+            self.single = host.HostGemmBF16(M, N, K, self.device)
+            self.steps = self.single.blocks
+            self.h2d_bytes, self.d2h_bytes = self.single.h2d_bytes, self.single.d2h_bytes
+            return
+        if steps == 0:
+            steps = next((s for s in (4, 2, 1) if N % (s * 512) == 0 and (N // s) % (self.world * 8) == 0), 0)
+        if steps < 1 or N % steps or (N // steps) % 128 or (N // steps) % self.world:
+            raise ValueError(f"N={N} does not cut into {steps} blocks of a multiple of 128 rows that {self.world} ranks share")
+        self.steps = steps
+        self.block = N // steps                  # rows of B (columns of C) per step
+        self.piece = self.block // self.world    # rows of B this rank uploads per step
+        self.h2d_bytes = (self.rows + N // self.world) * K * 2
+        self.d2h_bytes = N * self.rows * 2
+        self.a = torch.empty((self.rows, K), dtype=torch.bfloat16, device=self.device)
+        self.b = torch.empty((N, K), dtype=torch.bfloat16, device=self.device)
+        self.c = torch.empty((N, self.rows), dtype=torch.bfloat16, device=self.device)
+        # upload, gather, kernel, download
+        self.lanes = [torch.cuda.Stream(self.device) for _ in range(4)] if self.on_cuda else [None] * 4
+
+    def __call__(self, A_host_local: torch.Tensor, B_host: torch.Tensor, C_host_local: torch.Tensor) -> torch.Tensor:
+        if self.single is not None:
+            return self.single(A_host_local, B_host, C_host_local)
+        import contextlib
+        for name, t, shape in (("A", A_host_local, (self.rows, self.K)), ("B", B_host, (self.N, self.K)),
+                               ("C", C_host_local, (self.N, self.rows))):
+            if t.device.type != "cpu" or t.dtype != torch.bfloat16 or tuple(t.shape) != shape or not t.is_contiguous():
+                raise ValueError(f"{name} must be a contiguous host bf16 tensor of shape {shape}")
+        gemm = self._gemm
+        if gemm is None:
+            import prism_b200 as pb
+            gemm = pb.runmyh100
+        up, gather, kernel, down = self.lanes
+        cuda = self.on_cuda
+        on = (lambda s: torch.cuda.stream(s)) if cuda else (lambda s: contextlib.nullcontext())
+        event = (lambda: torch.cuda.Event()) if cuda else (lambda: None)
+        record = (lambda e, s: e.record(s)) if cuda else (lambda e, s: None)
+        wait = (lambda s, e: s.wait_event(e)) if cuda else (lambda s, e: None)
+        caller = torch.cuda.current_stream(self.device) if cuda else None
+        begin = event()
+        record(begin, caller)
+        for s in self.lanes:
+            wait(s, begin)
+        a_done = event()
+        for i in range(self.steps):
+            lo = i * self.block
+            mine = slice(lo + self.rank * self.piece, lo + (self.rank + 1) * self.piece)
+            uploaded, gathered, computed = event(), event(), event()
+            with on(up):
+                self.b[mine].copy_(B_host[mine], non_blocking=True)
+                record(uploaded, up)
+                if i == 0:          # A goes up while the first block is being gathered
+                    self.a.copy_(A_host_local, non_blocking=True)
+                    record(a_done, up)
+            with on(gather):
+                wait(gather, uploaded)
+                # On the GPU in place: this rank's piece already sits at its position in the block.
+                piece = self.b[mine] if cuda else self.b[mine].clone()
+                if self.world > 1:
+                    dist.all_gather_into_tensor(self.b[lo:lo + self.block], piece, group=self.group)
+                record(gathered, gather)
+            with on(kernel):
+                wait(kernel, gathered)
+                if i == 0:
+                    wait(kernel, a_done)
+                gemm(self.rows, self.block, self.K, self.a, self.b[lo:lo + self.block], self.c[lo:lo + self.block])
+                record(computed, kernel)
+            with on(down):
+                wait(down, computed)
+                C_host_local[lo:lo + self.block].copy_(self.c[lo:lo + self.block], non_blocking=True)
+        for s in self.lanes:
+            done = event()
+            record(done, s)
+            wait(caller, done)
+        return C_host_local

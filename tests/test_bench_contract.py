@@ -35,3 +35,22 @@ def test_own_arm_fails_loudly_without_a_gpu():
                        text=True, timeout=300)
     assert r.returncode != 0
     assert "no CPU path" in r.stdout
+
+
+def test_reference_arm_uses_every_core_under_a_launcher_that_exports_one_thread():
+    """torch.distributed.run exports OMP_NUM_THREADS=1 to its workers; the CPU arm must undo that before BLAS loads,
+    and must carry the same `config` as the GPU arm (M, N, K, sharding for the number of GPUs)."""
+    import os
+    env = dict(os.environ, OMP_NUM_THREADS="1", RANK="0", WORLD_SIZE="2")
+    r = subprocess.run([sys.executable, str(ROOT / "bench.py"), "--impl", "reference", "--gpus", "2", "--steps", "1",
+                        "--warmup", "0"], capture_output=True, text=True, timeout=600, env=env)
+    assert r.returncode == 0, r.stderr[-2000:]
+    d = json.loads(r.stdout.strip().splitlines()[-1])
+    want = len(os.sched_getaffinity(0))
+    assert d["cpu_baseline"]["cores"] == want, d["cpu_baseline"]
+    assert d["config"]["M"] == d["config"]["N"] == d["config"]["K"] == 8192 and d["config"]["rows_per_gpu"] == 4096
+    # a rank other than 0 prints nothing and exits 0
+    env["RANK"] = "1"
+    r = subprocess.run([sys.executable, str(ROOT / "bench.py"), "--impl", "reference", "--gpus", "2", "--steps", "1",
+                        "--warmup", "0"], capture_output=True, text=True, timeout=600, env=env)
+    assert r.returncode == 0 and r.stdout.strip() == ""

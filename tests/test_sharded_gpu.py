@@ -40,6 +40,32 @@ for schedule in (sharded.ShardedScan.PEER_SCHEDULE,) + sharded.ShardedScan.SCHED
         assert sum(scan.totals_int64()) & 0xFFFFFFFF == int(expect[-1]), (schedule, rank, rep)
 assert sharded.ShardedScan(hi - lo, dev).schedule == "peer_words"
 
+# the fused launch with a longer limit and the checked mode; an array so short that the last rank's chunk is empty
+for n_small in (3 * world + 1, 4 * (world - 1)):
+    full_s = O.scan_inputs(n_small, seed=6, high=9)
+    lo_s, hi_s = sharded.chunk_bounds(n_small, world, rank)
+    scan = sharded.ShardedScan(hi_s - lo_s, dev, schedule="peer_words", wait_limit_s=5.0, checked=True)
+    for rep in range(3):
+        x = torch.from_numpy(full_s[lo_s:hi_s].view(np.int32).copy()).to(dev)
+        scan(x)
+        assert np.array_equal(x.cpu().numpy().view(np.uint32), O.scan_cpu(full_s)[lo_s:hi_s]), (n_small, rank, rep)
+
+# bf16 GEMM from host arrays: every rank uploads its rows of A and 1/world of B, B is completed over NVLink
+Mh, Nh, Kh = 256 * world, 2048, 512
+A, B = O.gemm_bf16_inputs(Mh, Nh, Kh, seed=19)
+op = sharded.ShardedHostGemmBF16(Mh, Nh, Kh, dev)
+from prism_b200 import host
+ah = host.pinned_near(dev, (op.rows, Kh), torch.bfloat16); ah.copy_(torch.from_numpy(A[op.lo:op.hi].view(np.int16)).view(torch.bfloat16))
+bh = host.pinned_near(dev, (Nh, Kh), torch.bfloat16); bh.copy_(torch.from_numpy(B.view(np.int16)).view(torch.bfloat16))
+ch = host.pinned_near(dev, (Nh, op.rows), torch.bfloat16)
+for rep in range(2):
+    ch.fill_(float("nan"))
+    op(ah, bh, ch)
+    torch.cuda.synchronize()
+    ok, worst = O.gemm_bf16_check(ch.view(torch.int16).numpy().view(np.uint16), O.gemm_bf16_cpu(A[op.lo:op.hi], B))
+    assert ok, (rank, rep, worst)
+assert op.steps == 4 and op.h2d_bytes == (op.rows + Nh // world) * Kh * 2
+
 # bf16 GEMM: rows of M sharded, B replicated, no collective
 M, N, K = 256 * world, 512, 256
 A, B = O.gemm_bf16_inputs(M, N, K, seed=9)

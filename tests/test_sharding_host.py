@@ -156,3 +156,49 @@ def test_row_shard():
         sharded.row_shard(8192, 3, 0)
     with pytest.raises(ValueError):
         sharded.row_shard(1024, 16, 0)  # 64 rows per rank is not a multiple of the 128-row tile
+
+
+def _gemm_worker(rank, world, port, q):
+    """Host-side logic of the sharded host-buffer GEMM: which rows of B each rank uploads, the in-place
+    gather of each block and the block-wise GEMM, with the kernel replaced by a float64 product on the CPU."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        M, N, K = 256 * world, 1024, 64
+        A, B = O.gemm_bf16_inputs(M, N, K, seed=12)
+        a_all = torch.from_numpy(A.view(np.int16)).view(torch.bfloat16)
+        b_all = torch.from_numpy(B.view(np.int16)).view(torch.bfloat16)
+
+        def gemm(rows, n, k, a, b_block, c_block):
+            c_block.copy_((b_block.double() @ a.double().t()).to(torch.bfloat16))
+
+        op = sharded.ShardedHostGemmBF16(M, N, K, "cpu", gemm=gemm)
+        assert op.steps == 2 and op.block == 512 and op.piece == 512 // world
+        # a rank only ever reads its own pieces of B: everything else is poisoned in its host copy
+        b_host = torch.full_like(b_all, float("nan"))
+        for i in range(op.steps):
+            mine = slice(i * op.block + rank * op.piece, i * op.block + (rank + 1) * op.piece)
+            b_host[mine] = b_all[mine]
+        c_host = torch.empty((N, op.rows), dtype=torch.bfloat16)
+        op(a_all[op.lo:op.hi].contiguous(), b_host, c_host)
+        ref = O.gemm_bf16_cpu(A[op.lo:op.hi], B)
+        ok, worst = O.gemm_bf16_check(c_host.view(torch.int16).numpy().view(np.uint16), ref)
+        q.put((rank, ok, worst, op.h2d_bytes, op.d2h_bytes))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_sharded_host_gemm_uploads_each_row_of_b_once_across_ranks():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_gemm_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=120) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, ok, worst, h2d, d2h in results:
+        assert ok, (rank, worst)
+        assert h2d == (256 + 512) * 64 * 2 and d2h == 1024 * 256 * 2

@@ -11,7 +11,10 @@
 4. oracle/_ref/relink_sgemm_sweep  the reference's SGEMM sweep program (evals/4090_sgemm/main.cu), unmodified, linked
                                against libprism_b200.so through relink_sgemm_runner.cu instead of its own runner.cu.
 
-Steps 2 to 4 compile the reference's sources from where they lie (include path
+5. oracle/_ref/relink_scan_main  the reference's scan harness program (evals/4090_scan/main.cu and scan_harness.cuh), unmodified,
+                               on libprism_b200.so through relink_scan_main.cu.
+
+Steps 2 to 5 compile the reference's sources from where they lie (include path
 = the reference root); nothing is copied.  They are skipped when the reference
 tree is absent (e.g. on a GPU box, which uses the files built beforehand).
 The bf16 kernel is not built: wgmma does not assemble for sm_100.
@@ -73,7 +76,27 @@ def build_reference(reference: str = DEFAULT_REFERENCE, force: bool = False) -> 
     relink = build_relinked_sgemm_sweep(ref, force)
     if relink is not None:
         built["relink_sgemm_sweep"] = relink
+    relink = build_relinked_scan_main(ref, force)
+    if relink is not None:
+        built["relink_scan_main"] = relink
     return built
+
+
+def build_relinked_scan_main(ref: Path, force: bool = False) -> Path | None:
+    """The reference's own scan harness main and header, compiled in place, on this library's scan."""
+    main_cu = ref / "evals" / "4090_scan" / "main.cu"
+    lib = HERE.parent / "prism_b200" / "libprism_b200.so"
+    if not main_cu.exists() or not lib.exists():
+        return None
+    out = REF_OUT / "relink_scan_main"
+    shim = HERE / "relink_scan_main.cu"
+    if force or not _newer(out, [shim, lib]):
+        nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+        # flags of evals/4090_scan/Makefile:3-4 with the architecture changed; include path = the reference root
+        _run([nvcc, "-arch=sm_100", "-O3", "-w", "-std=c++17", f"-I{ref}", f"-I{HERE.parent / 'include'}", str(shim),
+              "-o", str(out), f"-L{lib.parent}", "-lprism_b200", "-Xlinker", "-rpath", "-Xlinker",
+              "$ORIGIN/../../prism_b200"])
+    return out
 
 
 def build_relinked_sgemm_sweep(ref: Path, force: bool = False) -> Path | None:

@@ -1,34 +1,48 @@
 // Scan sweep against CUB, the program behind the reference's scan figure
 // (evals/4090_scan/bench.cu:156-267): for n = 2^20 ... 2^30 both scans are checked element by
-// element against a CPU loop and timed as the best single run inside a 500 ms window, host clock
-// around launch + synchronise, input restored before every run (the reference re-uploads it from
-// the host; here a device-to-device copy of the same data, untimed).  Same table as the reference,
-// so evals/plot_results.py:82-108 parses it.
+// element against a CPU loop and then timed; the table has the reference's columns, so
+// evals/plot_results.py:82-108 parses it.  Timing differs from the reference's program in two
+// stated ways: a run is timed on the device (a pair of CUDA events around the launch, so launch
+// and synchronisation overhead of the host is not part of the figure; the reference reads the host
+// clock around launch + cudaDeviceSynchronize), and the input is restored before every run by a
+// device-to-device copy of the same data (the reference uploads it from the host again), untimed.
+// The figure reported is the fastest run, as in the reference.
 //
 //   scan_bench [max_log2n]        default 30
-#include <chrono>
 #include <cstdint>
 #include <cub/device/device_scan.cuh>
-#include <limits>
 #include <vector>
 
 #include "common.h"
 
-template <typename Reset, typename F>
-static double best_ms(double window_ms, Reset&& reset, F&& f) {
-    double best = std::numeric_limits<double>::infinity(), spent = 0.0;
-    while (spent < window_ms) {
-        reset();
-        EVAL_CUDA(cudaDeviceSynchronize());
-        const auto t0 = std::chrono::high_resolution_clock::now();
-        f();
-        EVAL_CUDA(cudaDeviceSynchronize());
-        const double ms = std::chrono::duration<double, std::milli>(std::chrono::high_resolution_clock::now() - t0).count();
-        spent += ms;
-        if (ms < best) best = ms;
+// Fastest of the runs that fit in `budget_ms` of device time (at least three runs).
+struct FastestRun {
+    cudaEvent_t begin, end;
+    FastestRun() {
+        EVAL_CUDA(cudaEventCreate(&begin));
+        EVAL_CUDA(cudaEventCreate(&end));
     }
-    return best;
-}
+    ~FastestRun() {
+        cudaEventDestroy(begin);
+        cudaEventDestroy(end);
+    }
+    template <typename Prepare, typename Run>
+    double operator()(double budget_ms, Prepare&& prepare, Run&& run) {
+        double fastest = 0.0, used = 0.0;
+        for (int runs = 0; runs < 3 || used < budget_ms; ++runs) {
+            prepare();
+            EVAL_CUDA(cudaEventRecord(begin, nullptr));
+            run();
+            EVAL_CUDA(cudaEventRecord(end, nullptr));
+            EVAL_CUDA(cudaEventSynchronize(end));
+            float ms = 0.f;
+            EVAL_CUDA(cudaEventElapsedTime(&ms, begin, end));
+            used += ms;
+            if (runs == 0 || ms < fastest) fastest = ms;
+        }
+        return fastest;
+    }
+};
 
 int main(int argc, char** argv) {
     const int max_log = argc > 1 ? std::atoi(argv[1]) : 30;
@@ -36,6 +50,7 @@ int main(int argc, char** argv) {
     std::printf("%-14s-+-%-10s-%-14s-+-%-10s-%-14s\n", "--------------", "----------", "--------------", "----------",
                 "--------------");
     Lcg rng(0xCA7CAFE);
+    FastestRun fastest;
     for (int lg = 20; lg <= max_log; ++lg) {
         const size_t n = size_t(1) << lg;
         std::vector<uint32_t> in(n), expect(n), got(n);
@@ -67,7 +82,7 @@ int main(int argc, char** argv) {
         EVAL_CUDA(cudaMemcpy(got.data(), d_out, n * 4, cudaMemcpyDeviceToHost));
         for (size_t i = 0; i < n; ++i)
             if (got[i] != expect[i]) { std::printf("CUB mismatch at %zu: got %u expected %u\n", i, got[i], expect[i]); return 1; }
-        const double cub_ms = best_ms(500.0, upload, [&] { cub::DeviceScan::InclusiveSum(d_cub, cub_bytes, d_in, d_out, n); });
+        const double cub_ms = fastest(500.0, upload, [&] { cub::DeviceScan::InclusiveSum(d_cub, cub_bytes, d_in, d_out, n); });
         EVAL_CUDA(cudaFree(d_cub));
         EVAL_CUDA(cudaFree(d_out));
 
@@ -81,7 +96,7 @@ int main(int argc, char** argv) {
         EVAL_CUDA(cudaMemcpy(got.data(), d_in, n * 4, cudaMemcpyDeviceToHost));
         for (size_t i = 0; i < n; ++i)
             if (got[i] != expect[i]) { std::printf("Ours mismatch at %zu: got %u expected %u\n", i, got[i], expect[i]); return 1; }
-        const double our_ms = best_ms(500.0, upload, [&] { eval_check(prism_b200_scan(n, d_in, d_ws, nullptr), "prism_b200_scan"); });
+        const double our_ms = fastest(500.0, upload, [&] { eval_check(prism_b200_scan(n, d_in, d_ws, nullptr), "prism_b200_scan"); });
         EVAL_CUDA(cudaFree(d_ws));
         EVAL_CUDA(cudaFree(d_in));
         EVAL_CUDA(cudaFree(d_src));

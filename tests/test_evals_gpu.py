@@ -77,6 +77,23 @@ def test_reference_sgemm_sweep_relinked_against_this_library():
     assert len(vals) == 36 and all(float(v) > 0 for v, _ in vals)
 
 
+def test_reference_scan_harness_relinked_against_this_library():
+    """The reference's scan harness program (evals/4090_scan/main.cu with scan_harness.cuh, both unmodified,
+    compiled where a checkout of the reference was present) on this library's scan: its own element-by-element
+    comparison with scan_cpu must pass at its five sizes (16384 ... 64 Mi) and its benchmark must print a
+    throughput.  Skipped where the binary was not built."""
+    exe = ROOT / "oracle" / "_ref" / "relink_scan_main"
+    if not exe.exists():
+        pytest.skip("oracle/_ref/relink_scan_main not built (needs a checkout of the reference at build time)")
+    out = _run([exe])
+    assert "Mismatch" not in out and "not yet implemented" not in out
+    sizes = [int(m.group(1)) for m in re.finditer(r"Testing size\s+(\d+)", out)]
+    assert sizes == [16384, 32768, 1 << 20, 16 << 20, 64 << 20]
+    assert out.count("  OK") == 5
+    m = re.search(r"Throughput:\s+([\d.]+) GB/s", out)
+    assert m and float(m.group(1)) > 0
+
+
 def test_host_e2e_program_through_the_c_abi_alone(binaries):
     """Host plans driven from C++ with cudaHostAlloc'ed arrays (no Python on the data path), small sizes."""
     out = _run([binaries / "host_e2e", 1024, 512, 23])

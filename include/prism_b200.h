@@ -227,6 +227,17 @@ int prism_b200_gemm_bf16(int M, int N, int K, const uint16_t* A, const uint16_t*
                          uint16_t* C, void* stream);
 
 /*
+ * The same product with a scaling epilogue: D = alpha * (A * B^T) + beta * Cin, all three matrices in the
+ * layouts of prism_b200_gemm_bf16 (Cin and D column-major M x N bf16; Cin == D is allowed, partial overlap is
+ * not).  The sum alpha * acc + beta * Cin is formed in fp32 from the fp32 accumulator and rounded once; with
+ * beta == 0 the values of Cin do not enter (NaN included).  No
+ * counterpart in the reference, whose bf16 kernel has no alpha/beta (its SGEMM kernels do,
+ * generated/my_sgemm_kernel_5.cu:56-77).  Runs on the one-CTA form of the kernel for every shape.
+ */
+int prism_b200_gemm_bf16_axpby(int M, int N, int K, float alpha, const uint16_t* A, const uint16_t* B, float beta,
+                               const uint16_t* Cin, uint16_t* D, void* stream);
+
+/*
  * How the 512 x 256 two-CTA form of the kernel above divides `tiles` output tiles of `k_blocks`
  * 64-wide k-blocks among `pairs` CTA pairs when the last wave of tiles is only partly filled: pair
  * `pair` computes out7[0] whole tiles (tile = i * pairs + pair) and then out7[1] (0, 1 or 2)

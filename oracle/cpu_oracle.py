@@ -127,6 +127,14 @@ def gemm_bf16_cpu(A_bits: np.ndarray, B_bits: np.ndarray) -> np.ndarray:
     return B @ A.T
 
 
+def gemm_bf16_axpby_cpu(alpha: float, A_bits: np.ndarray, B_bits: np.ndarray, beta: float, C_bits: np.ndarray) -> np.ndarray:
+    """fp64 value of alpha * (A @ B^T) + beta * C in the kernel's (N, M) layout; C_bits is the (N, M) array of bf16
+    bit patterns.  The reference's bf16 kernel has no such epilogue (its SGEMM kernels do,
+    generated/my_sgemm_kernel_5.cu:56-77); this is the checker of the library's flavour."""
+    C = bf16_bits_to_f32(C_bits).astype(np.float64).reshape(B_bits.shape[0], A_bits.shape[0])
+    return alpha * gemm_bf16_cpu(A_bits, B_bits) + beta * C
+
+
 GEMM_BF16_RTOL = 1e-2
 
 

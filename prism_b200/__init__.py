@@ -24,7 +24,7 @@ from ._lib import PrismB200Error, last_error, load  # noqa: F401
 
 __all__ = [
     "run_my_kernel", "get_workspace_size", "launch_scan", "runmyh100",
-    "sgemm", "scan_", "scan", "scan_f32_", "scan_static_", "scan_workspace", "gemm_bf16", "reduce_u32", "scan_seeded_", "scan_add_carry_",
+    "sgemm", "scan_", "scan", "scan_f32_", "scan_static_", "scan_workspace", "gemm_bf16", "gemm_bf16_axpby", "reduce_u32", "scan_seeded_", "scan_add_carry_",
     "scan_publish_total", "scan_seeded_peers_", "scan_sharded_",
     "launch_count", "last_error", "clear_error", "version", "PrismB200Error",
 ]
@@ -259,6 +259,26 @@ def runmyh100(M: int, N: int, K: int, A: torch.Tensor, B: torch.Tensor, C: torch
     with torch.cuda.device(C.device):
         _lib.check(load().prism_b200_gemm_bf16(int(M), int(N), int(K), A.data_ptr(), B.data_ptr(), C.data_ptr(),
                                                _stream(C)))
+
+
+def gemm_bf16_axpby(alpha: float, A: torch.Tensor, B: torch.Tensor, beta: float, C: torch.Tensor,
+                    out: torch.Tensor | None = None) -> torch.Tensor:
+    """alpha * (A @ B.T) + beta * C for A (M, K), B (N, K) and C given as the (N, M) tensor that holds the
+    column-major M x N matrix; returns `out` in the same layout (C itself by default: in place)."""
+    M, K = A.shape
+    N, K2 = B.shape
+    if K2 != K:
+        raise ValueError(f"K mismatch: A {tuple(A.shape)}, B {tuple(B.shape)}")
+    if out is None:
+        out = C
+    for name, t, numel in (("A", A, M * K), ("B", B, N * K), ("C", C, M * N), ("out", out, M * N)):
+        _require_cuda(name, t, torch.bfloat16)
+        if t.numel() != numel:
+            raise ValueError(f"{name} holds {t.numel()} elements, needs {numel}")
+    with torch.cuda.device(out.device):
+        _lib.check(load().prism_b200_gemm_bf16_axpby(int(M), int(N), int(K), float(alpha), A.data_ptr(), B.data_ptr(),
+                                                     float(beta), C.data_ptr(), out.data_ptr(), _stream(out)))
+    return out
 
 
 def gemm_bf16(A: torch.Tensor, B: torch.Tensor, out: torch.Tensor | None = None, row_major: bool = False) -> torch.Tensor:

@@ -140,10 +140,29 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
     tn = in / rows;
 }
 
-template <int BLOCK_Q>
-__global__ void __launch_bounds__(g16::THREADS, 1)
-cutlass_my_h100_match_no_tail(int M, int N, int K, __nv_bfloat16* C, const __grid_constant__ CUtensorMap tensorMapA,
-                              const __grid_constant__ CUtensorMap tensorMapB) {
+// alpha * acc + beta * c for eight bf16 values of C held in a uint4, packed back to bf16.
+__device__ __forceinline__ uint4 axpby8(const uint32_t* acc_bits, uint4 c, float alpha, float beta) {
+    const uint32_t cw[4] = {c.x, c.y, c.z, c.w};
+    uint32_t ow[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        // beta == 0 means "Cin does not enter", whatever it holds (NaN included), as in BLAS
+        const float c_lo = beta != 0.f ? beta * __uint_as_float(cw[i] << 16) : 0.f;
+        const float c_hi = beta != 0.f ? beta * __uint_as_float(cw[i] & 0xFFFF0000u) : 0.f;
+        const float lo = fmaf(alpha, __uint_as_float(acc_bits[2 * i]), c_lo);
+        const float hi = fmaf(alpha, __uint_as_float(acc_bits[2 * i + 1]), c_hi);
+        ow[i] = pack_bf16(__float_as_uint(lo), __float_as_uint(hi));
+    }
+    return make_uint4(ow[0], ow[1], ow[2], ow[3]);
+}
+
+// AXPBY: the epilogue stores alpha * (A * B^T) + beta * Cin instead of A * B^T (Cin in C's layout; Cin == C allowed).
+template <int BLOCK_Q, bool AXPBY>
+__device__ __forceinline__ void single_cta_body(int M, int N, int K, __nv_bfloat16* C, const CUtensorMap* mapA,
+                                                const CUtensorMap* mapB, float alpha, float beta,
+                                                const __nv_bfloat16* Cin) {
+    const CUtensorMap& tensorMapA = *mapA;
+    const CUtensorMap& tensorMapB = *mapB;
     using namespace g16;
     using C_ = Cfg<BLOCK_Q>;
     constexpr int STAGES = C_::STAGES;
@@ -295,7 +314,8 @@ cutlass_my_h100_match_no_tail(int M, int N, int K, __nv_bfloat16* C, const __gri
             }
             tc_fence_after();
             const size_t n = static_cast<size_t>(tn) * BLOCK_P + quarter * 32 + lane;
-            __nv_bfloat16* c_row = C + n * static_cast<size_t>(M) + static_cast<size_t>(tm) * BLOCK_Q;
+            const size_t c_off = n * static_cast<size_t>(M) + static_cast<size_t>(tm) * BLOCK_Q;
+            __nv_bfloat16* c_row = C + c_off;
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                                    static_cast<uint32_t>(acc * BLOCK_Q);
 #pragma unroll 2
@@ -307,10 +327,14 @@ cutlass_my_h100_match_no_tail(int M, int N, int K, __nv_bfloat16* C, const __gri
 #pragma unroll
                 for (int v = 0; v < 4; ++v) {
                     uint4 o;
-                    o.x = pack_bf16(r[8 * v + 0], r[8 * v + 1]);
-                    o.y = pack_bf16(r[8 * v + 2], r[8 * v + 3]);
-                    o.z = pack_bf16(r[8 * v + 4], r[8 * v + 5]);
-                    o.w = pack_bf16(r[8 * v + 6], r[8 * v + 7]);
+                    if constexpr (AXPBY) {
+                        o = axpby8(&r[8 * v], reinterpret_cast<const uint4*>(Cin + c_off + c)[v], alpha, beta);
+                    } else {
+                        o.x = pack_bf16(r[8 * v + 0], r[8 * v + 1]);
+                        o.y = pack_bf16(r[8 * v + 2], r[8 * v + 3]);
+                        o.z = pack_bf16(r[8 * v + 4], r[8 * v + 5]);
+                        o.w = pack_bf16(r[8 * v + 6], r[8 * v + 7]);
+                    }
                     dst[v] = o;
                 }
             }
@@ -337,6 +361,22 @@ cutlass_my_h100_match_no_tail(int M, int N, int K, __nv_bfloat16* C, const __gri
                      "r"(static_cast<uint32_t>(TMEM_COLS))
                      : "memory");
     }
+}
+
+template <int BLOCK_Q>
+__global__ void __launch_bounds__(g16::THREADS, 1)
+cutlass_my_h100_match_no_tail(int M, int N, int K, __nv_bfloat16* C, const __grid_constant__ CUtensorMap tensorMapA,
+                              const __grid_constant__ CUtensorMap tensorMapB) {
+    single_cta_body<BLOCK_Q, false>(M, N, K, C, &tensorMapA, &tensorMapB, 1.f, 0.f, nullptr);
+}
+
+// D = alpha * A * B^T + beta * Cin (no counterpart in the reference, whose kernel has no scaling epilogue).
+template <int BLOCK_Q>
+__global__ void __launch_bounds__(g16::THREADS, 1)
+cutlass_my_h100_match_no_tail_axpby(int M, int N, int K, __nv_bfloat16* D, const __grid_constant__ CUtensorMap tensorMapA,
+                                    const __grid_constant__ CUtensorMap tensorMapB, float alpha, float beta,
+                                    const __nv_bfloat16* Cin) {
+    single_cta_body<BLOCK_Q, true>(M, N, K, D, &tensorMapA, &tensorMapB, alpha, beta, Cin);
 }
 
 // ============================================================================
@@ -931,9 +971,18 @@ __device__ __forceinline__ void pair_wide_body(int M, int N, int K, __nv_bfloat1
                 tile_phase ^= 1u;
                 continue;
             }
-            // Pairs whose slots complete this tile (none unless this pair holds only the head of the tile).
-            int q_end = pair + 1;
+            // A lane reads one accumulator row (one n, consecutive m).  Writing that row straight to
+            // global memory would make every store instruction touch 32 different lines, 16 bytes
+            // each; instead the warp passes 32 rows x 64 columns at a time through shared memory
+            // (16-byte chunks XOR-swizzled by row, conflict-free both ways) and stores whole
+            // 128-byte lines: 4 rows per instruction.
+            const size_t n_warp = static_cast<size_t>(tn) * W_::TILE_N + rank * 256 + block * W_::HALF + quarter * 32;
+            __nv_bfloat16* c_warp = C + n_warp * static_cast<size_t>(M) + static_cast<size_t>(tm) * W_::TILE_M;
+            unsigned char* stage_buf = epi_smem + (warp - 2) * W_::EPI_WARP_BYTES;
             if (SPLIT && kb1 < k_blocks) {
+                // Finisher: this pair holds the head of the tile; the pairs after it, up to the one whose
+                // range reaches the tile's end, hold the rest and have written it to their slots.
+                int q_end = pair + 1;
                 const long long tile_end = (static_cast<long long>(t) - plan.rem_first_tile + 1) * k_blocks;
                 while (q_end < pairs && plan.rem_units * q_end / pairs < tile_end) ++q_end;
                 // This warp's rows of every contributing slot must have landed.
@@ -951,7 +1000,7 @@ __device__ __forceinline__ void pair_wide_body(int M, int N, int K, __nv_bfloat1
                                 landed = false;
                                 break;
                             }
-                            __nanosleep(100);
+                            __nanosleep(40);
                         }
                     }
                 }
@@ -959,15 +1008,57 @@ __device__ __forceinline__ void pair_wide_body(int M, int N, int K, __nv_bfloat1
                     timed_out = true;
                     break;
                 }
+                __syncwarp();
+                // 64 columns at a time: the partial sums of those columns are requested first (they come
+                // from L2, a microsecond away), then the accumulator is read, then both are added in pair
+                // order, rounded once and sent out through the staging buffer.
+                const float* slots = split.partials + tile_row;
+#pragma unroll 1
+                for (int c0 = 0; c0 < W_::TILE_M; c0 += 64) {
+                    float add[64];
+#pragma unroll
+                    for (int e = 0; e < 64; ++e) add[e] = 0.f;
+                    for (int q = pair + 1; q < q_end; ++q) {
+                        if (plan.rem_units * (q + 1) / pairs == plan.rem_units * q / pairs) continue;
+                        const float* slot = slots + static_cast<size_t>(q) * (W_::TILE_N * W_::TILE_M) +
+                                            static_cast<size_t>(c0) * W_::TILE_N;
+                        float got[64];
+#pragma unroll
+                        for (int e = 0; e < 64; ++e) got[e] = __ldcg(slot + static_cast<size_t>(e) * W_::TILE_N);
+#pragma unroll
+                        for (int e = 0; e < 64; ++e) add[e] += got[e];
+                    }
+                    uint32_t r0[32], r1[32];
+                    tmem_ld_32cols(t_row + c0, r0);
+                    tmem_ld_32cols(t_row + c0 + 32, r1);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int ch = 0; ch < 8; ++ch) {
+                        const uint32_t* r = ch < 4 ? &r0[8 * ch] : &r1[8 * (ch - 4)];
+                        const float* a = &add[8 * ch];
+                        uint4 o;
+                        o.x = pack_bf16(__float_as_uint(__uint_as_float(r[0]) + a[0]), __float_as_uint(__uint_as_float(r[1]) + a[1]));
+                        o.y = pack_bf16(__float_as_uint(__uint_as_float(r[2]) + a[2]), __float_as_uint(__uint_as_float(r[3]) + a[3]));
+                        o.z = pack_bf16(__float_as_uint(__uint_as_float(r[4]) + a[4]), __float_as_uint(__uint_as_float(r[5]) + a[5]));
+                        o.w = pack_bf16(__float_as_uint(__uint_as_float(r[6]) + a[6]), __float_as_uint(__uint_as_float(r[7]) + a[7]));
+                        *reinterpret_cast<uint4*>(stage_buf + lane * 128 + ((ch ^ (lane & 7)) << 4)) = o;
+                    }
+                    __syncwarp();
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const int row = 4 * j + (lane >> 3);
+                        const int ch = lane & 7;
+                        const uint4 v = *reinterpret_cast<const uint4*>(stage_buf + row * 128 + ((ch ^ (row & 7)) << 4));
+                        *reinterpret_cast<uint4*>(c_warp + static_cast<size_t>(row) * M + c0 + ch * 8) = v;
+                    }
+                    __syncwarp();
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(cluster_addr(acc_empty_bar, 0));
+                tile_phase ^= 1u;
+                continue;
             }
-            // A lane reads one accumulator row (one n, consecutive m).  Writing that row straight to
-            // global memory would make every store instruction touch 32 different lines, 16 bytes
-            // each; instead the warp passes 32 rows x 64 columns at a time through shared memory
-            // (16-byte chunks XOR-swizzled by row, conflict-free both ways) and stores whole
-            // 128-byte lines: 4 rows per instruction.
-            const size_t n_warp = static_cast<size_t>(tn) * W_::TILE_N + rank * 256 + block * W_::HALF + quarter * 32;
-            __nv_bfloat16* c_warp = C + n_warp * static_cast<size_t>(M) + static_cast<size_t>(tm) * W_::TILE_M;
-            unsigned char* stage_buf = epi_smem + (warp - 2) * W_::EPI_WARP_BYTES;
             // The whole accumulator row first goes into registers as packed bf16 (256 columns = 128
             // registers), so that tensor memory can be handed back and the next tile's MMAs start
             // while this tile is still on its way to global memory.
@@ -977,15 +1068,6 @@ __device__ __forceinline__ void pair_wide_body(int M, int N, int K, __nv_bfloat1
                 uint32_t r[32];
                 tmem_ld_32cols(t_row + c0, r);
                 tmem_ld_wait();
-                if (SPLIT && q_end > pair + 1) {
-                    for (int q = pair + 1; q < q_end; ++q) {
-                        if (plan.rem_units * (q + 1) / pairs == plan.rem_units * q / pairs) continue;
-                        const float* slot = split.partials + static_cast<size_t>(q) * (W_::TILE_N * W_::TILE_M) + tile_row;
-#pragma unroll
-                        for (int e = 0; e < 32; ++e)
-                            r[e] = __float_as_uint(__uint_as_float(r[e]) + __ldcg(slot + static_cast<size_t>(c0 + e) * W_::TILE_N));
-                    }
-                }
 #pragma unroll
                 for (int e = 0; e < 16; ++e) packed[c0 / 2 + e] = pack_bf16(r[2 * e], r[2 * e + 1]);
             }
@@ -1129,6 +1211,34 @@ int launch_gemm(int dev, int sms, int M, int N, int K, const void* A, const void
     const int tiles = (M / BLOCK_Q) * (N / g16::BLOCK_P);
     const int grid = tiles < sms ? tiles : sms;
     kern<<<grid, g16::THREADS, C_::SMEM_BYTES, s>>>(M, N, K, static_cast<__nv_bfloat16*>(C), map_a, map_b);
+    PRISM_CUDA_TRY(cudaGetLastError());
+    count_launch();
+    return PRISM_B200_OK;
+}
+
+// The one-CTA kernel with the scaling epilogue: D = alpha * A * B^T + beta * Cin.
+template <int BLOCK_Q>
+int launch_gemm_axpby(int dev, int sms, int M, int N, int K, float alpha, const void* A, const void* B, float beta,
+                      const void* Cin, void* D, cudaStream_t s) {
+    using C_ = g16::Cfg<BLOCK_Q>;
+    CUtensorMap map_a, map_b;
+    if (int rc = get_tensor_map(dev, A, M, K, BLOCK_Q, &map_a)) return rc;
+    if (int rc = get_tensor_map(dev, B, N, K, g16::BLOCK_P, &map_b)) return rc;
+    auto kern = cutlass_my_h100_match_no_tail_axpby<BLOCK_Q>;
+    {
+        static bool attr_set[64] = {};
+        static std::mutex mu;
+        std::lock_guard<std::mutex> lk(mu);
+        if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+            PRISM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                static_cast<int>(C_::SMEM_BYTES)));
+            if (dev >= 0 && dev < 64) attr_set[dev] = true;
+        }
+    }
+    const int tiles = (M / BLOCK_Q) * (N / g16::BLOCK_P);
+    const int grid = tiles < sms ? tiles : sms;
+    kern<<<grid, g16::THREADS, C_::SMEM_BYTES, s>>>(M, N, K, static_cast<__nv_bfloat16*>(D), map_a, map_b, alpha, beta,
+                                                    static_cast<const __nv_bfloat16*>(Cin));
     PRISM_CUDA_TRY(cudaGetLastError());
     count_launch();
     return PRISM_B200_OK;
@@ -1341,6 +1451,38 @@ extern "C" int prism_b200_gemm_bf16_split_plan(int tiles, int pairs, int k_block
     out7[0] = p.full; out7[1] = p.segs; out7[2] = p.tile0; out7[3] = p.kb0_0; out7[4] = p.kb1_0; out7[5] = p.tile1;
     out7[6] = p.kb1_1;
     return PRISM_B200_OK;
+}
+
+extern "C" int prism_b200_gemm_bf16_axpby(int M, int N, int K, float alpha, const uint16_t* A, const uint16_t* B, float beta,
+                                          const uint16_t* Cin, uint16_t* D, void* stream) {
+    if (M < 0 || N < 0 || K < 0) return set_error(PRISM_B200_ERR_INVALID_ARGUMENT, "gemm_bf16_axpby: negative dimension");
+    if (M == 0 || N == 0) return PRISM_B200_OK;
+    if (!A || !B || !Cin || !D) return set_error(PRISM_B200_ERR_INVALID_ARGUMENT, "gemm_bf16_axpby: null pointer");
+    if (M % 128 || N % 128 || K % 64 || K == 0)
+        return set_error(PRISM_B200_ERR_UNSUPPORTED_SHAPE,
+                         "gemm_bf16_axpby: need M %% 128 == 0, N %% 128 == 0, K %% 64 == 0, K > 0 (got %d, %d, %d)", M, N, K);
+    if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(Cin) |
+         reinterpret_cast<uintptr_t>(D)) & 15u)
+        return set_error(PRISM_B200_ERR_MISALIGNED, "gemm_bf16_axpby: A, B, Cin and D must be 16-byte aligned");
+    if (Cin != D) {
+        const uintptr_t a = reinterpret_cast<uintptr_t>(Cin), b = reinterpret_cast<uintptr_t>(D);
+        const size_t bytes = static_cast<size_t>(M) * N * 2;
+        if (a < b + bytes && b < a + bytes)
+            return set_error(PRISM_B200_ERR_INVALID_ARGUMENT, "gemm_bf16_axpby: Cin and D overlap without being equal");
+    }
+    if (int rc = bind_status_word()) return rc;
+    int dev = 0, sms = 0;
+    PRISM_CUDA_TRY(cudaGetDevice(&dev));
+    PRISM_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // 256-wide m-tiles unless M does not divide or they would leave a poorly filled last wave (as in prism_b200_gemm_bf16).
+    bool wide = (M % 256 == 0);
+    if (wide) {
+        auto eff = [&](int tiles) { return static_cast<double>(tiles) / (((tiles + sms - 1) / sms) * sms); };
+        if (eff((M / 256) * (N / 128)) + 0.10 < eff((M / 128) * (N / 128))) wide = false;
+    }
+    return wide ? launch_gemm_axpby<256>(dev, sms, M, N, K, alpha, A, B, beta, Cin, D, s)
+                : launch_gemm_axpby<128>(dev, sms, M, N, K, alpha, A, B, beta, Cin, D, s);
 }
 
 extern "C" int prism_b200_gemm_bf16(int M, int N, int K, const uint16_t* A, const uint16_t* B, uint16_t* C,

@@ -238,13 +238,17 @@ int prism_b200_gemm_bf16_axpby(int M, int N, int K, float alpha, const uint16_t*
                                const uint16_t* Cin, uint16_t* D, void* stream);
 
 /*
- * How the 512 x 256 two-CTA form of the kernel above divides `tiles` output tiles of `k_blocks`
- * 64-wide k-blocks among `pairs` CTA pairs when the last wave of tiles is only partly filled: pair
+ * How the split variant of the 512 x 256 two-CTA form of the kernel above divides `tiles` output tiles of
+ * `k_blocks` 64-wide k-blocks among `pairs` CTA pairs when the last wave of tiles is only partly filled.  The
+ * variant runs only on request (environment variable PRISM_B200_GEMM_SPLIT=1): measured on a B200 it loses to
+ * the unsplit kernel at the benchmark shapes, because pairs that start at different k-blocks stop sharing
+ * operand rows in L2.  Pair
  * `pair` computes out7[0] whole tiles (tile = i * pairs + pair) and then out7[1] (0, 1 or 2)
  * segments of the last wave, which is cut along K into `pairs` equal ranges:
  *   segment 1: tile out7[2], k-blocks [out7[3], out7[4]);  segment 2: tile out7[5], k-blocks [0, out7[6]).
  * A segment that does not start at k-block 0 is written as fp32 partial sums to a workspace owned by
- * the library (one per device and stream, 37 MB on a B200, allocated at the first launch that splits);
+ * the library (one per device and stream, 37 MB on a B200, allocated at the first launch that splits,
+ * freed when the host plan that owns the stream is destroyed, else at exit);
  * the pair that holds k-block 0 of the tile adds the others' partial sums in pair order and stores
  * the tile, so results do not depend on timing.  Host-side arithmetic only (no GPU needed); it is
  * the same function the kernel evaluates.  The reference's kernel has a fixed grid of 128 CTAs and

@@ -1386,21 +1386,7 @@ void release_gemm_split_workspace(cudaStream_t stream) {
 
 namespace {
 
-// k-blocks that the dump of a contribution and its addition cost, in units of main-loop k-blocks
-// (an estimate for the decision below, not a measured constant of the kernel).
-constexpr int kSplitOverheadKb = 8;
-
-// Time of the 512 x 256 form in k-blocks per pair, with and without the split of the last wave.
-void wide_estimate(long long tiles, int pairs, int k_blocks, double* unsplit, double* split) {
-    const long long full = tiles / pairs, rem = tiles % pairs;
-    *unsplit = static_cast<double>((full + (rem ? 1 : 0)) * k_blocks);
-    const double share = static_cast<double>(rem) * k_blocks / pairs;
-    *split = (rem && share >= 8.0 && share + kSplitOverheadKb < k_blocks)
-                 ? static_cast<double>(full * k_blocks) + share + kSplitOverheadKb
-                 : *unsplit;
-}
-
-int g_forced_split = -2;   // PRISM_B200_GEMM_SPLIT = 0 / 1 forces the unsplit / split kernel (tests)
+int g_forced_split = -1;   // PRISM_B200_GEMM_SPLIT=1 asks for the split kernel (tests, measurements)
 
 int launch_gemm_pair_wide(int dev, int M, int N, int K, const void* A, const void* B, void* C, cudaStream_t s) {
     using W_ = g16::WideCfg;
@@ -1414,12 +1400,13 @@ int launch_gemm_pair_wide(int dev, int M, int N, int K, const void* A, const voi
     if (int rc = pair_capacity(cutlass_my_h100_match_no_tail_pair_wide_split<16>, max_pairs_split, W_::THREADS,
                                W_::SMEM_BYTES, dev, &pairs_cap))
         return rc;
-    double t_unsplit, t_split;
-    wide_estimate(tiles, pairs_cap, k_blocks, &t_unsplit, &t_split);
-    bool want_split = t_split < t_unsplit;
-    if (g_forced_split == 0) want_split = false;
-    // Forced: any shape with a partly filled last wave whose pairs all get at least one k-block.
-    if (g_forced_split == 1) want_split = tiles % pairs_cap != 0 && static_cast<long long>(tiles % pairs_cap) * k_blocks >= pairs_cap;
+    // Measured on a B200, the split kernel loses at every benchmark shape (8192^3 on 1, 2, 4 and 8 GPUs, 4096^3,
+    // 6144^3): pairs whose ranges start at different k-blocks no longer load the same operand rows at the same
+    // time, so the split wave streams its operands from HBM instead of sharing them in L2 and runs about 1.4
+    // times slower per k-block, which costs more than the idle pairs it saves.  It therefore runs only on request
+    // (PRISM_B200_GEMM_SPLIT=1): any shape with a partly filled last wave whose pairs all get at least one k-block.
+    const bool want_split = g_forced_split == 1 && tiles % pairs_cap != 0 &&
+                            static_cast<long long>(tiles % pairs_cap) * k_blocks >= pairs_cap;
     if (want_split) {
         SplitArgs split{};
         bool have = false;
@@ -1543,10 +1530,7 @@ extern "C" int prism_b200_gemm_bf16(int M, int N, int K, const uint16_t* A, cons
                 if (t < best) { best = t; form = 1; }
             }
             if (wide_ok) {
-                // with its last wave cut along K the 512 x 256 form has no partly filled wave to pay for
-                double t_unsplit, t_split;
-                wide_estimate(static_cast<long long>(M / 256) * (N / 512), pairs, K / g16::BLOCK_K, &t_unsplit, &t_split);
-                const double t = (g_forced_split == 0 ? t_unsplit : t_split) / (K / g16::BLOCK_K) * 2.0;
+                const double t = waves(static_cast<long long>(M / 256) * (N / 512), pairs) * 2.0;
                 if (t <= best) { best = t; form = 2; }
             }
         }

@@ -45,7 +45,8 @@ SIGNATURES = {
     "prism_b200_scan_static": (c_int, [c_size_t, c_void_p, c_void_p]),
     "prism_b200_gemm_bf16": (c_int, [c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     "prism_b200_gemm_bf16_axpby": (c_int, [c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p]),
-    "prism_b200_gemm_bf16_split_plan": (c_int, [c_int, c_int, c_int, c_int, POINTER(c_int)]),
+    "prism_b200_gemm_bf16_split_mode": (c_int, [c_int]),
+    "prism_b200_gemm_bf16_split_plan": (c_int, [c_int, c_int, c_int, c_int, c_int, POINTER(c_int)]),
     "prism_b200_host_gemm_bf16_create": (c_int, [c_int, c_int, c_int, c_int, POINTER(c_void_p)]),
     "prism_b200_host_gemm_bf16_run": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "prism_b200_host_sgemm_create": (c_int, [c_int, c_int, c_int, c_int, c_int, POINTER(c_void_p)]),

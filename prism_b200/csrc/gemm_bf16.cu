@@ -718,76 +718,73 @@ struct WideCfg {
 
 // What the split form needs beyond the reference's parameter list.
 struct SplitArgs {
-    float* partials;      // one 512 x 256 fp32 slot per CTA pair
-    uint32_t* flags;      // 16 words per pair (one per epilogue warp of the pair); a slot is valid when they hold `epoch`
+    float* partials;      // one 512 x 256 fp32 slot per tile of the last wave
+    uint32_t* flags;      // 16 words per slot (one per epilogue warp of a pair); a slot is valid when they hold `epoch`
     uint32_t epoch;       // differs from every earlier launch that used this workspace
+    int tail;             // k-blocks at the end of every tile of the last wave that a helper pair computes
 };
 
-// The work of one CTA pair: `full` whole tiles (tile = i * pairs + pair), then up to two segments of
-// the last, partly filled wave.  Without SPLIT a pair simply takes every pairs-th tile.  With SPLIT
-// the R = tiles mod pairs tiles of the last wave are cut along K into pairs equal ranges of
-// k-blocks (R * k_blocks / pairs each, less than one tile), so a pair gets the tail of one tile
-// and/or the head of the next:
-//   kb0 > 0   the pair contributes: it writes its fp32 accumulators to its slot and raises its flags;
-//   kb0 == 0  the pair finishes the tile: it adds the slots of the pairs that hold the rest of the
-//             tile, in pair order (so the result does not depend on timing), and stores bf16.
-// A pair contributes first and finishes last, and the pairs it waits for contribute first too, so
-// the wait is short; a pair never waits for a pair that waits for it.
+// The work of one CTA pair: `full` whole tiles (tile = i * pairs + pair), then its part of the last,
+// partly filled wave.  Without SPLIT a pair simply takes every pairs-th tile.  With SPLIT the
+// R = tiles mod pairs tiles of the last wave are shared between the R pairs that would have computed
+// them alone and the pairs - R pairs that would have had nothing to do:
+//   pair < R   "owner": computes k-blocks [0, k_blocks - tail) of tile R0 + pair, then adds the fp32 sums
+//              that a helper left in the tile's slot and stores bf16;
+//   pair >= R  "helper": computes the last `tail` k-blocks of a few consecutive tiles of the wave, one
+//              after the other, writes each result to that tile's slot and raises the slot's flags.
+// The owners all walk k from 0 in step, so they keep sharing operand rows in L2 as in a full wave; the
+// few helpers re-read one narrow k-range for several neighbouring tiles.  A helper never waits, and
+// an owner waits only for a slot that was filled while it was still in its own main loop, so there
+// is no cycle of waits.  The sum is owner part + helper part, always in that order.
 struct PairPlan {
-    int full;
-    int segs;
-    int tile0, kb0_0, kb1_0;               // first segment (tail or middle of a tile, or a head)
-    int tile1, kb1_1;                      // second segment: always the head of the next tile (kb0 = 0)
-    long long rem_units, rem_first_tile;   // k-blocks of the split wave; its first tile
+    int full;        // whole tiles before the last wave
+    int segs;        // items of the last wave: 1 for an owner, the number of tails for a helper, else 0
+    int first_tile;  // tile of the first of them (the others follow consecutively)
+    int kb0, kb1;    // their k-block range
+    int wave_first;  // first tile of the last wave (slot index = tile - wave_first)
 };
 
 template <bool SPLIT>
-__host__ __device__ __forceinline__ PairPlan make_pair_plan(int pair, int pairs, int total_tiles, int k_blocks) {
+__host__ __device__ __forceinline__ PairPlan make_pair_plan(int pair, int pairs, int total_tiles, int k_blocks, int tail) {
     PairPlan p;
     p.segs = 0;
-    p.tile0 = p.tile1 = p.kb0_0 = p.kb1_0 = p.kb1_1 = 0;
-    p.rem_units = 0;
-    p.rem_first_tile = total_tiles;
+    p.first_tile = 0;
+    p.kb0 = 0;
+    p.kb1 = k_blocks;
+    p.wave_first = total_tiles;
     if constexpr (!SPLIT) {
         p.full = pair < total_tiles ? (total_tiles - pair + pairs - 1) / pairs : 0;
     } else {
         p.full = total_tiles / pairs;
-        const int rem = total_tiles - p.full * pairs;
-        p.rem_first_tile = static_cast<long long>(p.full) * pairs;
-        p.rem_units = static_cast<long long>(rem) * k_blocks;
-        const long long r0 = p.rem_units * pair / pairs, r1 = p.rem_units * (pair + 1) / pairs;
-        if (r1 > r0) {
-            const int t0 = static_cast<int>(r0 / k_blocks), kb0 = static_cast<int>(r0 % k_blocks);
-            const long long len = r1 - r0;
-            const int first = static_cast<int>(len < k_blocks - kb0 ? len : k_blocks - kb0);
-            p.tile0 = static_cast<int>(p.rem_first_tile) + t0;
-            p.kb0_0 = kb0;
-            p.kb1_0 = kb0 + first;
+        const int rem = total_tiles - p.full * pairs;       // tiles of the last wave = number of owners
+        const int helpers = pairs - rem;
+        p.wave_first = p.full * pairs;
+        if (rem > 0 && pair < rem) {
             p.segs = 1;
-            if (len > first) {   // less than one tile per pair, so the rest lies in the next tile
-                p.tile1 = p.tile0 + 1;
-                p.kb1_1 = static_cast<int>(len - first);
-                p.segs = 2;
-            }
+            p.first_tile = p.wave_first + pair;
+            p.kb1 = k_blocks - tail;
+        } else if (rem > 0 && tail > 0) {
+            const int h = pair - rem;                        // helper h takes tiles [h * rem / helpers, (h + 1) * rem / helpers)
+            const int i0 = static_cast<int>(static_cast<long long>(h) * rem / helpers);
+            const int i1 = static_cast<int>(static_cast<long long>(h + 1) * rem / helpers);
+            p.segs = i1 - i0;
+            p.first_tile = p.wave_first + i0;
+            p.kb0 = k_blocks - tail;
         }
     }
     return p;
 }
 
-__device__ __forceinline__ void plan_item(const PairPlan& p, int i, int pair, int pairs, int k_blocks, int& tile, int& kb0,
-                                          int& kb1) {
+__host__ __device__ __forceinline__ void plan_item(const PairPlan& p, int i, int pair, int pairs, int k_blocks, int& tile,
+                                                   int& kb0, int& kb1) {
     if (i < p.full) {
         tile = i * pairs + pair;
         kb0 = 0;
         kb1 = k_blocks;
-    } else if (i == p.full) {
-        tile = p.tile0;
-        kb0 = p.kb0_0;
-        kb1 = p.kb1_0;
     } else {
-        tile = p.tile1;
-        kb0 = 0;
-        kb1 = p.kb1_1;
+        tile = p.first_tile + (i - p.full);
+        kb0 = p.kb0;
+        kb1 = p.kb1;
     }
 }
 
@@ -821,7 +818,7 @@ __device__ __forceinline__ void pair_wide_body(int M, int N, int K, __nv_bfloat1
     const int tiles_n = N / W_::TILE_N;
     const int total_tiles = tiles_m * tiles_n;
     const int k_blocks = K / BLOCK_K;
-    const PairPlan plan = make_pair_plan<SPLIT>(pair, pairs, total_tiles, k_blocks);
+    const PairPlan plan = make_pair_plan<SPLIT>(pair, pairs, total_tiles, k_blocks, split.tail);
     const int items = plan.full + plan.segs;
 
     if (threadIdx.x == 0) {
@@ -949,9 +946,10 @@ __device__ __forceinline__ void pair_wide_body(int M, int N, int K, __nv_bfloat1
             tc_fence_after();
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(block * 256);
             if (SPLIT && kb0 > 0) {
-                // Contributor: fp32 accumulators to this pair's slot, column by column so that the 32 lanes
+                // Helper: fp32 accumulators to the tile's slot, column by column so that the 32 lanes
                 // (32 consecutive rows) write one 128-byte line per store; then this warp's flag.
-                float* slot = split.partials + static_cast<size_t>(pair) * (W_::TILE_N * W_::TILE_M) + tile_row;
+                const int slot_idx = t - plan.wave_first;
+                float* slot = split.partials + static_cast<size_t>(slot_idx) * (W_::TILE_N * W_::TILE_M) + tile_row;
 #pragma unroll 1
                 for (int c0 = 0; c0 < W_::TILE_M; c0 += 32) {
                     uint32_t r[32];
@@ -960,12 +958,14 @@ __device__ __forceinline__ void pair_wide_body(int M, int N, int K, __nv_bfloat1
 #pragma unroll
                     for (int e = 0; e < 32; ++e) __stcg(slot + static_cast<size_t>(c0 + e) * W_::TILE_N, __uint_as_float(r[e]));
                 }
+                // Tensor memory has been read (the stores may still be on their way): the next tail's MMAs can start.
                 tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(cluster_addr(acc_empty_bar, 0));
                 __threadfence();
                 __syncwarp();
                 if (lane == 0) {
-                    mbar_arrive_cluster(cluster_addr(acc_empty_bar, 0));
-                    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(split.flags + pair * 16 + flag_idx), "r"(split.epoch)
+                    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(split.flags + slot_idx * 16 + flag_idx), "r"(split.epoch)
                                  : "memory");
                 }
                 tile_phase ^= 1u;
@@ -979,29 +979,23 @@ __device__ __forceinline__ void pair_wide_body(int M, int N, int K, __nv_bfloat1
             const size_t n_warp = static_cast<size_t>(tn) * W_::TILE_N + rank * 256 + block * W_::HALF + quarter * 32;
             __nv_bfloat16* c_warp = C + n_warp * static_cast<size_t>(M) + static_cast<size_t>(tm) * W_::TILE_M;
             unsigned char* stage_buf = epi_smem + (warp - 2) * W_::EPI_WARP_BYTES;
-            if (SPLIT && kb1 < k_blocks) {
-                // Finisher: this pair holds the head of the tile; the pairs after it, up to the one whose
-                // range reaches the tile's end, hold the rest and have written it to their slots.
-                int q_end = pair + 1;
-                const long long tile_end = (static_cast<long long>(t) - plan.rem_first_tile + 1) * k_blocks;
-                while (q_end < pairs && plan.rem_units * q_end / pairs < tile_end) ++q_end;
-                // This warp's rows of every contributing slot must have landed.
+            if (SPLIT && kb1 < k_blocks) {   // kb0 == 0 here: the helpers' items were handled above
+                // Owner: a helper computed the last k-blocks of this tile and left them in the tile's slot;
+                // this warp's rows of the slot must have landed.
+                const int slot_idx = t - plan.wave_first;
                 bool landed = true;
                 if (lane == 0) {
-                    for (int q = pair + 1; q < q_end && landed; ++q) {
-                        if (plan.rem_units * (q + 1) / pairs == plan.rem_units * q / pairs) continue;   // a pair without work
-                        const uint32_t* f = split.flags + q * 16 + flag_idx;
-                        const unsigned long long t0 = global_timer_ns();
-                        uint32_t v;
-                        for (uint32_t spin = 0;; ++spin) {
-                            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
-                            if (v == split.epoch) break;
-                            if ((spin & 63u) == 63u && (*abort_flag || global_timer_ns() - t0 > kWaitLimitNs)) {
-                                landed = false;
-                                break;
-                            }
-                            __nanosleep(40);
+                    const uint32_t* f = split.flags + slot_idx * 16 + flag_idx;
+                    const unsigned long long t0 = global_timer_ns();
+                    uint32_t v;
+                    for (uint32_t spin = 0;; ++spin) {
+                        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+                        if (v == split.epoch) break;
+                        if ((spin & 63u) == 63u && (*abort_flag || global_timer_ns() - t0 > kWaitLimitNs)) {
+                            landed = false;
+                            break;
                         }
+                        __nanosleep(40);
                     }
                 }
                 if (!__all_sync(0xffffffffu, landed)) {
@@ -1012,22 +1006,12 @@ __device__ __forceinline__ void pair_wide_body(int M, int N, int K, __nv_bfloat1
                 // 64 columns at a time: the partial sums of those columns are requested first (they come
                 // from L2, a microsecond away), then the accumulator is read, then both are added in pair
                 // order, rounded once and sent out through the staging buffer.
-                const float* slots = split.partials + tile_row;
+                const float* slot = split.partials + static_cast<size_t>(slot_idx) * (W_::TILE_N * W_::TILE_M) + tile_row;
 #pragma unroll 1
                 for (int c0 = 0; c0 < W_::TILE_M; c0 += 64) {
                     float add[64];
 #pragma unroll
-                    for (int e = 0; e < 64; ++e) add[e] = 0.f;
-                    for (int q = pair + 1; q < q_end; ++q) {
-                        if (plan.rem_units * (q + 1) / pairs == plan.rem_units * q / pairs) continue;
-                        const float* slot = slots + static_cast<size_t>(q) * (W_::TILE_N * W_::TILE_M) +
-                                            static_cast<size_t>(c0) * W_::TILE_N;
-                        float got[64];
-#pragma unroll
-                        for (int e = 0; e < 64; ++e) got[e] = __ldcg(slot + static_cast<size_t>(e) * W_::TILE_N);
-#pragma unroll
-                        for (int e = 0; e < 64; ++e) add[e] += got[e];
-                    }
+                    for (int e = 0; e < 64; ++e) add[e] = __ldcg(slot + static_cast<size_t>(c0 + e) * W_::TILE_N);
                     uint32_t r0[32], r1[32];
                     tmem_ld_32cols(t_row + c0, r0);
                     tmem_ld_32cols(t_row + c0 + 32, r1);
@@ -1386,7 +1370,10 @@ void release_gemm_split_workspace(cudaStream_t stream) {
 
 namespace {
 
-int g_forced_split = -1;   // PRISM_B200_GEMM_SPLIT=1 asks for the split kernel (tests, measurements)
+bool g_split_mode_set = false;   // prism_b200_gemm_bf16_split_mode was called: the environment no longer decides
+int g_forced_split = -1;   // 1 (PRISM_B200_GEMM_SPLIT=1 or prism_b200_gemm_bf16_split_mode) asks for the split kernel
+// Cost of one hand-over of partial sums (helper writes 512 KB, owner re-reads them), in main-loop k-blocks.
+constexpr int kSplitDumpKb = 7;
 
 int launch_gemm_pair_wide(int dev, int M, int N, int K, const void* A, const void* B, void* C, cudaStream_t s) {
     using W_ = g16::WideCfg;
@@ -1400,18 +1387,27 @@ int launch_gemm_pair_wide(int dev, int M, int N, int K, const void* A, const voi
     if (int rc = pair_capacity(cutlass_my_h100_match_no_tail_pair_wide_split<16>, max_pairs_split, W_::THREADS,
                                W_::SMEM_BYTES, dev, &pairs_cap))
         return rc;
-    // Measured on a B200, the split kernel loses at every benchmark shape (8192^3 on 1, 2, 4 and 8 GPUs, 4096^3,
-    // 6144^3): pairs whose ranges start at different k-blocks no longer load the same operand rows at the same
-    // time, so the split wave streams its operands from HBM instead of sharing them in L2 and runs about 1.4
-    // times slower per k-block, which costs more than the idle pairs it saves.  It therefore runs only on request
-    // (PRISM_B200_GEMM_SPLIT=1): any shape with a partly filled last wave whose pairs all get at least one k-block.
-    const bool want_split = g_forced_split == 1 && tiles % pairs_cap != 0 &&
-                            static_cast<long long>(tiles % pairs_cap) * k_blocks >= pairs_cap;
+    // Sharing the last wave's R tiles with the pairs - R idle pairs: a helper with n tails spends n * (tail + hand-over)
+    // k-block times while the owners spend k_blocks - tail, so tail = (k_blocks - n * hand-over) / (n + 1) makes both
+    // end together.  Measured on a B200 (split on and off alternating in one process, median of 30): 8192^3 cut over
+    // 8 / 4 / 2 / 1 GPUs 11 % slower / 2 % faster / equal / 3 % slower, 4096^3 3 % slower, 6144^3 6 % slower, 12288^3
+    // 2 % faster -- handing 512 KB of fp32 sums per tile from one pair to another (write, fence, flag, re-read, add)
+    // costs about as much as the idle pairs are worth.  The split therefore runs only on request
+    // (prism_b200_gemm_bf16_split_mode(1) or PRISM_B200_GEMM_SPLIT=1), wherever the shape allows a tail of >= 1.
+    const int rem = tiles % pairs_cap, helpers = pairs_cap - rem;
+    int tail = 0;
+    if (rem > 0 && helpers > 0) {
+        const int n = (rem + helpers - 1) / helpers;
+        tail = (k_blocks - n * kSplitDumpKb) / (n + 1);
+        if (tail >= k_blocks) tail = k_blocks - 1;
+    }
+    const bool want_split = g_forced_split == 1 && tail >= 1;
     if (want_split) {
         SplitArgs split{};
         bool have = false;
         if (int rc = split_workspace(dev, s, pairs_cap, &split, &have)) return rc;
         if (have) {
+            split.tail = tail;
             cudaLaunchConfig_t cfg;
             cudaLaunchAttribute attr[1];
             pair_launch_config(&cfg, attr, W_::THREADS, W_::SMEM_BYTES, s);
@@ -1431,12 +1427,19 @@ int launch_gemm_pair_wide(int dev, int M, int N, int K, const void* A, const voi
 
 using namespace prism_b200;
 
-extern "C" int prism_b200_gemm_bf16_split_plan(int tiles, int pairs, int k_blocks, int pair, int* out7) {
-    if (!out7 || tiles < 0 || pairs < 1 || k_blocks < 1 || pair < 0 || pair >= pairs)
+extern "C" int prism_b200_gemm_bf16_split_mode(int mode) {
+    if (mode < -1 || mode > 1) return set_error(PRISM_B200_ERR_INVALID_ARGUMENT, "gemm_bf16_split_mode: -1, 0 or 1");
+    std::lock_guard<std::mutex> lk(g_launch_mu);
+    g_split_mode_set = true;
+    g_forced_split = mode;
+    return PRISM_B200_OK;
+}
+
+extern "C" int prism_b200_gemm_bf16_split_plan(int tiles, int pairs, int k_blocks, int tail, int pair, int* out5) {
+    if (!out5 || tiles < 0 || pairs < 1 || k_blocks < 1 || tail < 0 || tail >= k_blocks || pair < 0 || pair >= pairs)
         return set_error(PRISM_B200_ERR_INVALID_ARGUMENT, "gemm_bf16_split_plan: bad argument");
-    const PairPlan p = make_pair_plan<true>(pair, pairs, tiles, k_blocks);
-    out7[0] = p.full; out7[1] = p.segs; out7[2] = p.tile0; out7[3] = p.kb0_0; out7[4] = p.kb1_0; out7[5] = p.tile1;
-    out7[6] = p.kb1_1;
+    const PairPlan p = make_pair_plan<true>(pair, pairs, tiles, k_blocks, tail);
+    out5[0] = p.full; out5[1] = p.segs; out5[2] = p.first_tile; out5[3] = p.kb0; out5[4] = p.kb1;
     return PRISM_B200_OK;
 }
 
@@ -1502,7 +1505,7 @@ extern "C" int prism_b200_gemm_bf16(int M, int N, int K, const uint16_t* A, cons
             const char* e = getenv("PRISM_B200_GEMM_PAIR");
             forced = e ? atoi(e) : -1;
             const char* sp = getenv("PRISM_B200_GEMM_SPLIT");
-            g_forced_split = sp ? atoi(sp) : -1;
+            if (!g_split_mode_set) g_forced_split = sp ? atoi(sp) : -1;
             env_read = true;
         }
     }

@@ -87,11 +87,12 @@ def test_random_shapes_match_fp64_oracle(pb):
     ("1", [(256, 256, 64), (256, 512, 1024), (1024, 2048, 320), (4096, 4096, 256)]),
     # two-CTA kernel, 512 x 256 pair tiles
     ("2", [(256, 512, 64), (512, 512, 1024), (1024, 2048, 320), (4096, 4096, 256), (2048, 8192, 128)]),
-    # the same with the last wave of tiles cut along K over all CTA pairs: one tile cut 74 ways (every pair but one
-    # contributes one or two k-blocks), a few tiles, one full wave plus a cut one, and K not a multiple of the cut
-    ("2+split", [(256, 512, 8192), (1024, 2048, 1024), (4096, 4096, 256), (2048, 8192, 512), (1024, 1024, 4160),
+    # the same with the last wave shared between owners and helper pairs: one tile split in two, a few tiles with one
+    # helper each, one full wave plus a last wave whose helpers take three tails each, K not a multiple of the tile's
+    # k-block count times anything, and a shape too shallow to split (runs unsplit)
+    ("2+split", [(256, 512, 8192), (1024, 2048, 1024), (2048, 8192, 2048), (1024, 1024, 4160), (1024, 8192, 2048),
                  (256, 512, 64)]),
-    ("2-split", [(256, 512, 8192), (4096, 4096, 256)]),
+    ("2-split", [(256, 512, 8192), (2048, 8192, 2048)]),
 ])
 def test_every_kernel_form_forced(mode, shapes):
     """The launcher picks a kernel form by problem size; each form is forced here on small and

@@ -365,8 +365,10 @@ def run_gemm_bf16(args, world, rank, peaks):
     ok = rows_ok(C[n_idx])
 
     # what the kernel sustains: back to back for seconds, clocks sampled over the whole window
-    sustained = sustained_run(lambda: plan(A, B, C), 2.0 * rows * S * S, 2.5, torch.cuda.current_device(),
-                              peaks["bf16_tflops_sustained"])
+    sustained = None
+    if args.sustained_seconds > 0:
+        sustained = sustained_run(lambda: plan(A, B, C), 2.0 * rows * S * S, args.sustained_seconds,
+                                  torch.cuda.current_device(), peaks["bf16_tflops_sustained"])
 
     # end to end through the host-buffer operator: pinned host arrays in, pinned host array out
     link = measure_host_link(dev)
@@ -699,6 +701,8 @@ def main():
     ap.add_argument("--size", type=int, default=0,
                     help="square GEMM size for --workload gemm_bf16/sgemm (default 8192 / 4096); smaller sizes are for profiling")
     ap.add_argument("--scan-log2n", type=int, default=0, help="scan length 2^k (default: 28 on one GPU, 30 sharded)")
+    ap.add_argument("--sustained-seconds", type=float, default=2.5,
+                    help="length of the back-to-back run that measures what the bf16 kernel sustains (0 = skip, e.g. under a profiler)")
     ap.add_argument("--no-extras", action="store_true", help="skip the other two kernel families and the CPU baseline")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup

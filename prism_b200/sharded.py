@@ -272,7 +272,7 @@ class ShardedHostGemmBF16:
             self.h2d_bytes, self.d2h_bytes = self.single.h2d_bytes, self.single.d2h_bytes
             return
         if steps == 0:
-            steps = next((s for s in (4, 2, 1) if N % (s * 512) == 0 and (N // s) % (self.world * 8) == 0), 0)
+            steps = self._pick_steps(N, K)
         if steps < 1 or N % steps or (N // steps) % 128 or (N // steps) % self.world:
             raise ValueError(f"N={N} does not cut into {steps} blocks of a multiple of 128 rows that {self.world} ranks share")
         self.steps = steps
@@ -285,6 +285,22 @@ class ShardedHostGemmBF16:
         self.c = torch.empty((N, self.rows), dtype=torch.bfloat16, device=self.device)
         # upload, gather, kernel, download
         self.lanes = [torch.cuda.Stream(self.device) for _ in range(4)] if self.on_cuda else [None] * 4
+
+    def _pick_steps(self, N: int, K: int) -> int:
+        """As many blocks as keep the kernels hidden behind the uploads: more blocks shorten what is left to do
+        after the last byte has gone up (one block's gather, GEMM and download), but a block's GEMM takes a whole
+        wave of the machine however few tiles it has, so the sum of the GEMMs must stay below the upload time.
+        Rough machine constants (a B200 on PCIe 5): 55 GB/s up, 0.83 us per 64-wide k-block of a 512 x 256 tile,
+        74 CTA pairs."""
+        upload_ms = (self.rows + N // self.world) * K * 2 / 55e6
+        wave_ms = (K / 64) * 0.83e-3
+        for s in (16, 8, 4, 2, 1):
+            if N % (s * 512) or (N // s) % (self.world * 8):
+                continue
+            tiles = max(1, self.rows // 256) * (N // s // 512)
+            if s == 1 or s * wave_ms * -(-tiles // 74) <= 0.7 * upload_ms:
+                return s
+        return 0
 
     def __call__(self, A_host_local: torch.Tensor, B_host: torch.Tensor, C_host_local: torch.Tensor) -> torch.Tensor:
         if self.single is not None:

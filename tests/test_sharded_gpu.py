@@ -53,7 +53,7 @@ for n_small in (3 * world + 1, 4 * (world - 1)):
 # bf16 GEMM from host arrays: every rank uploads its rows of A and 1/world of B, B is completed over NVLink
 Mh, Nh, Kh = 256 * world, 2048, 512
 A, B = O.gemm_bf16_inputs(Mh, Nh, Kh, seed=19)
-op = sharded.ShardedHostGemmBF16(Mh, Nh, Kh, dev)
+op = sharded.ShardedHostGemmBF16(Mh, Nh, Kh, dev, steps=4)
 from prism_b200 import host
 ah = host.pinned_near(dev, (op.rows, Kh), torch.bfloat16); ah.copy_(torch.from_numpy(A[op.lo:op.hi].view(np.int16)).view(torch.bfloat16))
 bh = host.pinned_near(dev, (Nh, Kh), torch.bfloat16); bh.copy_(torch.from_numpy(B.view(np.int16)).view(torch.bfloat16))

@@ -172,7 +172,7 @@ def _gemm_worker(rank, world, port, q):
         def gemm(rows, n, k, a, b_block, c_block):
             c_block.copy_((b_block.double() @ a.double().t()).to(torch.bfloat16))
 
-        op = sharded.ShardedHostGemmBF16(M, N, K, "cpu", gemm=gemm)
+        op = sharded.ShardedHostGemmBF16(M, N, K, "cpu", gemm=gemm, steps=2)
         assert op.steps == 2 and op.block == 512 and op.piece == 512 // world
         # a rank only ever reads its own pieces of B: everything else is poisoned in its host copy
         b_host = torch.full_like(b_all, float("nan"))

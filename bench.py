@@ -42,9 +42,9 @@ SCAN_NG = 1 << 30
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel,
 # from the ncu captures whose summaries sit in the profiles/ folder (None = not captured).
 NCU_TRAFFIC_BYTES = {
-    "gemm_bf16": 1007.4e6,  # 8192^3: 880.4 MB read + 127.0 MB written
-    "sgemm": 640.5e6,       # 4096^3: 579.5 MB read + 61.0 MB written
-    "scan": 1919.3e6,       # 2^28: 4 x the 479.8 MB captured at 2^26
+    "gemm_bf16": 1045.3e6,  # 8192^3: 917.6 MB read + 127.7 MB written
+    "sgemm": 631.5e6,       # 4096^3: 569.1 MB read + 62.3 MB written
+    "scan": 1916.4e6,       # 2^28: 4 x the 479.1 MB captured at 2^26 (an undercount: the last writes are still in L2 when the kernel ends)
 }
 
 

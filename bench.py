@@ -235,7 +235,7 @@ def time_steps(step, steps: int, warmup: int, world: int, reset=None):
 
 
 def measure_host_link(dev, mib: int = 256) -> dict:
-    """Pinned host <-> device copy rates of this GPU's link, each direction alone, best of 3 (GB/s)."""
+    """Pinned host <-> device copy rates of this GPU's link, each direction alone, best of 6 (GB/s)."""
     import torch
     n = mib << 20
     h = torch.empty(n, dtype=torch.uint8).pin_memory()
@@ -243,7 +243,9 @@ def measure_host_link(dev, mib: int = 256) -> dict:
     out = {}
     for name, (dst, src) in (("h2d_gbs", (d, h)), ("d2h_gbs", (h, d))):
         best = float("inf")
-        for _ in range(4):
+        dst.copy_(src, non_blocking=True)      # warm-up: first touch of the pages
+        torch.cuda.synchronize()
+        for _ in range(6):
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
             dst.copy_(src, non_blocking=True)
@@ -253,6 +255,13 @@ def measure_host_link(dev, mib: int = 256) -> dict:
         out[name] = n / (best * 1e-3) / 1e9
     out["sample_mib"] = mib
     return out
+
+
+def host_link(args, dev) -> dict:
+    """The link rates, measured once per run."""
+    if getattr(args, "link", None) is None:
+        args.link = measure_host_link(dev)
+    return args.link
 
 
 def link_fraction(e2e_ms: float, h2d_bytes: float, d2h_bytes: float, link: dict) -> float:
@@ -371,7 +380,7 @@ def run_gemm_bf16(args, world, rank, peaks):
                                   torch.cuda.current_device(), peaks["bf16_tflops_sustained"])
 
     # end to end through the host-buffer operator: pinned host arrays in, pinned host array out
-    link = measure_host_link(dev)
+    link = host_link(args, dev)
     op = sharded.ShardedHostGemmBF16(S, S, S, dev)
     Ah = host.pinned_near(dev, (rows, S), torch.bfloat16); Ah.copy_(A)
     Bh = host.pinned_near(dev, (S, S), torch.bfloat16); Bh.copy_(B)
@@ -461,6 +470,8 @@ def run_sgemm(args, world, rank, peaks, steps=None, warmup=None):
                          "traffic": NCU_TRAFFIC_BYTES["sgemm"] if (S == SGEMM_S and world == 1) else None},
             "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": op.h2d_bytes, "d2h_bytes_per_step": op.d2h_bytes,
+                    "link_gbs": host_link(args, dev),
+                    "frac_of_link": link_fraction(e2e_ms, op.h2d_bytes, op.d2h_bytes, host_link(args, dev)),
                     "pipeline": "%d blocks of rows of M, upload / kernel / download on three streams" % op.blocks},
             "gpu_launches": launches, "clocks": clocks, "rel_error_sampled_rows": err, "spot_check_ok": err <= 1e-5}
 
@@ -500,6 +511,8 @@ def run_scan(args, world, rank, peaks, steps=None, warmup=None):
         e2e_ms = e2e_total / 3
         e2e = {"value": nbytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_ms,
                "h2d_bytes_per_step": op.h2d_bytes, "d2h_bytes_per_step": op.d2h_bytes,
+               "link_gbs": host_link(args, dev),
+               "frac_of_link": link_fraction(e2e_ms, op.h2d_bytes, op.d2h_bytes, host_link(args, dev)),
                "pipeline": "%d blocks chained by their last element, upload / kernel / download on three streams" % op.blocks}
     kernel_ms = sum(per) / len(per)
     achieved = 8.0 * n / (kernel_ms * 1e-3) / 1e9

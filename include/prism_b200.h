@@ -96,6 +96,14 @@ int prism_b200_sgemm(int kernel_id, int M, int N, int K, float alpha,
                      const float* A, const float* B, float beta, float* C,
                      void* stream);
 
+/*
+ * Tile of kernel 5: -1 (default) the launcher picks by the number of tiles (128 x 128; 64 x 128 below half a wave
+ * of those; 64 x 64 below a quarter of a wave), 0 / 1 / 2 forces 128 x 128 / 64 x 128 / 64 x 64.  Every form gives the same bits.
+ * Process-wide; for tests and measurements.  The reference's launcher has one tile per kernel
+ * (evals/4090_sgemm/runner.cu:191-243).
+ */
+int prism_b200_sgemm_tile_mode(int mode);
+
 /* ---- uint32 inclusive scan (single pass, decoupled look-back) ------------- */
 
 /*

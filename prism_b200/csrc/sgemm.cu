@@ -271,9 +271,10 @@ __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wai
 
 // WARPS_M x WARPS_N warps (four in all), each on a 64 x (16 NV) warp tile; NV = 16-byte B vectors
 // per lane per k.  <2, 2, 4>: the 128 x 128 tile.  <1, 4, 2>: a 64 x 128 tile of 64 x 32 warp
-// tiles (8 x 8 outputs per lane, three CTAs per SM) for problems with few tiles.
+// tiles (8 x 8 outputs per lane, three CTAs per SM) and <1, 4, 1>: a 64 x 64 tile of 64 x 16 warp
+// tiles (8 x 4 outputs per lane, five CTAs per SM) for problems with few tiles.
 template <bool PACKED, int WARPS_M, int WARPS_N, int NV>
-__global__ void __launch_bounds__(k5::THREADS, NV == 4 ? 2 : 3)
+__global__ void __launch_bounds__(k5::THREADS, NV == 4 ? 2 : (NV == 2 ? 3 : 5))
 my_sgemm_kernel_5(int M, int N, int K, float alpha, float* A, float* B, float beta, float* C, int num_blocks_N) {
     using namespace k5;
     static_assert(WARPS_M * WARPS_N == WARPS, "four warps");
@@ -457,11 +458,19 @@ int launch_generic(int M, int N, int K, float alpha, const float* A, const float
 
 bool g_k5_scalar = false;  // PRISM_B200_SGEMM_SCALAR=1 selects the plain fmaf form of kernel 5 (same bits, slower)
 bool g_k5_env_read = false;
+int g_k5_tile_mode = -1;   // prism_b200_sgemm_tile_mode: -1 = by shape, 0 / 1 / 2 = 128 x 128 / 64 x 128 / 64 x 64 (tests)
 
 }  // namespace
 }  // namespace prism_b200
 
 using namespace prism_b200;
+
+extern "C" int prism_b200_sgemm_tile_mode(int mode) {
+    if (mode < -1 || mode > 2) return set_error(PRISM_B200_ERR_INVALID_ARGUMENT, "sgemm_tile_mode: -1, 0, 1 or 2");
+    std::lock_guard<std::mutex> lk(g_sgemm_mu);
+    g_k5_tile_mode = mode;
+    return PRISM_B200_OK;
+}
 
 extern "C" int prism_b200_sgemm(int kernel_id, int M, int N, int K, float alpha, const float* A, const float* B,
                                 float beta, float* C, void* stream) {
@@ -520,15 +529,21 @@ extern "C" int prism_b200_sgemm(int kernel_id, int M, int N, int K, float alpha,
                     g_k5_env_read = true;
                 }
             }
-            // Fewer 128 x 128 tiles than half the SMs: halve the tile's height so twice as many SMs work
-            // (same k order per output element, so the same bits; 1024^3: 29 -> 37 TFLOP/s).
+            // Few tiles: a smaller tile puts more SMs, and more warps per SM, to work.  Every form adds the
+            // products of one output element in the same k order, so all give the same bits.
+            //   0  128 x 128   1  64 x 128 (fewer 128 x 128 tiles than half the SMs)   2  64 x 64 (fewer than a quarter)
             const long long tiles = static_cast<long long>(M / k5::BM) * (N / k5::BN);
-            const bool half_height = 2 * tiles <= sm_count();
-            auto kern = half_height
-                            ? (g_k5_scalar ? my_sgemm_kernel_5<false, 1, 4, 2> : my_sgemm_kernel_5<true, 1, 4, 2>)
+            int form = g_k5_tile_mode;
+            // Measured on a B200 (TFLOP/s, 128 x 128 / 64 x 128 / 64 x 64 tiles, single launches): 512^3 4.2 / 6.4 / 7.6,
+            // 768^3 10.8 / 16.8 / 20.6, 1024^3 20.4 / 32.4 / 27.3, 1536^3 48.4 / 47.3 / 38.6, 4096^3 62.4 / 59.8 / 45.0.
+            if (form < 0) form = 4 * tiles <= sm_count() ? 2 : (2 * tiles <= sm_count() ? 1 : 0);
+            void (*kern)(int, int, int, float, float*, float*, float, float*, int) =
+                form == 2   ? (g_k5_scalar ? my_sgemm_kernel_5<false, 1, 4, 1> : my_sgemm_kernel_5<true, 1, 4, 1>)
+                : form == 1 ? (g_k5_scalar ? my_sgemm_kernel_5<false, 1, 4, 2> : my_sgemm_kernel_5<true, 1, 4, 2>)
                             : (g_k5_scalar ? my_sgemm_kernel_5<false, 2, 2, 4> : my_sgemm_kernel_5<true, 2, 2, 4>);
-            const int nbn = N / k5::BN;
-            const long long blocks = (half_height ? 2 : 1) * tiles;
+            const int tile_n = form == 2 ? 64 : 128;
+            const int nbn = N / tile_n;
+            const long long blocks = static_cast<long long>(M / (form == 0 ? 128 : 64)) * nbn;
             kern<<<static_cast<unsigned>(blocks), k5::THREADS, 0, s>>>(
                 M, N, K, alpha, const_cast<float*>(A), const_cast<float*>(B), beta, C, nbn);
         } else {

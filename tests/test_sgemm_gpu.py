@@ -84,16 +84,27 @@ def test_kernel5_scalar_and_packed_fma_agree(pb, monkeypatch):
     assert np.array_equal(outs[0], outs[1])
 
 
-def test_kernel5_both_tile_forms(pb):
-    """Kernel 5 runs 128 x 128 tiles, or 64 x 128 tiles when fewer than half the SMs would get a tile.
-    1152 x 1152 (81 tiles) takes the first form, its top 512 rows alone (36 tiles) the second; both are
-    checked against fp64 and, having the same k order per element, against each other bit for bit."""
+def test_kernel5_every_tile_form(pb):
+    """Kernel 5 runs 128 x 128 tiles, 64 x 128 tiles when fewer than half the SMs would get a tile, and 64 x 64
+    tiles when fewer than a quarter would.  1152 x 1152 (81 tiles of 128 x 128) takes the first form, its top 512 rows
+    (36 tiles) the second and its top 256 rows (18 tiles) the third; all are checked against fp64 and, having the same k
+    order per element, against each other bit for bit.  Then each form is forced on the whole matrix."""
     M, N, K = 1152, 1152, 80
     A, B, C = O.sgemm_inputs(M, N, K, seed=1152)
     big = _run(pb, 5, 1.5, A, B, 0.5, C)
-    small = _run(pb, 5, 1.5, A[:512].copy(), B, 0.5, C[:512].copy())
     assert O.sgemm_rel_error(big, O.sgemm_cpu(1.5, A, B, 0.5, C)) <= O.SGEMM_TOL
-    assert np.array_equal(big[:512], small)
+    for rows in (512, 256):
+        small = _run(pb, 5, 1.5, A[:rows].copy(), B, 0.5, C[:rows].copy())
+        assert np.array_equal(big[:rows], small), rows
+    lib = pb.load()
+    try:
+        for mode in (0, 1, 2):
+            assert lib.prism_b200_sgemm_tile_mode(mode) == 0
+            assert np.array_equal(_run(pb, 5, 1.5, A, B, 0.5, C), big), mode
+        assert lib.prism_b200_sgemm_tile_mode(3) == 1
+        pb.clear_error()
+    finally:
+        lib.prism_b200_sgemm_tile_mode(-1)
 
 
 @pytest.mark.parametrize("k", KERNELS)

@@ -132,13 +132,19 @@ int prism_b200_scan_f32(size_t n, float* x, void* workspace, void* stream);
 
 /*
  * The other flavours of the same kernel (no counterpart in the reference): separate input and
- * output (in == out is allowed, partial overlap is not), inclusive or exclusive, uint32 or fp32
- * adds.  Exclusive: out[0] = 0, out[i] = in[0] + ... + in[i-1].  Same workspace, limits and
- * alignment as prism_b200_scan; flags = 0 with in == out is prism_b200_scan.
+ * output (in == out is allowed, partial overlap is not), inclusive or exclusive, and the element type:
+ * uint32 (default), fp32 adds (PRISM_B200_SCAN_F32) or 64-bit integers with wrap-around adds
+ * (PRISM_B200_SCAN_I64, bit-identical for int64 and uint64; n counts elements, in and out hold 8 n bytes).
+ * Exclusive: out[0] = 0, out[i] = in[0] + ... + in[i-1].  Limits and alignment as for prism_b200_scan;
+ * flags = 0 with in == out is prism_b200_scan.  The 64-bit flavour needs twice the records per element
+ * (its tiles hold 2048 elements): size its workspace with prism_b200_scan_general_workspace_size, which
+ * for the 32-bit flavours returns what prism_b200_scan_workspace_size returns.
  */
 #define PRISM_B200_SCAN_EXCLUSIVE 1
 #define PRISM_B200_SCAN_F32 2
+#define PRISM_B200_SCAN_I64 4
 int prism_b200_scan_general(size_t n, const void* in, void* out, void* workspace, int flags, void* stream);
+int prism_b200_scan_general_workspace_size(size_t n, int flags, size_t* bytes);
 
 /*
  * Sharded scan helpers (no counterpart in the reference, which is single-GPU).

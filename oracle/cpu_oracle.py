@@ -48,6 +48,13 @@ def scan_f32_cpu(x: np.ndarray) -> np.ndarray:
     return np.cumsum(np.ascontiguousarray(x, dtype=np.float32).astype(np.float64))
 
 
+def scan_i64_cpu(x: np.ndarray) -> np.ndarray:
+    """Inclusive prefix sum of 64-bit integers with wrap-around: the reference's loop
+    (evals/4090_scan/scan_harness.cuh:30-36) with a 64-bit accumulator.  The reference scans uint32 only; this
+    is the checker of the library's 64-bit flavour."""
+    return np.cumsum(np.ascontiguousarray(x).view(np.uint64), dtype=np.uint64)
+
+
 def scan_cpu_loop(x: np.ndarray) -> np.ndarray:
     """The same thing as a literal loop (small inputs only); used to pin `scan_cpu`."""
     x = np.ascontiguousarray(x).view(np.uint32)

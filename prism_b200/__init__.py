@@ -136,20 +136,22 @@ def scan_f32_(x: torch.Tensor, workspace: torch.Tensor | None = None) -> torch.T
 
 def scan(x: torch.Tensor, out: torch.Tensor | None = None, exclusive: bool = False,
          workspace: torch.Tensor | None = None) -> torch.Tensor:
-    """Prefix sum of an int32/uint32 or float32 tensor into `out` (a new tensor by default; `out` may be `x`).
-    exclusive=True gives out[i] = x[0] + ... + x[i-1] with out[0] = 0."""
-    _require_cuda("x", x, _SCAN_DTYPES + (torch.float32,))
+    """Prefix sum of an int32/uint32, float32 or int64/uint64 tensor into `out` (a new tensor by default; `out`
+    may be `x`).  Integer adds wrap around.  exclusive=True gives out[i] = x[0] + ... + x[i-1] with out[0] = 0."""
+    _require_cuda("x", x, _SCAN_DTYPES + (torch.float32, torch.int64, torch.uint64))
     if out is None:
         out = torch.empty_like(x)
     _require_cuda("out", out, (x.dtype,))
     if out.numel() != x.numel() or out.device != x.device:
         raise ValueError("out must have the size and device of x")
+    flags = (1 if exclusive else 0) | (2 if x.dtype == torch.float32 else 0) | (4 if x.element_size() == 8 else 0)
+    need = ctypes.c_size_t(0)
+    _lib.check(load().prism_b200_scan_general_workspace_size(x.numel(), flags, ctypes.byref(need)))
     if workspace is None:
-        workspace = scan_workspace(x.numel(), x.device)
+        workspace = torch.empty(need.value, dtype=torch.uint8, device=x.device)
     _require_cuda("workspace", workspace)
-    if workspace.numel() * workspace.element_size() < get_workspace_size(x.numel()):
-        raise ValueError("workspace too small; see get_workspace_size(n)")
-    flags = (1 if exclusive else 0) | (2 if x.dtype == torch.float32 else 0)
+    if workspace.numel() * workspace.element_size() < need.value:
+        raise ValueError("workspace too small; see prism_b200_scan_general_workspace_size")
     with torch.cuda.device(x.device):
         _lib.check(load().prism_b200_scan_general(x.numel(), x.data_ptr(), out.data_ptr(), workspace.data_ptr(), flags,
                                                   _stream(x)))

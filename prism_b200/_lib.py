@@ -36,6 +36,7 @@ SIGNATURES = {
     "prism_b200_scan": (c_int, [c_size_t, c_void_p, c_void_p, c_void_p]),
     "prism_b200_scan_f32": (c_int, [c_size_t, c_void_p, c_void_p, c_void_p]),
     "prism_b200_scan_general": (c_int, [c_size_t, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
+    "prism_b200_scan_general_workspace_size": (c_int, [c_size_t, c_int, POINTER(c_size_t)]),
     "prism_b200_reduce_u32": (c_int, [c_size_t, c_void_p, c_void_p, c_void_p]),
     "prism_b200_scan_seeded": (c_int, [c_size_t, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
     "prism_b200_scan_add_carry": (c_int, [c_size_t, c_void_p, c_void_p, c_int, c_void_p]),

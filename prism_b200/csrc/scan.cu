@@ -42,6 +42,7 @@
 #include "common.cuh"
 
 #include <mutex>
+#include <type_traits>
 
 namespace prism_b200 {
 
@@ -61,12 +62,13 @@ constexpr int kLookbackWarps = 1;               // warp q resolves ring items q,
 constexpr int kThreads = kScanThreads + 32 + 32 * kLookbackWarps;  // + producer warp + look-back warps
 constexpr int kVecs = 4;                        // 16-byte vectors per lane
 constexpr int kTile = kScanThreads * 4 * kVecs; // 4096 elements = 16 KB
-constexpr int kWarpElems = 128 * kVecs;         // contiguous elements per scan warp
 constexpr int kSlots = 4;                       // ring depth: 3 CTAs of 64 KB per SM (3, 5 and 6 measured slower)
 constexpr uint32_t kSentinel = 0xFFFFFFFFu;
 
 constexpr size_t kSlotBytes = static_cast<size_t>(kTile) * 4;
-constexpr size_t kSmemBytes = kSlots * kSlotBytes + 4 * kSlots * 8 /* barriers */ + 3 * kSlots * 4 + 2 * 8 * 4 + 48;
+// slots, 4 barriers per slot, aggregate and prefix per slot and 2 x 8 warp totals (8 bytes each, whatever the
+// element width), tile index per slot, four control words
+constexpr size_t kSmemBytes = kSlots * kSlotBytes + 4 * kSlots * 8 + 2 * kSlots * 8 + 2 * 8 * 8 + kSlots * 4 + 4 * 4;
 
 __device__ __forceinline__ uint64_t ld_desc(const uint64_t* p) {
     uint64_t v;
@@ -83,19 +85,45 @@ __device__ __forceinline__ uint32_t ld_flag(const uint32_t* p) {
     return v;
 }
 
-// Element arithmetic on 32-bit containers: wrap-around uint32 adds, or fp32 adds on the bit patterns
-// (F32).  The all-zero pattern is the identity of both.
-template <bool F32>
-__device__ __forceinline__ uint32_t eadd(uint32_t a, uint32_t b) {
+// Element arithmetic on 32- or 64-bit containers: wrap-around integer adds, or fp32 adds on the bit
+// patterns (F32, 32-bit only).  The all-zero pattern is the identity of each.
+using u64 = unsigned long long;
+template <bool F32, typename E>
+__device__ __forceinline__ E eadd(E a, E b) {
     if constexpr (F32) return __float_as_uint(__fadd_rn(__uint_as_float(a), __uint_as_float(b)));
     else return a + b;
 }
 
-template <bool F32 = false>
-__device__ __forceinline__ uint32_t warp_sum(uint32_t v) {
+template <bool F32 = false, typename E = uint32_t>
+__device__ __forceinline__ E warp_sum(E v) {
 #pragma unroll
-    for (int d = 16; d > 0; d >>= 1) v = eadd<F32>(v, __shfl_xor_sync(0xffffffffu, v, d));
+    for (int d = 16; d > 0; d >>= 1) v = eadd<F32, E>(v, __shfl_xor_sync(0xffffffffu, v, d));
     return v;
+}
+
+// A tile's record.  32-bit values: ONE 64-bit word {state, value}.  64-bit values: TWO such words in the tile's
+// sector, {state, low half} and {state, high half}; each is written and read whole, and a reader takes the pair
+// only when both carry the same state (a word is written once per state, so equal states mean one publication).
+template <typename E>
+__device__ __forceinline__ void rec_publish(uint64_t* rec, uint32_t state, E value) {
+    if constexpr (sizeof(E) == 4) {
+        st_desc(rec, state, value);
+    } else {
+        st_desc(rec, state, static_cast<uint32_t>(value));
+        st_desc(rec + 1, state, static_cast<uint32_t>(value >> 32));
+    }
+}
+template <typename E>
+__device__ __forceinline__ uint32_t rec_read(const uint64_t* rec, E* value) {
+    if constexpr (sizeof(E) == 4) {
+        const uint64_t d = ld_desc(rec);
+        *value = static_cast<uint32_t>(d >> 32);
+        return static_cast<uint32_t>(d);
+    } else {
+        const uint64_t lo = ld_desc(rec), hi = ld_desc(rec + 1);
+        *value = (lo >> 32) | (hi & 0xFFFFFFFF00000000ull);
+        return static_cast<uint32_t>(lo) == static_cast<uint32_t>(hi) ? static_cast<uint32_t>(lo) : kStateInvalid;
+    }
 }
 
 __device__ __forceinline__ void bulk_load_tile(void* dst_smem, const void* src, uint32_t bytes, uint64_t* bar) {
@@ -110,30 +138,29 @@ __device__ __forceinline__ void bulk_load_tile(void* dst_smem, const void* src, 
 // lookback_to_prev_blocks, generated/lookback_to_prev_blocks.cu:8-25, done by a warp
 // instead of a thread and with bounded spins).  *failed is set if a poll ran out or
 // an abort was seen.
-template <bool F32>
-__device__ __forceinline__ uint32_t lookback(uint32_t tile, const uint64_t* desc, const uint32_t* abort_flag,
-                                             unsigned long long limit_ns, bool* failed) {
+template <bool F32, typename E>
+__device__ __forceinline__ E lookback(uint32_t tile, const uint64_t* desc, const uint32_t* abort_flag,
+                                      unsigned long long limit_ns, bool* failed) {
     const int lane = threadIdx.x & 31;
-    uint32_t exclusive = 0;
+    E exclusive = 0;
     long long idx = static_cast<long long>(tile) - 1 - lane;
     *failed = false;
     while (true) {
         // A slot before tile 0 behaves like a finished tile with prefix 0.
-        uint64_t d = kStatePrefix;
+        uint32_t state = kStatePrefix;
+        E value = 0;
         if (idx >= 0) {
             uint32_t polls = 0;
             unsigned long long t0 = 0;
-            d = ld_desc(desc + idx * kRecStride);
-            while (static_cast<uint32_t>(d) == kStateInvalid) {
+            state = rec_read<E>(desc + idx * kRecStride, &value);
+            while (state == kStateInvalid) {
                 if ((++polls & 1023u) == 0u) {
                     if (t0 == 0) t0 = global_timer_ns();
                     if (ld_flag(abort_flag) != 0u || global_timer_ns() - t0 > limit_ns) break;
                 }
-                d = ld_desc(desc + idx * kRecStride);
+                state = rec_read<E>(desc + idx * kRecStride, &value);
             }
         }
-        const uint32_t state = static_cast<uint32_t>(d);
-        const uint32_t value = static_cast<uint32_t>(d >> 32);
         if (!__all_sync(0xffffffffu, state != kStateInvalid)) {
             *failed = true;
             return exclusive;
@@ -141,10 +168,10 @@ __device__ __forceinline__ uint32_t lookback(uint32_t tile, const uint64_t* desc
         const unsigned has_prefix = __ballot_sync(0xffffffffu, state == kStatePrefix);
         if (has_prefix) {
             const int first = __ffs(has_prefix) - 1;  // nearest predecessor with a prefix
-            exclusive = eadd<F32>(exclusive, warp_sum<F32>(lane <= first ? value : 0u));
+            exclusive = eadd<F32, E>(exclusive, warp_sum<F32, E>(lane <= first ? value : E(0)));
             return exclusive;
         }
-        exclusive = eadd<F32>(exclusive, warp_sum<F32>(value));
+        exclusive = eadd<F32, E>(exclusive, warp_sum<F32, E>(value));
         idx -= 32;
     }
 }
@@ -259,33 +286,45 @@ __device__ __forceinline__ uint32_t wait_peer_words(const ShardArgs& sh, volatil
 }
 
 // `src` is read, `x` is written (the same pointer for the in-place entry points).  EXCL shifts the
-// result by one element: out[i] = in[0] + ... + in[i-1], out[0] = the seed.
-template <int SEED, bool F32 = false, bool EXCL = false>
-__device__ __forceinline__ void scan_body(uint32_t n, const uint32_t* src, uint32_t* x, uint32_t* header, uint64_t* desc,
+// result by one element: out[i] = in[0] + ... + in[i-1], out[0] = the seed.  I64: the elements are
+// 64-bit integers (wrap-around adds); a tile is then 2048 elements, still 16 KB, and a 16-byte vector
+// holds two of them.  `n` counts elements.
+template <int SEED, bool F32 = false, bool EXCL = false, bool I64 = false>
+__device__ __forceinline__ void scan_body(uint32_t n, const void* src_v, void* x_v, uint32_t* header, uint64_t* desc,
                                           const void* seed_src, int rank, const ShardArgs* shard = nullptr) {
-    static_assert(!F32 || SEED == kSeedNone, "the sharded forms are uint32 only");
+    static_assert(!(F32 || I64) || SEED == kSeedNone, "the sharded forms are uint32 only");
+    static_assert(!(F32 && I64), "fp32 adds are 32-bit");
+    using E = typename std::conditional<I64, u64, uint32_t>::type;
+    constexpr int EPV = 16 / static_cast<int>(sizeof(E));        // elements per 16-byte vector
+    constexpr uint32_t TILE = kTile * 4 / sizeof(E);             // elements per tile
+    constexpr int CHUNK = 32 * EPV;                              // elements a warp covers with one vector per lane
+    const E* src = static_cast<const E*>(src_v);
+    E* x = static_cast<E*>(x_v);
     // Longest single wait inside this kernel.  The sharded form may be told to wait longer for its peers;
     // every other wait then gets twice that, so that the wait for the peers is the one that gives up first.
     const unsigned long long limit_ns = SEED == kSeedPeers ? 2ull * shard->wait_ns : kWaitLimitNs;
     constexpr int S = kSlots;
     extern __shared__ __align__(128) unsigned char p_smem[];
-    uint32_t* slots = reinterpret_cast<uint32_t*>(p_smem);
+    E* slots = reinterpret_cast<E*>(p_smem);
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(p_smem + S * kSlotBytes);  // tile landed in the slot
     uint64_t* agg_bar = full_bar + S;                                           // phase A done, aggregate known
     uint64_t* pre_bar = agg_bar + S;                                            // exclusive prefix known
     uint64_t* empty_bar = pre_bar + S;                                          // phase B done, slot reusable
-    uint32_t* s_tile = reinterpret_cast<uint32_t*>(empty_bar + S);
-    uint32_t* s_agg = s_tile + S;
-    uint32_t* s_excl = s_agg + S;
-    uint32_t* s_warp_total = s_excl + S;  // [2][8]
-    volatile uint32_t* abort_flag = s_warp_total + 16;
-    volatile uint32_t* s_ctrl = s_warp_total + 17;  // [2]: outcome of thread 0's bounded wait, double-buffered
-    volatile uint32_t* s_end_item = s_warp_total + 19;  // ring item that carried the end-of-work mark
+    u64* s_agg64 = reinterpret_cast<u64*>(empty_bar + S);       // the three value arrays are laid out for 8-byte elements
+    u64* s_excl64 = s_agg64 + S;
+    u64* s_warp_total64 = s_excl64 + S;                          // [2][8]
+    E* s_agg = reinterpret_cast<E*>(s_agg64);
+    E* s_excl = reinterpret_cast<E*>(s_excl64);
+    E* s_warp_total = reinterpret_cast<E*>(s_warp_total64);
+    uint32_t* s_tile = reinterpret_cast<uint32_t*>(s_warp_total64 + 16);
+    volatile uint32_t* abort_flag = s_tile + S;
+    volatile uint32_t* s_ctrl = s_tile + S + 1;      // [2]: outcome of thread 0's bounded wait, double-buffered
+    volatile uint32_t* s_end_item = s_tile + S + 3;  // ring item that carried the end-of-work mark
 
     const int tid = threadIdx.x;
     const int lane = tid & 31;
     const int warp = tid >> 5;
-    const uint32_t tiles = static_cast<uint32_t>((static_cast<unsigned long long>(n) + kTile - 1) / kTile);
+    const uint32_t tiles = static_cast<uint32_t>((static_cast<unsigned long long>(n) + TILE - 1) / TILE);
 
     if (tid == 0) {
         for (int s = 0; s < S; ++s) {
@@ -301,7 +340,9 @@ __device__ __forceinline__ void scan_body(uint32_t n, const uint32_t* src, uint3
     __syncthreads();
 
     if constexpr (SEED == kSeedPeers) {
-        if (shard->phases & kPhaseReduce) reduce_and_publish(n, src, header, *shard, s_tile, s_warp_total);
+        if (shard->phases & kPhaseReduce)
+            reduce_and_publish(n, static_cast<const uint32_t*>(src_v), header, *shard, s_tile,
+                               reinterpret_cast<volatile uint32_t*>(s_warp_total64));
         if (!(shard->phases & kPhaseScan)) return;
         __syncthreads();
     }
@@ -326,13 +367,13 @@ __device__ __forceinline__ void scan_body(uint32_t n, const uint32_t* src, uint3
                     break;
                 }
                 s_tile[s] = t;
-                const unsigned long long base = static_cast<unsigned long long>(t) * kTile;
+                const unsigned long long base = static_cast<unsigned long long>(t) * TILE;
                 const unsigned long long left = n - base;
-                const uint32_t cnt = left < kTile ? static_cast<uint32_t>(left) : kTile;
-                const uint32_t bytes = (cnt * 4u) & ~15u;  // whole 16-byte vectors; a ragged end is read by its owner
+                const uint32_t cnt = left < TILE ? static_cast<uint32_t>(left) : TILE;
+                const uint32_t bytes = (cnt * static_cast<uint32_t>(sizeof(E))) & ~15u;  // whole 16-byte vectors; a ragged end is read by its owner
                 if (bytes) {
                     mbar_arrive_expect_tx(&full_bar[s], bytes);
-                    bulk_load_tile(slots + s * kTile, src + base, bytes, &full_bar[s]);
+                    bulk_load_tile(slots + s * TILE, src + base, bytes, &full_bar[s]);
                 } else {
                     mbar_arrive(&full_bar[s]);
                 }
@@ -369,18 +410,18 @@ __device__ __forceinline__ void scan_body(uint32_t n, const uint32_t* src, uint3
             }
             if (k >= *s_end_item) break;   // the work ended before this ring item
             const uint32_t t = s_tile[s];
-            const uint32_t agg = s_agg[s];
-            uint32_t exclusive = 0;
+            const E agg = s_agg[s];
+            E exclusive = 0;
             bool failed = false;
             if (t == 0) {
-                if (SEED == kSeedTotals) {
+                if constexpr (SEED == kSeedTotals) {
                     const uint32_t* totals = static_cast<const uint32_t*>(seed_src);
                     for (int r = 0; r < rank; ++r) exclusive += totals[r];
-                } else if (SEED == kSeedPeers) {
+                } else if constexpr (SEED == kSeedPeers) {
                     exclusive = wait_peer_words(*shard, abort_flag, &failed);
                 }
             } else {
-                exclusive = lookback<F32>(t, desc, header + 1, limit_ns, &failed);
+                exclusive = lookback<F32, E>(t, desc, header + 1, limit_ns, &failed);
             }
             if (lane == 0) {
                 if (failed) {
@@ -388,7 +429,7 @@ __device__ __forceinline__ void scan_body(uint32_t n, const uint32_t* src, uint3
                     atomicExch(header + 1, 1u);
                     raise_device_status(DEV_SCAN_LOOKBACK_TIMEOUT);
                 }
-                st_desc(desc + static_cast<size_t>(t) * kRecStride, kStatePrefix, eadd<F32>(exclusive, agg));  // as write_block_prefix.cu:8-10
+                rec_publish<E>(desc + static_cast<size_t>(t) * kRecStride, kStatePrefix, eadd<F32, E>(exclusive, agg));  // as write_block_prefix.cu:8-10
                 s_excl[s] = exclusive;
                 mbar_arrive(&pre_bar[s]);
             }
@@ -400,8 +441,8 @@ __device__ __forceinline__ void scan_body(uint32_t n, const uint32_t* src, uint3
 
     // ------------------------------ scan warps ------------------------------
     // Lane l of warp w owns the 16-byte vectors at tile-local elements
-    // w * 512 + q * 128 + l * 4 (q = 0..3), in phase A and again in phase B.
-    const int vec0 = warp * kWarpElems + lane * 4;
+    // w * kVecs * CHUNK + q * CHUNK + l * EPV (q = 0..3), in phase A and again in phase B.
+    const int vec0 = warp * (kVecs * CHUNK) + lane * EPV;
     uint32_t i = 0, j = 0;  // ring items taken through phase A / phase B so far
     bool drained = false;
     // Scheduling.  Phase A (which publishes the aggregate that every later tile waits for) runs as
@@ -437,6 +478,22 @@ __device__ __forceinline__ void scan_body(uint32_t n, const uint32_t* src, uint3
         asm volatile("bar.sync 1, %0;" ::"n"(kScanThreads) : "memory");
         return *c;
     };
+    // A 16-byte vector as EPV elements and back.
+    auto unpack = [](const uint4& v, E (&e)[EPV]) {
+        if constexpr (I64) {
+            e[0] = static_cast<u64>(v.x) | (static_cast<u64>(v.y) << 32);
+            e[1] = static_cast<u64>(v.z) | (static_cast<u64>(v.w) << 32);
+        } else {
+            e[0] = v.x; e[1] = v.y; e[2] = v.z; e[3] = v.w;
+        }
+    };
+    auto pack = [](const E (&e)[EPV]) -> uint4 {
+        if constexpr (I64)
+            return make_uint4(static_cast<uint32_t>(e[0]), static_cast<uint32_t>(e[0] >> 32), static_cast<uint32_t>(e[1]),
+                              static_cast<uint32_t>(e[1] >> 32));
+        else
+            return make_uint4(e[0], e[1], e[2], e[3]);
+    };
 
     while (true) {
         const uint32_t what = decide();
@@ -455,80 +512,78 @@ __device__ __forceinline__ void scan_body(uint32_t n, const uint32_t* src, uint3
                 }
                 continue;
             }
-            uint32_t* slot = slots + s * kTile;
-            const unsigned long long base = static_cast<unsigned long long>(t) * kTile;
+            E* slot = slots + s * TILE;
+            const unsigned long long base = static_cast<unsigned long long>(t) * TILE;
             const unsigned long long left = n - base;
-            const uint32_t cnt = left < kTile ? static_cast<uint32_t>(left) : kTile;
-            uint4 v[kVecs];
+            const uint32_t cnt = left < TILE ? static_cast<uint32_t>(left) : TILE;
+            E v[kVecs][EPV];
 #pragma unroll
             for (int q = 0; q < kVecs; ++q) {
-                const uint32_t e = vec0 + q * 128;
-                if (e + 4 <= (cnt & ~3u)) {
-                    v[q] = *reinterpret_cast<const uint4*>(slot + e);
+                const uint32_t e = vec0 + q * CHUNK;
+                if (e + EPV <= (cnt & ~static_cast<uint32_t>(EPV - 1))) {
+                    unpack(*reinterpret_cast<const uint4*>(slot + e), v[q]);
                 } else {  // the ragged end of the last tile: straight from global memory, zero beyond n
-                    v[q].x = (e + 0 < cnt) ? src[base + e + 0] : 0u;
-                    v[q].y = (e + 1 < cnt) ? src[base + e + 1] : 0u;
-                    v[q].z = (e + 2 < cnt) ? src[base + e + 2] : 0u;
-                    v[q].w = (e + 3 < cnt) ? src[base + e + 3] : 0u;
+#pragma unroll
+                    for (int k = 0; k < EPV; ++k) v[q][k] = (e + k < cnt) ? src[base + e + k] : E(0);
                 }
             }
             // Inside each 16-byte group, then across the 32 lanes of each of the four chunks
             // (the work of scan_warps.cu / naive_scan_warp_ends.cu in the reference).
-            uint32_t sum[kVecs], inc[kVecs];
+            E sum[kVecs], inc[kVecs];
 #pragma unroll
             for (int q = 0; q < kVecs; ++q) {
-                v[q].y = eadd<F32>(v[q].y, v[q].x);
-                v[q].z = eadd<F32>(v[q].z, v[q].y);
-                v[q].w = eadd<F32>(v[q].w, v[q].z);
-                sum[q] = v[q].w;
+#pragma unroll
+                for (int k = 1; k < EPV; ++k) v[q][k] = eadd<F32, E>(v[q][k], v[q][k - 1]);
+                sum[q] = v[q][EPV - 1];
                 inc[q] = sum[q];
             }
 #pragma unroll
             for (int d = 1; d < 32; d <<= 1) {
 #pragma unroll
                 for (int q = 0; q < kVecs; ++q) {
-                    const uint32_t up = __shfl_up_sync(0xffffffffu, inc[q], d);
-                    if (lane >= d) inc[q] = eadd<F32>(inc[q], up);
+                    const E up = __shfl_up_sync(0xffffffffu, inc[q], d);
+                    if (lane >= d) inc[q] = eadd<F32, E>(inc[q], up);
                 }
             }
-            uint32_t chunk_off = 0, excl[kVecs];
+            E chunk_off = 0, excl[kVecs];
 #pragma unroll
             for (int q = 0; q < kVecs; ++q) {
                 if constexpr (F32) {   // no subtraction in floating point: the lane below's inclusive value
-                    const uint32_t below = __shfl_up_sync(0xffffffffu, inc[q], 1);
-                    excl[q] = eadd<F32>(chunk_off, lane == 0 ? 0u : below);
+                    const E below = __shfl_up_sync(0xffffffffu, inc[q], 1);
+                    excl[q] = eadd<F32, E>(chunk_off, lane == 0 ? E(0) : below);
                 } else {
                     excl[q] = chunk_off + inc[q] - sum[q];
                 }
-                chunk_off = eadd<F32>(chunk_off, __shfl_sync(0xffffffffu, inc[q], 31));
+                chunk_off = eadd<F32, E>(chunk_off, __shfl_sync(0xffffffffu, inc[q], 31));
             }
-            uint32_t* wt = s_warp_total + (i & 1u) * 8;
+            E* wt = s_warp_total + (i & 1u) * 8;
             if (lane == 0) wt[warp] = chunk_off;
             asm volatile("bar.sync 1, %0;" ::"n"(kScanThreads) : "memory");
-            uint32_t warp_off = 0, aggregate = 0;
+            E warp_off = 0, aggregate = 0;
 #pragma unroll
             for (int w = 0; w < kScanThreads / 32; ++w) {
-                const uint32_t tot = wt[w];
-                if (w < warp) warp_off = eadd<F32>(warp_off, tot);
-                aggregate = eadd<F32>(aggregate, tot);
+                const E tot = wt[w];
+                if (w < warp) warp_off = eadd<F32, E>(warp_off, tot);
+                aggregate = eadd<F32, E>(aggregate, tot);
             }
             if (tid == 0) {
-                if (t != 0) st_desc(desc + static_cast<size_t>(t) * kRecStride, kStateAggregate, aggregate);  // as write_block_aggregate.cu:8-10
+                if (t != 0) rec_publish<E>(desc + static_cast<size_t>(t) * kRecStride, kStateAggregate, aggregate);  // as write_block_aggregate.cu:8-10
                 s_agg[s] = aggregate;
                 mbar_arrive(&agg_bar[s]);
             }
             // Tile-local inclusive scan back into the slot; the same lane reads it again in phase B.
 #pragma unroll
             for (int q = 0; q < kVecs; ++q) {
-                const uint32_t a = eadd<F32>(warp_off, excl[q]);
+                const E a = eadd<F32, E>(warp_off, excl[q]);
                 if constexpr (EXCL) {   // each element gets the sum of the ones before it
-                    v[q].w = eadd<F32>(v[q].z, a); v[q].z = eadd<F32>(v[q].y, a);
-                    v[q].y = eadd<F32>(v[q].x, a); v[q].x = a;
+#pragma unroll
+                    for (int k = EPV - 1; k > 0; --k) v[q][k] = eadd<F32, E>(v[q][k - 1], a);
+                    v[q][0] = a;
                 } else {
-                    v[q].x = eadd<F32>(v[q].x, a); v[q].y = eadd<F32>(v[q].y, a);
-                    v[q].z = eadd<F32>(v[q].z, a); v[q].w = eadd<F32>(v[q].w, a);
+#pragma unroll
+                    for (int k = 0; k < EPV; ++k) v[q][k] = eadd<F32, E>(v[q][k], a);
                 }
-                *reinterpret_cast<uint4*>(slot + vec0 + q * 128) = v[q];
+                *reinterpret_cast<uint4*>(slot + vec0 + q * CHUNK) = pack(v[q]);
             }
             ++i;
         } else {
@@ -536,24 +591,24 @@ __device__ __forceinline__ void scan_body(uint32_t n, const uint32_t* src, uint3
             const int s = j % S;
             (void)mbar_try_wait(&pre_bar[s], (j / S) & 1u);
             const uint32_t t = s_tile[s];
-            const uint32_t add = s_excl[s];
-            const uint32_t* slot = slots + s * kTile;
-            const unsigned long long base = static_cast<unsigned long long>(t) * kTile;
+            const E add = s_excl[s];
+            const E* slot = slots + s * TILE;
+            const unsigned long long base = static_cast<unsigned long long>(t) * TILE;
             const unsigned long long left = n - base;
-            const uint32_t cnt = left < kTile ? static_cast<uint32_t>(left) : kTile;
+            const uint32_t cnt = left < TILE ? static_cast<uint32_t>(left) : TILE;
 #pragma unroll
             for (int q = 0; q < kVecs; ++q) {
-                const uint32_t e = vec0 + q * 128;
-                uint4 v = *reinterpret_cast<const uint4*>(slot + e);
-                v.x = eadd<F32>(v.x, add); v.y = eadd<F32>(v.y, add);
-                v.z = eadd<F32>(v.z, add); v.w = eadd<F32>(v.w, add);
-                if (e + 4 <= cnt) {
-                    __stcg(reinterpret_cast<uint4*>(x + base + e), v);
+                const uint32_t e = vec0 + q * CHUNK;
+                E v[EPV];
+                unpack(*reinterpret_cast<const uint4*>(slot + e), v);
+#pragma unroll
+                for (int k = 0; k < EPV; ++k) v[k] = eadd<F32, E>(v[k], add);
+                if (e + EPV <= cnt) {
+                    __stcg(reinterpret_cast<uint4*>(x + base + e), pack(v));
                 } else {
-                    if (e + 0 < cnt) x[base + e + 0] = v.x;
-                    if (e + 1 < cnt) x[base + e + 1] = v.y;
-                    if (e + 2 < cnt) x[base + e + 2] = v.z;
-                    if (e + 3 < cnt) x[base + e + 3] = v.w;
+#pragma unroll
+                    for (int k = 0; k < EPV; ++k)
+                        if (e + k < cnt) x[base + e + k] = v[k];
                 }
             }
             // The slot was written with ordinary stores; the next write comes from the bulk-copy engine.
@@ -592,6 +647,15 @@ template <bool F32, bool EXCL>
 __global__ void __launch_bounds__(kThreads, kCtasPerSm)
 scan_kernel_general(uint32_t n, const uint32_t* in, uint32_t* out, uint32_t* block_idx_counter, int* block_infos) {
     scan_body<kSeedNone, F32, EXCL>(n, in, out, block_idx_counter, reinterpret_cast<uint64_t*>(block_infos), nullptr, 0);
+}
+
+// 64-bit integer flavour (no counterpart in the reference, whose scan is uint32 only): the same pipeline on
+// 2048-element tiles, a tile's record split over two 64-bit words.
+template <bool EXCL>
+__global__ void __launch_bounds__(kThreads, kCtasPerSm)
+scan_kernel_i64(uint32_t n, const unsigned long long* in, unsigned long long* out, uint32_t* block_idx_counter,
+                int* block_infos) {
+    scan_body<kSeedNone, false, EXCL, true>(n, in, out, block_idx_counter, reinterpret_cast<uint64_t*>(block_infos), nullptr, 0);
 }
 
 // Sharded form: tile 0 starts from totals[0] + ... + totals[rank-1].
@@ -670,7 +734,11 @@ __global__ void __launch_bounds__(256) add_carry_kernel(size_t n, uint32_t* x, c
 
 namespace {
 
-size_t scan_tiles(size_t n) { return (n + kTile - 1) / kTile; }
+// Tiles of n elements of elem_bytes (4 or 8) each: a tile is always 16 KB.
+size_t scan_tiles(size_t n, size_t elem_bytes = 4) {
+    const size_t per_tile = kSlotBytes / elem_bytes;
+    return (n + per_tile - 1) / per_tile;
+}
 
 // Resident CTAs of the persistent kernel on the current device (SMs x CTAs per SM), found
 // once per device; also raises the kernels' dynamic shared-memory limit.
@@ -700,6 +768,10 @@ int persistent_grid(unsigned* out) {
     PRISM_CUDA_TRY(cudaFuncSetAttribute(scan_kernel_general<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         static_cast<int>(kSmemBytes)));
     PRISM_CUDA_TRY(cudaFuncSetAttribute(scan_kernel_general<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        static_cast<int>(kSmemBytes)));
+    PRISM_CUDA_TRY(cudaFuncSetAttribute(scan_kernel_i64<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        static_cast<int>(kSmemBytes)));
+    PRISM_CUDA_TRY(cudaFuncSetAttribute(scan_kernel_i64<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         static_cast<int>(kSmemBytes)));
     PRISM_CUDA_TRY(cudaFuncSetAttribute(scan_kernel_sharded, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         static_cast<int>(kSmemBytes)));
@@ -776,21 +848,24 @@ int scan_sharded_launch(size_t n, uint32_t* x, void* workspace, const uint64_t* 
 }
 
 // The general flavour: same re-arming and grid as scan_enqueue.
-int scan_general_launch(size_t n, const uint32_t* in, uint32_t* out, void* workspace, int flags, cudaStream_t stream) {
-    if (flags & ~(PRISM_B200_SCAN_EXCLUSIVE | PRISM_B200_SCAN_F32))
+int scan_general_launch(size_t n, const void* in, void* out, void* workspace, int flags, cudaStream_t stream) {
+    if (flags & ~(PRISM_B200_SCAN_EXCLUSIVE | PRISM_B200_SCAN_F32 | PRISM_B200_SCAN_I64))
         return set_error(PRISM_B200_ERR_INVALID_ARGUMENT, "scan_general: unknown flag bits 0x%x", flags);
+    if ((flags & PRISM_B200_SCAN_F32) && (flags & PRISM_B200_SCAN_I64))
+        return set_error(PRISM_B200_ERR_INVALID_ARGUMENT, "scan_general: F32 and I64 exclude each other");
     if (n == 0) return PRISM_B200_OK;
     if (!in || !out || !workspace) return set_error(PRISM_B200_ERR_INVALID_ARGUMENT, "scan_general: null pointer");
     if (n >= (1ull << 32)) return set_error(PRISM_B200_ERR_TOO_LARGE, "scan_general: n=%zu must be below 2^32", n);
     if ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(workspace)) & 15u)
         return set_error(PRISM_B200_ERR_MISALIGNED, "scan_general: in, out and workspace must be 16-byte aligned");
+    const size_t elem = (flags & PRISM_B200_SCAN_I64) ? 8 : 4;
     if (in != out) {
         const uintptr_t a = reinterpret_cast<uintptr_t>(in), b = reinterpret_cast<uintptr_t>(out);
-        if (a < b + n * 4 && b < a + n * 4)
+        if (a < b + n * elem && b < a + n * elem)
             return set_error(PRISM_B200_ERR_INVALID_ARGUMENT, "scan_general: in and out overlap without being equal");
     }
     if (int rc = bind_status_word()) return rc;
-    const uint32_t tiles = static_cast<uint32_t>(scan_tiles(n));
+    const uint32_t tiles = static_cast<uint32_t>(scan_tiles(n, elem));
     uint32_t* header = static_cast<uint32_t*>(workspace);
     int* desc = reinterpret_cast<int*>(static_cast<char*>(workspace) + kHeaderBytes);
     unsigned grid = 0;
@@ -798,11 +873,17 @@ int scan_general_launch(size_t n, const uint32_t* in, uint32_t* out, void* works
     if (grid > tiles) grid = tiles;
     PRISM_CUDA_TRY(cudaMemsetAsync(workspace, 0, kHeaderBytes + static_cast<size_t>(tiles) * kRecStride * sizeof(uint64_t), stream));
     const uint32_t n32 = static_cast<uint32_t>(n);
+    const uint32_t* in32 = static_cast<const uint32_t*>(in);
+    uint32_t* out32 = static_cast<uint32_t*>(out);
+    const unsigned long long* in64 = static_cast<const unsigned long long*>(in);
+    unsigned long long* out64 = static_cast<unsigned long long*>(out);
     switch (flags) {
-    case 0: scan_kernel_general<false, false><<<grid, kThreads, kSmemBytes, stream>>>(n32, in, out, header, desc); break;
-    case PRISM_B200_SCAN_EXCLUSIVE: scan_kernel_general<false, true><<<grid, kThreads, kSmemBytes, stream>>>(n32, in, out, header, desc); break;
-    case PRISM_B200_SCAN_F32: scan_kernel_general<true, false><<<grid, kThreads, kSmemBytes, stream>>>(n32, in, out, header, desc); break;
-    default: scan_kernel_general<true, true><<<grid, kThreads, kSmemBytes, stream>>>(n32, in, out, header, desc); break;
+    case 0: scan_kernel_general<false, false><<<grid, kThreads, kSmemBytes, stream>>>(n32, in32, out32, header, desc); break;
+    case PRISM_B200_SCAN_EXCLUSIVE: scan_kernel_general<false, true><<<grid, kThreads, kSmemBytes, stream>>>(n32, in32, out32, header, desc); break;
+    case PRISM_B200_SCAN_F32: scan_kernel_general<true, false><<<grid, kThreads, kSmemBytes, stream>>>(n32, in32, out32, header, desc); break;
+    case PRISM_B200_SCAN_F32 | PRISM_B200_SCAN_EXCLUSIVE: scan_kernel_general<true, true><<<grid, kThreads, kSmemBytes, stream>>>(n32, in32, out32, header, desc); break;
+    case PRISM_B200_SCAN_I64: scan_kernel_i64<false><<<grid, kThreads, kSmemBytes, stream>>>(n32, in64, out64, header, desc); break;
+    default: scan_kernel_i64<true><<<grid, kThreads, kSmemBytes, stream>>>(n32, in64, out64, header, desc); break;
     }
     PRISM_CUDA_TRY(cudaGetLastError());
     count_launch();
@@ -905,8 +986,14 @@ extern "C" int prism_b200_scan_f32(size_t n, float* x, void* workspace, void* st
 }
 
 extern "C" int prism_b200_scan_general(size_t n, const void* in, void* out, void* workspace, int flags, void* stream) {
-    return scan_general_launch(n, static_cast<const uint32_t*>(in), static_cast<uint32_t*>(out), workspace, flags,
-                               static_cast<cudaStream_t>(stream));
+    return scan_general_launch(n, in, out, workspace, flags, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int prism_b200_scan_general_workspace_size(size_t n, int flags, size_t* bytes) {
+    if (!bytes) return set_error(PRISM_B200_ERR_INVALID_ARGUMENT, "scan_general_workspace_size: null bytes");
+    if (n >= (1ull << 32)) return set_error(PRISM_B200_ERR_TOO_LARGE, "scan: n=%zu must be below 2^32", n);
+    *bytes = kHeaderBytes + scan_tiles(n, (flags & PRISM_B200_SCAN_I64) ? 8 : 4) * kRecStride * sizeof(uint64_t);
+    return PRISM_B200_OK;
 }
 
 extern "C" int prism_b200_scan_seeded(size_t n, uint32_t* x, void* workspace, const uint32_t* totals, int rank,

@@ -207,6 +207,50 @@ def test_scan_general_f32_exclusive(pb):
     assert np.array_equal(out.cpu().numpy().astype(np.float64), want)
 
 
+@pytest.mark.parametrize("n", [1, 2, 3, 2047, 2048, 2049, 100003, (1 << 22) + 1])
+@pytest.mark.parametrize("exclusive", [False, True])
+def test_scan_int64(pb, n, exclusive):
+    """64-bit integer flavour (2048-element tiles, a record in two words): full-range values, so that sums wrap
+    around 2^64 and both halves of every record matter; bit-exact against the oracle, out of place and in place."""
+    rng = np.random.default_rng(n * 2 + exclusive)
+    x = rng.integers(0, 1 << 64, n, dtype=np.uint64)
+    inc = O.scan_i64_cpu(x)
+    want = np.concatenate([np.zeros(1, np.uint64), inc[:-1]]) if exclusive else inc
+    t = torch.from_numpy(x.view(np.int64).copy()).to(DEV)
+    out = pb.scan(t, exclusive=exclusive)
+    torch.cuda.synchronize()
+    assert np.array_equal(out.cpu().numpy().view(np.uint64), want)
+    assert np.array_equal(t.cpu().numpy().view(np.uint64), x)
+    pb.scan(t, out=t, exclusive=exclusive)
+    torch.cuda.synchronize()
+    assert np.array_equal(t.cpu().numpy().view(np.uint64), want)
+
+
+def test_scan_int64_large_with_carries_between_the_halves(pb):
+    """2^26 elements just below 2^32 each: the running sum crosses 2^32 every element or two, so the low half of a
+    tile's record overflows into the high half all the time; checked completely."""
+    n = 1 << 26
+    g = torch.Generator(device=DEV).manual_seed(64)
+    x = torch.randint((1 << 32) - (1 << 20), 1 << 32, (n,), dtype=torch.int64, device=DEV, generator=g)
+    out = pb.scan(x)
+    torch.cuda.synchronize()
+    assert torch.equal(out, torch.cumsum(x, 0))
+
+
+def test_scan_int64_workspace_is_twice_the_uint32_one(pb):
+    import ctypes
+    import prism_b200._lib as L
+    lib = L.load()
+    a, b = ctypes.c_size_t(0), ctypes.c_size_t(0)
+    assert lib.prism_b200_scan_general_workspace_size(1 << 20, 0, ctypes.byref(a)) == 0
+    assert lib.prism_b200_scan_general_workspace_size(1 << 20, 4, ctypes.byref(b)) == 0
+    assert a.value == pb.get_workspace_size(1 << 20) and b.value - 128 == 2 * (a.value - 128)
+    x = torch.zeros(16, dtype=torch.int64, device=DEV)
+    ws = torch.empty(b.value, dtype=torch.uint8, device=DEV)
+    assert lib.prism_b200_scan_general(16, x.data_ptr(), x.data_ptr(), ws.data_ptr(), 2 | 4, None) == 1   # F32 and I64
+    pb.clear_error()
+
+
 def test_scan_general_rejects_partial_overlap(pb):
     buf = torch.zeros(4096 + 8, dtype=torch.int32, device=DEV)
     ws = pb.scan_workspace(4096, DEV)

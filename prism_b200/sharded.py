@@ -252,9 +252,15 @@ class ShardedHostGemmBF16:
     launches and copies everything out on one GPU (evals/h100_bench/main.cu:105-130).
     """
 
-    def __init__(self, M: int, N: int, K: int, device, group: Any = None, steps: int = 0, gemm: Any = None):
+    def __init__(self, M: int, N: int, K: int, device, group: Any = None, steps: int = 0, gemm: Any = None,
+                 overlap_download: bool | None = None):
         """`gemm(rows, n, K, A, B_block, C_block)` replaces the kernel call; the tests of the host-side
-        logic pass a CPU stand-in together with device="cpu" (then there are no streams either)."""
+        logic pass a CPU stand-in together with device="cpu" (then there are no streams either).
+        `overlap_download`: send blocks of C back while later blocks of B still go up (True), or only after the
+        last upload (False).  Default: overlap on one or two GPUs only -- with more GPUs on one host, copies in
+        both directions at once share the host's memory system and slow each other down by more than the overlap
+        gains (measured on a 4-GPU box: 55 GB/s up and 36-45 GB/s down per GPU when all copy one way, 38 and 23
+        when the directions mix)."""
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -265,6 +271,7 @@ class ShardedHostGemmBF16:
         self.rows = self.hi - self.lo
         self.single = None
         self._gemm = gemm
+        self.overlap_download = (self.world <= 2) if overlap_download is None else bool(overlap_download)
         if self.world == 1 and gemm is None:
             from . import host
             self.single = host.HostGemmBF16(M, N, K, self.device)
@@ -326,6 +333,7 @@ class ShardedHostGemmBF16:
         for s in self.lanes:
             wait(s, begin)
         a_done = event()
+        all_up = event()
         for i in range(self.steps):
             lo = i * self.block
             mine = slice(lo + self.rank * self.piece, lo + (self.rank + 1) * self.piece)
@@ -336,6 +344,10 @@ class ShardedHostGemmBF16:
                 if i == 0:          # A goes up while the first block is being gathered
                     self.a.copy_(A_host_local, non_blocking=True)
                     record(a_done, up)
+                if i == self.steps - 1:
+                    record(all_up, up)
+                    if not self.overlap_download:
+                        wait(down, all_up)   # the download stream was idle until here: nothing of C has gone back yet
             with on(gather):
                 wait(gather, uploaded)
                 # On the GPU in place: this rank's piece already sits at its position in the block.
@@ -349,9 +361,12 @@ class ShardedHostGemmBF16:
                     wait(kernel, a_done)
                 gemm(self.rows, self.block, self.K, self.a, self.b[lo:lo + self.block], self.c[lo:lo + self.block])
                 record(computed, kernel)
-            with on(down):
-                wait(down, computed)
-                C_host_local[lo:lo + self.block].copy_(self.c[lo:lo + self.block], non_blocking=True)
+            if self.overlap_download or i == self.steps - 1:
+                first = i if self.overlap_download else 0
+                with on(down):
+                    wait(down, computed)
+                    lo_d = first * self.block
+                    C_host_local[lo_d:lo + self.block].copy_(self.c[lo_d:lo + self.block], non_blocking=True)
         for s in self.lanes:
             done = event()
             record(done, s)

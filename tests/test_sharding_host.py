@@ -183,6 +183,11 @@ def _gemm_worker(rank, world, port, q):
         op(a_all[op.lo:op.hi].contiguous(), b_host, c_host)
         ref = O.gemm_bf16_cpu(A[op.lo:op.hi], B)
         ok, worst = O.gemm_bf16_check(c_host.view(torch.int16).numpy().view(np.uint16), ref)
+        # the same with C sent back in one piece after the last upload
+        late = sharded.ShardedHostGemmBF16(M, N, K, "cpu", gemm=gemm, steps=2, overlap_download=False)
+        c_late = torch.full((N, op.rows), float("nan"), dtype=torch.bfloat16)
+        late(a_all[op.lo:op.hi].contiguous(), b_host, c_late)
+        ok = ok and torch.equal(c_late, c_host)
         q.put((rank, ok, worst, op.h2d_bytes, op.d2h_bytes))
     finally:
         dist.destroy_process_group()

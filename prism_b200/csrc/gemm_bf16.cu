@@ -1229,7 +1229,6 @@ int launch_gemm_axpby(int dev, int sms, int M, int N, int K, float alpha, const 
 }
 
 using PairKernel = void (*)(int, int, int, __nv_bfloat16*, const CUtensorMap, const CUtensorMap);
-using PairSplitKernel = void (*)(int, int, int, __nv_bfloat16*, const CUtensorMap, const CUtensorMap, const SplitArgs);
 
 std::mutex g_launch_mu;   // guards the per-device caches below; entry points may be called from several host threads
 

@@ -213,8 +213,10 @@ def max_over_ranks(value: float, world: int) -> float:
     return float(t.item())
 
 
-def time_steps(step, steps: int, warmup: int, world: int, reset=None):
-    """Per-step CUDA-event timing on the current stream; returns (total_ms_max_over_ranks, per_step_ms list)."""
+def time_steps(step, steps: int, warmup: int, world: int, reset=None, wait_for_result: bool = False):
+    """Per-step CUDA-event timing on the current stream; returns (total_ms_max_over_ranks, per_step_ms list).
+    wait_for_result: the host waits for each step to finish before it issues the next, as a caller does who
+    reads the step's result from host memory (the end-to-end measurements)."""
     import torch
     for _ in range(warmup):
         if reset:
@@ -229,6 +231,8 @@ def time_steps(step, steps: int, warmup: int, world: int, reset=None):
         starts[i].record()
         step()
         ends[i].record()
+        if wait_for_result:
+            ends[i].synchronize()
     barrier(world)
     per = [s.elapsed_time(e) for s, e in zip(starts, ends)]
     return max_over_ranks(sum(per), world), per
@@ -386,7 +390,7 @@ def run_gemm_bf16(args, world, rank, peaks):
     Bh = host.pinned_near(dev, (S, S), torch.bfloat16); Bh.copy_(B)
     Ch = host.pinned_near(dev, (S, rows), torch.bfloat16)
     e2e_steps = max(3, min(args.steps, 5))
-    e2e_total, _ = time_steps(lambda: op(Ah, Bh, Ch), e2e_steps, 2, world)
+    e2e_total, _ = time_steps(lambda: op(Ah, Bh, Ch), e2e_steps, 2, world, wait_for_result=True)
     e2e_ms = e2e_total / e2e_steps
     torch.cuda.synchronize()
     e2e_ok = rows_ok(Ch[n_idx].to(dev))
@@ -451,7 +455,7 @@ def run_sgemm(args, world, rank, peaks, steps=None, warmup=None):
     op = host.HostSgemm(rows, S, S, dev)
     Ah, Bh, Ch = A.cpu().pin_memory(), B.cpu().pin_memory(), C0.cpu().pin_memory()
     e2e_steps = 3
-    e2e_total, _ = time_steps(lambda: op(1.5, Ah, Bh, 0.5, Ch), e2e_steps, 1, world)
+    e2e_total, _ = time_steps(lambda: op(1.5, Ah, Bh, 0.5, Ch), e2e_steps, 1, world, wait_for_result=True)
     e2e_ms = e2e_total / e2e_steps
 
     kernel_ms = sum(per) / len(per)
@@ -507,7 +511,7 @@ def run_scan(args, world, rank, peaks, steps=None, warmup=None):
     if world == 1:
         op = host.HostScan(n, dev)
         xh = src.cpu().pin_memory()
-        e2e_total, _ = time_steps(lambda: op(xh), 3, 1, world)
+        e2e_total, _ = time_steps(lambda: op(xh), 3, 1, world, wait_for_result=True)
         e2e_ms = e2e_total / 3
         e2e = {"value": nbytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_ms,
                "h2d_bytes_per_step": op.h2d_bytes, "d2h_bytes_per_step": op.d2h_bytes,

@@ -290,7 +290,8 @@ int prism_b200_gemm_bf16_split_mode(int mode);
  * A run is asynchronous: it is ordered after the work already queued on `stream`, and `stream`
  * waits for it; synchronise `stream` before reading the host result.  Runs of one plan must
  * not overlap each other except through that ordering.  create/destroy allocate and free
- * device memory, a run does not.  block_rows / block_elems = 0 picks the default (1024 rows;
+ * device memory, a run does not.  block_rows / block_elems = 0 picks the default (GEMMs: blocks of 1024 rows with the
+ * last block cut again in halves down to 256 / 128 rows, so that little is left to do after the last upload; scan:
  * n / 16 elements, at least 2^22).  Operand layouts and dtypes are those of prism_b200_gemm_bf16,
  * prism_b200_sgemm and prism_b200_scan.  A plan belongs to the device that was current when it
  * was created.

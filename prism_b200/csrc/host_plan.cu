@@ -41,7 +41,11 @@ struct prism_b200_host_plan {
 
 namespace {
 
-void cut(std::vector<std::pair<size_t, size_t>>& out, size_t n, size_t block, size_t quantum) {
+// Cuts [0, n) into blocks of `block` (a multiple of `quantum`).  With `taper` the last block is cut again and again
+// in halves down to `quantum`: what remains to be done after the last byte has gone up is the last block's kernel
+// and download, so the last block should be small, while the earlier ones stay large enough to keep the kernel
+// efficient (1024, ..., 1024, 512, 256, 256 for n = 8192, block = 1024, quantum = 256).
+void cut(std::vector<std::pair<size_t, size_t>>& out, size_t n, size_t block, size_t quantum, bool taper = false) {
     out.clear();
     if (n == 0) return;
     if (n % quantum != 0 || n <= block) {
@@ -52,6 +56,13 @@ void cut(std::vector<std::pair<size_t, size_t>>& out, size_t n, size_t block, si
     if (block < quantum) block = quantum;
     if ((n + block - 1) / block > kMaxBlocks) block = ((n + kMaxBlocks - 1) / kMaxBlocks + quantum - 1) / quantum * quantum;
     for (size_t lo = 0; lo < n; lo += block) out.emplace_back(lo, lo + block < n ? lo + block : n);
+    while (taper && out.size() < kMaxBlocks) {
+        const size_t lo = out.back().first, hi = out.back().second;
+        const size_t half = (hi - lo) / 2 / quantum * quantum;
+        if (half < quantum || hi - lo - half < quantum) break;
+        out.back().second = lo + half;
+        out.emplace_back(lo + half, hi);
+    }
 }
 
 void destroy(prism_b200_host_plan* p) {
@@ -154,7 +165,7 @@ extern "C" int prism_b200_host_gemm_bf16_create(int M, int N, int K, int block_r
     auto* p = new prism_b200_host_plan;
     p->kind = kGemmBF16;
     p->M = M; p->N = N; p->K = K;
-    cut(p->blocks, static_cast<size_t>(N), block_rows ? block_rows : 1024, 256);
+    cut(p->blocks, static_cast<size_t>(N), block_rows ? block_rows : 1024, 256, /*taper=*/block_rows == 0);
     return finish_create(p, static_cast<size_t>(M) * K * 2, static_cast<size_t>(N) * K * 2, static_cast<size_t>(N) * M * 2, plan);
 }
 
@@ -195,7 +206,7 @@ extern "C" int prism_b200_host_sgemm_create(int kernel_id, int M, int N, int K, 
     auto* p = new prism_b200_host_plan;
     p->kind = kSgemm;
     p->M = M; p->N = N; p->K = K; p->kernel_id = kernel_id;
-    cut(p->blocks, static_cast<size_t>(M), block_rows ? block_rows : 1024, 128);
+    cut(p->blocks, static_cast<size_t>(M), block_rows ? block_rows : 1024, 128, /*taper=*/block_rows == 0);
     return finish_create(p, static_cast<size_t>(M) * K * 4, static_cast<size_t>(K) * N * 4, static_cast<size_t>(M) * N * 4, plan);
 }
 

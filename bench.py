@@ -238,14 +238,17 @@ def time_steps(step, steps: int, warmup: int, world: int, reset=None, wait_for_r
     return max_over_ranks(sum(per), world), per
 
 
-def measure_host_link(dev, mib: int = 256) -> dict:
-    """Pinned host <-> device copy rates of this GPU's link, each direction alone, best of 6 (GB/s)."""
+def measure_host_link(dev, mib: int = 256, world: int = 1) -> dict:
+    """Pinned host <-> device copy rates of this GPU's link, best of 6 (GB/s).  One direction at a time; with
+    several ranks all of them copy in that direction at once (a barrier keeps the directions apart), which is what
+    a rank gets while its neighbours upload or download too."""
     import torch
     n = mib << 20
     h = torch.empty(n, dtype=torch.uint8).pin_memory()
     d = torch.empty(n, dtype=torch.uint8, device=dev)
     out = {}
     for name, (dst, src) in (("h2d_gbs", (d, h)), ("d2h_gbs", (h, d))):
+        barrier(world)
         best = float("inf")
         dst.copy_(src, non_blocking=True)      # warm-up: first touch of the pages
         torch.cuda.synchronize()
@@ -257,14 +260,16 @@ def measure_host_link(dev, mib: int = 256) -> dict:
             b.synchronize()
             best = min(best, a.elapsed_time(b))
         out[name] = n / (best * 1e-3) / 1e9
+    barrier(world)
     out["sample_mib"] = mib
+    out["how"] = "each direction alone" + (f", all {world} ranks copying at once" if world > 1 else "")
     return out
 
 
 def host_link(args, dev) -> dict:
     """The link rates, measured once per run."""
     if getattr(args, "link", None) is None:
-        args.link = measure_host_link(dev)
+        args.link = measure_host_link(dev, world=int(os.environ.get("WORLD_SIZE", "1")))
     return args.link
 
 

@@ -405,9 +405,10 @@ def run_gemm_bf16(args, world, rank, peaks):
            "link_gbs": link, "frac_of_link": link_fraction(e2e_ms, op.h2d_bytes, op.d2h_bytes, link),
            "spot_check_ok": e2e_ok,
            "pipeline": ("%d blocks of B rows, upload / kernel / download on three streams" % op.steps) if world == 1 else
-                       ("per rank: its rows of A and 1/%d of B over PCIe; B completed by %d in-place NCCL all-gathers over "
-                        "NVLink into local HBM, each followed by the GEMM on that block of columns and its download"
-                        % (world, op.steps))}
+                       ("per rank: its rows of A and 1/%d of B over PCIe; B completed in %d blocks over NVLink into local HBM (%s), "
+                        "each followed by the GEMM on that block of columns and its download"
+                        % (world, op.steps, "one-sided pushes with flags, own kernels" if op.exchange == "peer"
+                           else "in-place NCCL all-gathers"))}
 
     kernel_ms = sum(per) / len(per)     # this rank's kernel: rows x S x S
     achieved = 2.0 * rows * S * S / (kernel_ms * 1e-3) / 1e12

@@ -273,6 +273,30 @@ int prism_b200_gemm_bf16_split_plan(int tiles, int pairs, int k_blocks, int tail
  * PRISM_B200_GEMM_SPLIT.  For tests and measurements. */
 int prism_b200_gemm_bf16_split_mode(int mode);
 
+/* ---- one-sided all-gather over peer memory --------------------------------- */
+
+/*
+ * The exchange step of the multi-GPU host-buffer GEMM (no counterpart in the reference, which is single-GPU):
+ * every rank pushes its piece of a block into every other rank's buffer over NVLink and raises a flag there; a
+ * consumer waits for all ranks' flags before it reads the block from its OWN memory.  All buffers must be
+ * peer-mapped (e.g. torch symmetric memory); `peer_dst` / `peer_flags` are device arrays of the `world` base
+ * addresses in rank order; `epoch` is non-zero, the same on every rank, and grows by one per call.
+ *   prism_b200_peer_push  copies `bytes` (a multiple of 16) from `src` to `dst_offset` in every OTHER rank's buffer
+ *                         (this rank's own copy is expected to be in place already), then stores `epoch` into flag
+ *                         word `flag_index` of every rank, its own included.  `done_counter` is one zeroed device
+ *                         word owned by the caller (the kernel leaves it zero).
+ *   prism_b200_peer_wait  waits on the stream until flag words [first, first + count) of this rank's own array hold
+ *                         `epoch` or a later one, for at most wait_limit_ns (0 = 1 s); a wait that runs out sets
+ *                         PRISM_B200_ERR_DEVICE_TIMEOUT (prism_b200_last_error after synchronising).
+ * A rank can be one call ahead of another, so callers alternate between two destination buffers by the parity
+ * of the epoch.  world <= 32.
+ */
+int prism_b200_peer_push(const void* src, size_t bytes, void* const* peer_dst, size_t dst_offset, int world, int rank,
+                         uint32_t* const* peer_flags, int flag_index, uint32_t epoch, uint32_t* done_counter,
+                         void* stream);
+int prism_b200_peer_wait(const uint32_t* flags, int first, int count, uint32_t epoch,
+                         unsigned long long wait_limit_ns, void* stream);
+
 /* ---- host-buffer plans ------------------------------------------------------ */
 
 /*

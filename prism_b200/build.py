@@ -18,7 +18,7 @@ from pathlib import Path
 PKG_DIR = Path(__file__).resolve().parent
 CSRC = PKG_DIR / "csrc"
 LIB_PATH = PKG_DIR / "libprism_b200.so"
-SOURCES = ["api.cu", "scan.cu", "sgemm.cu", "gemm_bf16.cu", "host_plan.cu"]
+SOURCES = ["api.cu", "scan.cu", "sgemm.cu", "gemm_bf16.cu", "host_plan.cu", "peer_gather.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

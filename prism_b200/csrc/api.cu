@@ -96,6 +96,7 @@ extern "C" int prism_b200_last_error(int* code, char* msg, size_t len) {
                               : st == DEV_SGEMM_PIPE_TIMEOUT    ? "sgemm smem pipeline"
                               : st == DEV_GEMM_PIPE_TIMEOUT     ? "bf16 gemm pipeline"
                               : st == DEV_SELFTEST_TIMEOUT      ? "self-test (as requested)"
+                              : st == DEV_PEER_WAIT_TIMEOUT     ? "wait for the peers' blocks"
                                                                  : "unknown";
             snprintf(g_msg, sizeof(g_msg), "device %d: device-side wait ran out in %s (status 0x%08x)", d, which, st);
             break;

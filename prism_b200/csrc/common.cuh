@@ -34,6 +34,7 @@ enum : uint32_t {
     DEV_SGEMM_PIPE_TIMEOUT    = 0x56E30001u,  // reserved: the SGEMM kernels have no waits that can run out
     DEV_GEMM_PIPE_TIMEOUT     = 0xB16E0001u,
     DEV_SELFTEST_TIMEOUT      = 0x5E1F0001u,
+    DEV_PEER_WAIT_TIMEOUT     = 0x9EE20001u,
 };
 
 #define PRISM_CUDA_TRY(expr)                                            \

@@ -28,6 +28,7 @@ The reference has no multi-GPU code; its scan harness works on one device
 """
 from __future__ import annotations
 
+import ctypes
 from typing import Any
 
 import torch
@@ -87,6 +88,21 @@ class _CudaOps:
         if code:
             self._pb.clear_error()
             raise self._pb.PrismB200Error(code, msg)
+
+
+def _symmetric_bytes(n_bytes: int, device, group):
+    """`n_bytes` of device memory on this rank that every rank of the group can write (uint8 tensor), the
+    symmetric-memory handle, and the list of all ranks' base addresses; None if torch's symmetric memory cannot
+    provide them."""
+    try:
+        import torch.distributed._symmetric_memory as symm
+        raw = symm.empty(n_bytes, dtype=torch.uint8, device=device)
+        handle = symm.rendezvous(raw, group if group is not None else dist.group.WORLD)
+        return raw, handle, [int(p) for p in handle.buffer_ptrs]
+    except Exception as e:   # no peer access, several nodes, or a torch build without the module
+        import warnings
+        warnings.warn(f"peer exchange unavailable ({type(e).__name__}: {e}); using NCCL all-gathers")
+        return None
 
 
 def _symmetric_words(n_words: int, device, group):
@@ -237,9 +253,15 @@ class ShardedHostGemmBF16:
 
     Every rank holds its rows of A, all of B and its (N, M / g) block of the column-major C in pinned host
     memory.  B is the same on every rank, so no rank uploads all of it: per step each rank sends 1/g of a
-    block of B's rows over its own PCIe link, the ranks all-gather the block over NVLink into their OWN memory
-    (an NCCL all-gather in place; the kernel only ever reads local HBM), and the GEMM on that block of columns
-    of C runs while the next block is uploaded and gathered and the previous block of C goes back to the host:
+    block of B's rows over its own PCIe link, the ranks complete the block over NVLink in their OWN memory, and
+    the GEMM on that block of columns of C runs while the next block is uploaded and gathered and the previous
+    block of C goes back to the host.  The exchange is one-sided by default (`exchange="peer"`): each rank pushes
+    its piece into every other rank's copy of B with the library's own copy kernel and raises a flag there
+    (prism_b200_peer_push), and the kernel stream waits, bounded, for all ranks' flags of the block
+    (prism_b200_peer_wait) -- no collective call, nothing waits inside the copy.  B is double-buffered by the
+    parity of the call, since a rank can be one call ahead of another.  `exchange="nccl"` does the same with an
+    in-place NCCL all-gather per block and is what runs where symmetric memory is not available.  Either way the
+    GEMM only ever reads local HBM:
 
         upload stream    piece 0 | A rows | piece 1 | piece 2 | ...
         gather stream             gather 0          | gather 1 | ...
@@ -253,7 +275,8 @@ class ShardedHostGemmBF16:
     """
 
     def __init__(self, M: int, N: int, K: int, device, group: Any = None, steps: int = 0, gemm: Any = None,
-                 overlap_download: bool | None = None):
+                 overlap_download: bool | None = None, exchange: str | None = None, wait_limit_s: float = 0.0,
+                 symmetric_bytes: Any = None):
         """`gemm(rows, n, K, A, B_block, C_block)` replaces the kernel call; the tests of the host-side
         logic pass a CPU stand-in together with device="cpu" (then there are no streams either).
         `overlap_download`: send blocks of C back while later blocks of B still go up (True, the default), or
@@ -288,8 +311,33 @@ class ShardedHostGemmBF16:
         self.h2d_bytes = (self.rows + N // self.world) * K * 2
         self.d2h_bytes = N * self.rows * 2
         self.a = torch.empty((self.rows, K), dtype=torch.bfloat16, device=self.device)
-        self.b = torch.empty((N, K), dtype=torch.bfloat16, device=self.device)
         self.c = torch.empty((N, self.rows), dtype=torch.bfloat16, device=self.device)
+        if exchange not in (None, "peer", "nccl"):
+            raise ValueError("exchange must be 'peer' or 'nccl'")
+        self.epoch = 0
+        self.wait_limit_s = float(wait_limit_s)
+        self.exchange = "nccl"
+        if exchange != "nccl" and self.on_cuda and self.world > 1 and self.world <= 32:
+            # two copies of B (by call parity) and steps * world flag words, in one peer-mapped allocation
+            b_bytes = N * K * 2
+            got = (symmetric_bytes or _symmetric_bytes)(2 * b_bytes + steps * self.world * 4, self.device, group)
+            ok = torch.tensor([1 if got is not None else 0], dtype=torch.int32, device=self.device)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+            if int(ok.item()) == 1:
+                raw, self._symm, bases = got
+                self.b2 = raw[:2 * b_bytes].view(torch.bfloat16).view(2, N, K)
+                self.flags = raw[2 * b_bytes:].view(torch.int32)
+                self.flags.zero_()
+                self._dst_table = torch.tensor(bases, dtype=torch.int64, device=self.device)
+                self._flag_table = torch.tensor([p + 2 * b_bytes for p in bases], dtype=torch.int64, device=self.device)
+                self._counter = torch.zeros(1, dtype=torch.int32, device=self.device)
+                self.exchange = "peer"
+                torch.cuda.synchronize(self.device)
+                dist.barrier(group)   # every rank's flags are zero before anyone pushes
+            elif exchange == "peer":
+                raise RuntimeError("exchange='peer' needs peer-mapped (symmetric) memory on every rank")
+        if self.exchange == "nccl":
+            self.b2 = torch.empty((1, N, K), dtype=torch.bfloat16, device=self.device)
         # upload, gather, kernel, download
         self.lanes = [torch.cuda.Stream(self.device) for _ in range(4)] if self.on_cuda else [None] * 4
 
@@ -317,9 +365,10 @@ class ShardedHostGemmBF16:
                                ("C", C_host_local, (self.N, self.rows))):
             if t.device.type != "cpu" or t.dtype != torch.bfloat16 or tuple(t.shape) != shape or not t.is_contiguous():
                 raise ValueError(f"{name} must be a contiguous host bf16 tensor of shape {shape}")
+        import prism_b200 as pb
+        from . import _lib
         gemm = self._gemm
         if gemm is None:
-            import prism_b200 as pb
             gemm = pb.runmyh100
         up, gather, kernel, down = self.lanes
         cuda = self.on_cuda
@@ -334,12 +383,19 @@ class ShardedHostGemmBF16:
             wait(s, begin)
         a_done = event()
         all_up = event()
+        self.epoch += 1
+        peer = self.exchange == "peer"
+        b = self.b2[self.epoch & 1] if peer else self.b2[0]
+        if peer:
+            lib = pb.load()
+            row_bytes = self.K * 2
+            parity_off = (self.epoch & 1) * self.N * row_bytes
         for i in range(self.steps):
             lo = i * self.block
             mine = slice(lo + self.rank * self.piece, lo + (self.rank + 1) * self.piece)
             uploaded, gathered, computed = event(), event(), event()
             with on(up):
-                self.b[mine].copy_(B_host[mine], non_blocking=True)
+                b[mine].copy_(B_host[mine], non_blocking=True)
                 record(uploaded, up)
                 if i == 0:          # A goes up while the first block is being gathered
                     self.a.copy_(A_host_local, non_blocking=True)
@@ -350,16 +406,29 @@ class ShardedHostGemmBF16:
                         wait(down, all_up)   # the download stream was idle until here: nothing of C has gone back yet
             with on(gather):
                 wait(gather, uploaded)
-                # On the GPU in place: this rank's piece already sits at its position in the block.
-                piece = self.b[mine] if cuda else self.b[mine].clone()
-                if self.world > 1:
-                    dist.all_gather_into_tensor(self.b[lo:lo + self.block], piece, group=self.group)
+                if peer:
+                    # one-sided: push this rank's piece into every other rank's copy of the block, then flag it
+                    stream = ctypes.c_void_p(gather.cuda_stream)
+                    _lib.check(lib.prism_b200_peer_push(
+                        b[mine].data_ptr(), self.piece * row_bytes, self._dst_table.data_ptr(),
+                        parity_off + mine.start * row_bytes, self.world, self.rank, self._flag_table.data_ptr(),
+                        i * self.world + self.rank, self.epoch, self._counter.data_ptr(), stream))
+                else:
+                    # On the GPU in place: this rank's piece already sits at its position in the block.
+                    piece = b[mine] if cuda else b[mine].clone()
+                    if self.world > 1:
+                        dist.all_gather_into_tensor(b[lo:lo + self.block], piece, group=self.group)
                 record(gathered, gather)
             with on(kernel):
-                wait(kernel, gathered)
+                if peer:
+                    # the block is complete when every rank's flag of this step carries this call's epoch
+                    _lib.check(lib.prism_b200_peer_wait(self.flags.data_ptr(), i * self.world, self.world, self.epoch,
+                                                        int(self.wait_limit_s * 1e9), ctypes.c_void_p(kernel.cuda_stream)))
+                else:
+                    wait(kernel, gathered)
                 if i == 0:
                     wait(kernel, a_done)
-                gemm(self.rows, self.block, self.K, self.a, self.b[lo:lo + self.block], self.c[lo:lo + self.block])
+                gemm(self.rows, self.block, self.K, self.a, b[lo:lo + self.block], self.c[lo:lo + self.block])
                 record(computed, kernel)
             if self.overlap_download or i == self.steps - 1:
                 first = i if self.overlap_download else 0

@@ -105,6 +105,50 @@ def test_scan_step_gives_up_when_a_word_never_arrives(pb):
     assert int(y[-1]) == n and pb.last_error()[0] == 0
 
 
+def test_one_sided_gather_with_virtual_ranks(pb):
+    """prism_b200_peer_push / prism_b200_peer_wait with three virtual ranks whose buffers and flag arrays live on one
+    device: every rank pushes its piece into the others' buffers, then every rank's wait finds all flags raised and
+    every buffer holds the whole block.  Two epochs; a wait for an epoch nobody has pushed runs out and says so."""
+    lib = pb.load()
+    stream = ctypes.c_void_p(torch.cuda.current_stream(torch.device(DEV)).cuda_stream)
+    world, piece = 3, 1 << 20                     # bytes per rank and block
+    bufs = torch.zeros((world, world * piece), dtype=torch.uint8, device=DEV)
+    flags = torch.zeros((world, 8), dtype=torch.int32, device=DEV)
+    dst_table = torch.tensor([bufs[r].data_ptr() for r in range(world)], dtype=torch.int64, device=DEV)
+    flag_table = torch.tensor([flags[r].data_ptr() for r in range(world)], dtype=torch.int64, device=DEV)
+    counter = torch.zeros(1, dtype=torch.int32, device=DEV)
+    with torch.cuda.device(DEV):
+        for epoch in (1, 2):
+            g = torch.Generator(device=DEV).manual_seed(epoch)
+            want = torch.randint(0, 256, (world * piece,), dtype=torch.uint8, device=DEV, generator=g)
+            bufs.zero_()
+            for r in range(world):                # a rank's own piece is in place before it pushes
+                bufs[r, r * piece:(r + 1) * piece] = want[r * piece:(r + 1) * piece]
+            for r in range(world):
+                rc = lib.prism_b200_peer_push(bufs[r, r * piece:].data_ptr(), piece, dst_table.data_ptr(), r * piece, world, r,
+                                              flag_table.data_ptr(), 2 + r, epoch, counter.data_ptr(), stream)
+                assert rc == 0, pb.last_error()
+            for r in range(world):
+                assert lib.prism_b200_peer_wait(flags[r].data_ptr(), 2, world, epoch, 0, stream) == 0
+            torch.cuda.synchronize()
+            assert pb.last_error()[0] == 0, pb.last_error()
+            assert all(torch.equal(bufs[r], want) for r in range(world))
+            assert bool((flags[:, 2:2 + world] == epoch).all()) and int(counter[0]) == 0
+        # an earlier epoch's wait is satisfied by a later flag; a later epoch's wait runs out (2 ms) and is reported
+        assert lib.prism_b200_peer_wait(flags[0].data_ptr(), 2, world, 1, 0, stream) == 0
+        torch.cuda.synchronize()
+        assert pb.last_error()[0] == 0
+        assert lib.prism_b200_peer_wait(flags[0].data_ptr(), 2, world, 3, 2_000_000, stream) == 0
+        torch.cuda.synchronize()
+    code, msg = pb.last_error()
+    assert code == 5 and "peers" in msg
+    pb.clear_error()
+    assert lib.prism_b200_peer_push(bufs.data_ptr() + 8, 16, dst_table.data_ptr(), 0, world, 0, flag_table.data_ptr(), 0, 1,
+                                    counter.data_ptr(), None) == 3     # misaligned source
+    assert lib.prism_b200_peer_wait(flags.data_ptr(), 0, 33, 1, 0, None) == 1
+    pb.clear_error()
+
+
 def test_argument_checks(pb):
     lib = pb.load()
     words, table = _setup(2)

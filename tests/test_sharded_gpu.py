@@ -53,18 +53,26 @@ for n_small in (3 * world + 1, 4 * (world - 1)):
 # bf16 GEMM from host arrays: every rank uploads its rows of A and 1/world of B, B is completed over NVLink
 Mh, Nh, Kh = 256 * world, 2048, 512
 A, B = O.gemm_bf16_inputs(Mh, Nh, Kh, seed=19)
-op = sharded.ShardedHostGemmBF16(Mh, Nh, Kh, dev, steps=4)
 from prism_b200 import host
-ah = host.pinned_near(dev, (op.rows, Kh), torch.bfloat16); ah.copy_(torch.from_numpy(A[op.lo:op.hi].view(np.int16)).view(torch.bfloat16))
-bh = host.pinned_near(dev, (Nh, Kh), torch.bfloat16); bh.copy_(torch.from_numpy(B.view(np.int16)).view(torch.bfloat16))
-ch = host.pinned_near(dev, (Nh, op.rows), torch.bfloat16)
-for rep in range(2):
-    ch.fill_(float("nan"))
-    op(ah, bh, ch)
-    torch.cuda.synchronize()
-    ok, worst = O.gemm_bf16_check(ch.view(torch.int16).numpy().view(np.uint16), O.gemm_bf16_cpu(A[op.lo:op.hi], B))
-    assert ok, (rank, rep, worst)
-assert op.steps == 4 and op.h2d_bytes == (op.rows + Nh // world) * Kh * 2
+ref_c = None
+for exchange in ("peer", "nccl"):   # one-sided pushes over peer memory (own kernels), and NCCL all-gathers
+    op = sharded.ShardedHostGemmBF16(Mh, Nh, Kh, dev, steps=4, exchange=exchange)
+    assert op.exchange == exchange
+    if ref_c is None:
+        ah = host.pinned_near(dev, (op.rows, Kh), torch.bfloat16); ah.copy_(torch.from_numpy(A[op.lo:op.hi].view(np.int16)).view(torch.bfloat16))
+        bh = host.pinned_near(dev, (Nh, Kh), torch.bfloat16); bh.copy_(torch.from_numpy(B.view(np.int16)).view(torch.bfloat16))
+        ch = host.pinned_near(dev, (Nh, op.rows), torch.bfloat16)
+        ref_c = O.gemm_bf16_cpu(A[op.lo:op.hi], B)
+    for rep in range(4):            # four calls: both copies of B, twice, and back-to-back without a host wait first
+        ch.fill_(float("nan"))
+        op(ah, bh, ch)
+        if rep & 1:
+            op(ah, bh, ch)
+        torch.cuda.synchronize()
+        ok, worst = O.gemm_bf16_check(ch.view(torch.int16).numpy().view(np.uint16), ref_c)
+        assert ok, (exchange, rank, rep, worst)
+    assert op.steps == 4 and op.h2d_bytes == (op.rows + Nh // world) * Kh * 2
+    assert pb.last_error()[0] == 0, pb.last_error()
 
 # bf16 GEMM: rows of M sharded, B replicated, no collective
 M, N, K = 256 * world, 512, 256

@@ -165,6 +165,12 @@ class ShardedScan:
                 dist.barrier(group)   # every rank's words are zero before anyone publishes
             else:
                 schedule = "reduce_then_scan"
+        elif schedule == self.PEER_SCHEDULE and on_cuda and ops is None and asked == self.PEER_SCHEDULE:
+            # One rank, asked for by name: the same kernel with this rank as its only peer (12 B/element instead of
+            # the plain scan's 8).  Of no use in production; it lets the sharded kernel be measured on one GPU.
+            self.slots = torch.zeros(2, dtype=torch.int64, device=device)
+            self._table = torch.tensor([self.slots.data_ptr()], dtype=torch.int64, device=device)
+            self.peer_slots_dev = int(self._table.data_ptr())
         self.schedule = schedule
         self.fell_back = asked in (None, self.PEER_SCHEDULE) and schedule != self.PEER_SCHEDULE and on_cuda and self.world > 1
 
@@ -177,7 +183,7 @@ class ShardedScan:
     def __call__(self, x_local: torch.Tensor) -> torch.Tensor:
         if x_local.numel() != self.n_local:
             raise ValueError(f"shard has {x_local.numel()} elements, planned for {self.n_local}")
-        if self.schedule == self.PEER_SCHEDULE and self.world > 1:
+        if self.schedule == self.PEER_SCHEDULE and self.slots is not None:
             self.epoch += 1
             self.ops.scan_sharded_(x_local, self.workspace, self.slots, self.peer_slots_dev, self.rank, self.world,
                                    self.epoch, self.wait_limit_s)

@@ -212,7 +212,7 @@ constexpr uint32_t kSliceElems = 1u << 15;   // elements per reduce ticket (128 
 // in L2 afterwards is then the part the scan reads first), add them up, and whoever finishes the last
 // slice stores {epoch, total} into every rank's word array, one 64-bit system-scope store each, over
 // NVLink for the peers.  Slices are handed out by ticket, so a CTA that is not resident yet holds
-// nobody up.  All threads of the CTA take part; `s_ticket` and `s_part` are shared-memory scratch.
+// nobody up.  All threads of the CTA take part; `s_ticket` (two words) and `s_part` are shared-memory scratch.
 __device__ __forceinline__ void reduce_and_publish(uint32_t n, const uint32_t* src, uint32_t* header, const ShardArgs& sh,
                                                    volatile uint32_t* s_ticket, volatile uint32_t* s_part) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -225,16 +225,19 @@ __device__ __forceinline__ void reduce_and_publish(uint32_t n, const uint32_t* s
         if (blockIdx.x == 0 && tid == 0) publish(0u);
         return;
     }
-    for (;;) {
-        if (tid == 0) *s_ticket = atomicAdd(header + 2, 1u);
-        __syncthreads();
-        const uint32_t t = *s_ticket;
+    // The next ticket is drawn while the current slice is being read, and the partial sums stay in registers
+    // until the CTA has no more slices: one barrier per slice, one block-wide sum and two atomics per CTA.
+    uint32_t acc = 0, mine = 0;
+    if (tid == 0) s_ticket[0] = atomicAdd(header + 2, 1u);
+    __syncthreads();
+    for (uint32_t k = 0;; ++k) {
+        const uint32_t t = s_ticket[k & 1u];
         if (t >= slices) break;
+        if (tid == 0) s_ticket[(k + 1u) & 1u] = atomicAdd(header + 2, 1u);
         const unsigned long long lo = static_cast<unsigned long long>(slices - 1 - t) * kSliceElems;
         const uint32_t cnt = n - lo < kSliceElems ? static_cast<uint32_t>(n - lo) : kSliceElems;
         const uint4* p4 = reinterpret_cast<const uint4*>(src + lo);
         const uint32_t nv = cnt / 4;
-        uint32_t acc = 0;
         uint32_t v = tid;
         for (; v + 3 * kThreads < nv; v += 4 * kThreads) {
             const uint4 a = __ldcg(p4 + v), b = __ldcg(p4 + v + kThreads), c = __ldcg(p4 + v + 2 * kThreads),
@@ -247,18 +250,20 @@ __device__ __forceinline__ void reduce_and_publish(uint32_t n, const uint32_t* s
             acc += (a.x + a.y) + (a.z + a.w);
         }
         if (static_cast<uint32_t>(tid) < (cnt & 3u)) acc += src[lo + nv * 4 + tid];
-        acc = warp_sum(acc);
-        if (lane == 0) s_part[warp] = acc;
-        __syncthreads();
-        if (tid == 0) {
-            uint32_t tot = 0;
-            for (int w = 0; w < kThreads / 32; ++w) tot += s_part[w];
-            atomicAdd(header + 4, tot);
+        ++mine;
+        __syncthreads();   // the next ticket is in place, and everybody has read this one
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) s_part[warp] = acc;
+    __syncthreads();
+    if (tid == 0 && mine > 0) {
+        uint32_t tot = 0;
+        for (int w = 0; w < kThreads / 32; ++w) tot += s_part[w];
+        atomicAdd(header + 4, tot);
+        __threadfence();
+        if (atomicAdd(header + 3, mine) + mine == slices) {   // every slice has been added
             __threadfence();
-            if (atomicAdd(header + 3, 1u) == slices - 1) {   // every slice has been added
-                __threadfence();
-                publish(atomicAdd(header + 4, 0u));
-            }
+            publish(atomicAdd(header + 4, 0u));
         }
     }
 }

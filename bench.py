@@ -390,7 +390,7 @@ def run_gemm_bf16(args, world, rank, peaks):
 
     # end to end through the host-buffer operator: pinned host arrays in, pinned host array out
     link = host_link(args, dev)
-    op = sharded.ShardedHostGemmBF16(S, S, S, dev)
+    op = sharded.ShardedHostGemmBF16(S, S, S, dev, wait_limit_s=10.0)    # ranks of a benchmark can be seconds apart at their first call
     Ah = host.pinned_near(dev, (rows, S), torch.bfloat16); Ah.copy_(A)
     Bh = host.pinned_near(dev, (S, S), torch.bfloat16); Bh.copy_(B)
     Ch = host.pinned_near(dev, (S, rows), torch.bfloat16)
@@ -499,7 +499,7 @@ def run_scan(args, world, rank, peaks, steps=None, warmup=None):
     g = torch.Generator(device=dev).manual_seed(99 + rank)
     src = torch.randint(0, 2, (n,), dtype=torch.int32, device=dev, generator=g)
     x = torch.empty_like(src)
-    scan = sharded.ShardedScan(n, dev, schedule=args.scan_schedule)
+    scan = sharded.ShardedScan(n, dev, schedule=args.scan_schedule, wait_limit_s=10.0)
     sampler = ClockSampler(torch.cuda.current_device())
     sampler.start()
     l0 = pb.launch_count()

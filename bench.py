@@ -458,7 +458,7 @@ def run_sgemm(args, world, rank, peaks, steps=None, warmup=None):
     ref = 1.5 * (A[ridx].double() @ B.double()) + 0.5 * C0[ridx].double()
     err = float((C[ridx].double() - ref).abs().max() / ref.abs().max())
 
-    op = host.HostSgemm(rows, S, S, dev)
+    op = sharded.ShardedHostSgemm(S, S, S, dev, wait_limit_s=10.0)
     Ah, Bh, Ch = A.cpu().pin_memory(), B.cpu().pin_memory(), C0.cpu().pin_memory()
     e2e_steps = 3
     e2e_total, _ = time_steps(lambda: op(1.5, Ah, Bh, 0.5, Ch), e2e_steps, 1, world, wait_for_result=True)
@@ -482,7 +482,8 @@ def run_sgemm(args, world, rank, peaks, steps=None, warmup=None):
                     "h2d_bytes_per_step": op.h2d_bytes, "d2h_bytes_per_step": op.d2h_bytes,
                     "link_gbs": host_link(args, dev),
                     "frac_of_link": link_fraction(e2e_ms, op.h2d_bytes, op.d2h_bytes, host_link(args, dev)),
-                    "pipeline": "%d blocks of rows of M, upload / kernel / download on three streams" % op.blocks},
+                    "pipeline": ("%d blocks of rows of M, upload / kernel / download on three streams" % op.blocks) +
+                                ("" if op.exchange == "none" else "; each rank uploads 1/%d of B and pushes it to the others over NVLink" % world)},
             "gpu_launches": launches, "clocks": clocks, "rel_error_sampled_rows": err, "spot_check_ok": err <= 1e-5}
 
 

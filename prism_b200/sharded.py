@@ -447,3 +447,118 @@ class ShardedHostGemmBF16:
             record(done, s)
             wait(caller, done)
         return C_host_local
+
+
+class ShardedHostSgemm:
+    """C = alpha * A @ B + beta * C for operands in HOST memory on g GPUs (one process each), rows of M sharded.
+
+    The fp32 counterpart of ShardedHostGemmBF16.  Every rank holds its rows of A and C and all of B (K x N,
+    the same on every rank) in pinned host memory.  Each rank uploads only rows [r * K / g, (r + 1) * K / g) of B
+    and pushes them into every other rank's copy over NVLink (prism_b200_peer_push, one-sided, own kernel); its
+    rows of A and C go up meanwhile, in blocks.  Every output element needs all of B, so the kernels start when
+    all ranks' flags are up (prism_b200_peer_wait) and then run block by block of rows while later blocks of A and
+    C still go up and finished blocks of C go back.  Per rank and call the host link carries
+    (M / g * (K + N) + K / g * N) * 4 bytes up and M / g * N * 4 down, against (M / g * (K + N) + K * N) * 4 up when
+    every rank uploads all of B.  With one rank, or without peer-mapped memory, it is
+    prism_b200.host.HostSgemm on the rank's rows.  The reference's harness copies everything in, launches and
+    copies everything out on one GPU (evals/4090_sgemm/main.cu:64-120)."""
+
+    def __init__(self, M: int, N: int, K: int, device, group: Any = None, kernel: int = 5, block_rows: int = 0,
+                 wait_limit_s: float = 0.0, symmetric_bytes: Any = None):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.device = torch.device(device)
+        self.lo, self.hi = row_shard(M, self.world, self.rank)
+        self.M, self.N, self.K, self.kernel = M, N, K, kernel
+        self.rows = self.hi - self.lo
+        self.wait_limit_s = float(wait_limit_s)
+        self.epoch = 0
+        self.single = None
+        peer = self.world > 1 and self.world <= 32 and self.device.type == "cuda" and K % self.world == 0 and \
+            (K // self.world * N * 4) % 16 == 0
+        if peer:
+            b_bytes = K * N * 4
+            got = (symmetric_bytes or _symmetric_bytes)(2 * b_bytes + self.world * 4, self.device, group)
+            ok = torch.tensor([1 if got is not None else 0], dtype=torch.int32, device=self.device)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+            peer = int(ok.item()) == 1
+        if not peer:
+            from . import host
+            self.single = host.HostSgemm(self.rows, N, K, self.device, kernel=kernel, block_rows=block_rows)
+            self.h2d_bytes, self.d2h_bytes, self.blocks = self.single.h2d_bytes, self.single.d2h_bytes, self.single.blocks
+            self.exchange = "none"
+            return
+        raw, self._symm, bases = got
+        self.b2 = raw[:2 * b_bytes].view(torch.float32).view(2, K, N)
+        self.flags = raw[2 * b_bytes:].view(torch.int32)
+        self.flags.zero_()
+        self._dst_table = torch.tensor(bases, dtype=torch.int64, device=self.device)
+        self._flag_table = torch.tensor([p + 2 * b_bytes for p in bases], dtype=torch.int64, device=self.device)
+        self._counter = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.exchange = "peer"
+        self.piece = K // self.world                               # rows of B this rank uploads
+        block_rows = block_rows or 512     # large enough for the 128 x 128 tile form, small enough to pipeline
+        self.spans = [(lo, min(lo + block_rows, self.rows)) for lo in range(0, self.rows, block_rows)]
+        self.blocks = len(self.spans)
+        self.h2d_bytes = (self.rows * (K + N) + self.piece * N) * 4
+        self.d2h_bytes = self.rows * N * 4
+        self.a = torch.empty((self.rows, K), dtype=torch.float32, device=self.device)
+        self.c = torch.empty((self.rows, N), dtype=torch.float32, device=self.device)
+        self.lanes = [torch.cuda.Stream(self.device) for _ in range(4)]   # upload, exchange, kernel, download
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group)   # every rank's flags are zero before anyone pushes
+
+    def __call__(self, alpha: float, A_host_local: torch.Tensor, B_host: torch.Tensor, beta: float,
+                 C_host_local: torch.Tensor) -> torch.Tensor:
+        if self.single is not None:
+            return self.single(alpha, A_host_local, B_host, beta, C_host_local)
+        import prism_b200 as pb
+        from . import _lib
+        for name, t, shape in (("A", A_host_local, (self.rows, self.K)), ("B", B_host, (self.K, self.N)),
+                               ("C", C_host_local, (self.rows, self.N))):
+            if t.device.type != "cpu" or t.dtype != torch.float32 or tuple(t.shape) != shape or not t.is_contiguous():
+                raise ValueError(f"{name} must be a contiguous host float32 tensor of shape {shape}")
+        lib = pb.load()
+        up, exchange, kernel, down = self.lanes
+        caller = torch.cuda.current_stream(self.device)
+        begin = torch.cuda.Event()
+        begin.record(caller)
+        for s in self.lanes:
+            s.wait_event(begin)
+        self.epoch += 1
+        b = self.b2[self.epoch & 1]
+        mine = slice(self.rank * self.piece, (self.rank + 1) * self.piece)
+        row_bytes = self.N * 4
+        b_up = torch.cuda.Event()
+        with torch.cuda.stream(up):
+            b[mine].copy_(B_host[mine], non_blocking=True)     # this rank's rows of B first: the others wait for them
+            b_up.record(up)
+        with torch.cuda.stream(exchange):
+            exchange.wait_event(b_up)
+            _lib.check(lib.prism_b200_peer_push(
+                b[mine].data_ptr(), self.piece * row_bytes, self._dst_table.data_ptr(),
+                (self.epoch & 1) * self.K * row_bytes + mine.start * row_bytes, self.world, self.rank,
+                self._flag_table.data_ptr(), self.rank, self.epoch, self._counter.data_ptr(),
+                ctypes.c_void_p(exchange.cuda_stream)))
+        with torch.cuda.stream(kernel):
+            _lib.check(lib.prism_b200_peer_wait(self.flags.data_ptr(), 0, self.world, self.epoch,
+                                                int(self.wait_limit_s * 1e9), ctypes.c_void_p(kernel.cuda_stream)))
+        for lo, hi in self.spans:
+            uploaded, computed = torch.cuda.Event(), torch.cuda.Event()
+            with torch.cuda.stream(up):
+                self.a[lo:hi].copy_(A_host_local[lo:hi], non_blocking=True)
+                self.c[lo:hi].copy_(C_host_local[lo:hi], non_blocking=True)
+                uploaded.record(up)
+            with torch.cuda.stream(kernel):
+                kernel.wait_event(uploaded)
+                pb.run_my_kernel(self.kernel, hi - lo, self.N, self.K, alpha, self.a[lo:hi], b, beta, self.c[lo:hi])
+                computed.record(kernel)
+            with torch.cuda.stream(down):
+                down.wait_event(computed)
+                C_host_local[lo:hi].copy_(self.c[lo:hi], non_blocking=True)
+        for s in self.lanes:
+            done = torch.cuda.Event()
+            done.record(s)
+            caller.wait_event(done)
+        return C_host_local

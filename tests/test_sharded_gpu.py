@@ -98,6 +98,19 @@ sp(1.5, ta, tb, 0.5, tc)
 torch.cuda.synchronize()
 err = O.sgemm_rel_error(tc.cpu().numpy(), O.sgemm_cpu(1.5, A[sp.lo:sp.hi], B, 0.5, C[sp.lo:sp.hi]))
 assert err <= O.SGEMM_TOL, err
+# SGEMM from host arrays: every rank uploads 1 / world of B's rows and pushes them to the others
+Ms, Ns, Ks = 256 * world, 384, 128 * world
+A, B, C = O.sgemm_inputs(Ms, Ns, Ks, seed=23)
+hs = sharded.ShardedHostSgemm(Ms, Ns, Ks, dev, block_rows=128)
+assert hs.exchange == "peer" and hs.blocks == 2 and hs.h2d_bytes == (hs.rows * (Ks + Ns) + Ks // world * Ns) * 4
+ha, hb = (torch.from_numpy(np.ascontiguousarray(t)).pin_memory() for t in (A[hs.lo:hs.hi], B))
+want = O.sgemm_cpu(1.5, A[hs.lo:hs.hi], B, 0.5, C[hs.lo:hs.hi])
+for rep in range(3):
+    hc = torch.from_numpy(np.ascontiguousarray(C[hs.lo:hs.hi])).pin_memory()
+    hs(1.5, ha, hb, 0.5, hc)
+    torch.cuda.synchronize()
+    err = O.sgemm_rel_error(hc.numpy(), want)
+    assert err <= O.SGEMM_TOL, (rank, rep, err)
 assert pb.last_error()[0] == 0, pb.last_error()
 dist.barrier()
 dist.destroy_process_group()

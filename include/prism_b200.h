@@ -251,28 +251,6 @@ int prism_b200_gemm_bf16(int M, int N, int K, const uint16_t* A, const uint16_t*
 int prism_b200_gemm_bf16_axpby(int M, int N, int K, float alpha, const uint16_t* A, const uint16_t* B, float beta,
                                const uint16_t* Cin, uint16_t* D, void* stream);
 
-/*
- * How the 512 x 256 two-CTA form of the kernel above shares the last, partly filled wave of output tiles among
- * its CTA pairs.  With `tiles` tiles of `k_blocks` 64-wide k-blocks on `pairs` pairs, pair `pair` computes
- * out5[0] whole tiles (tile = i * pairs + pair) and then out5[1] items of the last wave: tiles out5[2],
- * out5[2] + 1, ..., each over k-blocks [out5[3], out5[4]).  The R = tiles mod pairs pairs that own a tile of
- * the last wave compute its k-blocks [0, k_blocks - tail); the other pairs ("helpers") compute the last `tail`
- * k-blocks of a few neighbouring tiles each and leave them as fp32 partial sums in a workspace owned by the
- * library (one per device and stream, 37 MB on a B200, allocated at the first launch that splits; freed when
- * the host plan that owns the stream is destroyed, else at exit); the owner adds them to its own sums, always in
- * the order owner + helper, and stores the tile, so results do not depend on timing.  The launcher picks
- * `tail` so that owners and helpers finish together.  Measured on a B200 the hand-over of the partial sums
- * costs about what the idle pairs are worth (between 11 % slower and 2 % faster at the benchmark shapes), so
- * the split runs only on request: prism_b200_gemm_bf16_split_mode(1) or PRISM_B200_GEMM_SPLIT=1.  This
- * function is host-side arithmetic only (no GPU
- * needed); it is the same function the kernel evaluates.  The reference's kernel has a fixed grid of 128
- * CTAs and no such split (generated/cutlass_my_h100_match_no_tail.cu:90-101).
- */
-int prism_b200_gemm_bf16_split_plan(int tiles, int pairs, int k_blocks, int tail, int pair, int* out5);
-/* 1: split wherever the shape allows; 0 or -1 (default): never.  Process-wide; overrides
- * PRISM_B200_GEMM_SPLIT.  For tests and measurements. */
-int prism_b200_gemm_bf16_split_mode(int mode);
-
 /* ---- one-sided all-gather over peer memory --------------------------------- */
 
 /*

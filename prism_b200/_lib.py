@@ -47,8 +47,6 @@ SIGNATURES = {
     "prism_b200_scan_static": (c_int, [c_size_t, c_void_p, c_void_p]),
     "prism_b200_gemm_bf16": (c_int, [c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     "prism_b200_gemm_bf16_axpby": (c_int, [c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p]),
-    "prism_b200_gemm_bf16_split_mode": (c_int, [c_int]),
-    "prism_b200_gemm_bf16_split_plan": (c_int, [c_int, c_int, c_int, c_int, c_int, POINTER(c_int)]),
     "prism_b200_peer_push": (c_int, [c_void_p, c_size_t, c_void_p, c_size_t, c_int, c_int, c_void_p, c_int, ctypes.c_uint32, c_void_p, c_void_p]),
     "prism_b200_peer_wait": (c_int, [c_void_p, c_int, c_int, ctypes.c_uint32, c_ulonglong, c_void_p]),
     "prism_b200_host_gemm_bf16_create": (c_int, [c_int, c_int, c_int, c_int, POINTER(c_void_p)]),

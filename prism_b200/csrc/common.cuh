@@ -23,10 +23,6 @@ void count_launch(unsigned n = 1);
 // (and sets the error state) if the buffer cannot be set up.
 uint32_t* device_status_word();
 
-// Gives back the bf16 GEMM's split-K workspace of (current device, stream), if there is one
-// (called when a stream that the library owns is destroyed).
-void release_gemm_split_workspace(cudaStream_t stream);
-
 // Codes written into the status word by kernels.
 enum : uint32_t {
     DEV_OK = 0,

@@ -716,85 +716,18 @@ struct WideCfg {
 };
 }  // namespace g16
 
-// What the split form needs beyond the reference's parameter list.
-struct SplitArgs {
-    float* partials;      // one 512 x 256 fp32 slot per tile of the last wave
-    uint32_t* flags;      // 16 words per slot (one per epilogue warp of a pair); a slot is valid when they hold `epoch`
-    uint32_t epoch;       // differs from every earlier launch that used this workspace
-    int tail;             // k-blocks at the end of every tile of the last wave that a helper pair computes
-};
-
-// The work of one CTA pair: `full` whole tiles (tile = i * pairs + pair), then its part of the last,
-// partly filled wave.  Without SPLIT a pair simply takes every pairs-th tile.  With SPLIT the
-// R = tiles mod pairs tiles of the last wave are shared between the R pairs that would have computed
-// them alone and the pairs - R pairs that would have had nothing to do:
-//   pair < R   "owner": computes k-blocks [0, k_blocks - tail) of tile R0 + pair, then adds the fp32 sums
-//              that a helper left in the tile's slot and stores bf16;
-//   pair >= R  "helper": computes the last `tail` k-blocks of a few consecutive tiles of the wave, one
-//              after the other, writes each result to that tile's slot and raises the slot's flags.
-// The owners all walk k from 0 in step, so they keep sharing operand rows in L2 as in a full wave; the
-// few helpers re-read one narrow k-range for several neighbouring tiles.  A helper never waits, and
-// an owner waits only for a slot that was filled while it was still in its own main loop, so there
-// is no cycle of waits.  The sum is owner part + helper part, always in that order.
-struct PairPlan {
-    int full;        // whole tiles before the last wave
-    int segs;        // items of the last wave: 1 for an owner, the number of tails for a helper, else 0
-    int first_tile;  // tile of the first of them (the others follow consecutively)
-    int kb0, kb1;    // their k-block range
-    int wave_first;  // first tile of the last wave (slot index = tile - wave_first)
-};
-
-template <bool SPLIT>
-__host__ __device__ __forceinline__ PairPlan make_pair_plan(int pair, int pairs, int total_tiles, int k_blocks, int tail) {
-    PairPlan p;
-    p.segs = 0;
-    p.first_tile = 0;
-    p.kb0 = 0;
-    p.kb1 = k_blocks;
-    p.wave_first = total_tiles;
-    if constexpr (!SPLIT) {
-        p.full = pair < total_tiles ? (total_tiles - pair + pairs - 1) / pairs : 0;
-    } else {
-        p.full = total_tiles / pairs;
-        const int rem = total_tiles - p.full * pairs;       // tiles of the last wave = number of owners
-        const int helpers = pairs - rem;
-        p.wave_first = p.full * pairs;
-        if (rem > 0 && pair < rem) {
-            p.segs = 1;
-            p.first_tile = p.wave_first + pair;
-            p.kb1 = k_blocks - tail;
-        } else if (rem > 0 && tail > 0) {
-            const int h = pair - rem;                        // helper h takes tiles [h * rem / helpers, (h + 1) * rem / helpers)
-            const int i0 = static_cast<int>(static_cast<long long>(h) * rem / helpers);
-            const int i1 = static_cast<int>(static_cast<long long>(h + 1) * rem / helpers);
-            p.segs = i1 - i0;
-            p.first_tile = p.wave_first + i0;
-            p.kb0 = k_blocks - tail;
-        }
-    }
-    return p;
-}
-
-__host__ __device__ __forceinline__ void plan_item(const PairPlan& p, int i, int pair, int pairs, int k_blocks, int& tile,
-                                                   int& kb0, int& kb1) {
-    if (i < p.full) {
-        tile = i * pairs + pair;
-        kb0 = 0;
-        kb1 = k_blocks;
-    } else {
-        tile = p.first_tile + (i - p.full);
-        kb0 = p.kb0;
-        kb1 = p.kb1;
-    }
-}
-
-template <int GROUP, bool SPLIT>
-__device__ __forceinline__ void pair_wide_body(int M, int N, int K, __nv_bfloat16* C, const CUtensorMap* tensorMapA,
-                                               const CUtensorMap* tensorMapB, const SplitArgs& split) {
+// 512 x 256 tiles: each CTA of the pair holds two 128-row n blocks (two accumulators of 256 columns, all of tensor
+// memory) against the pair's 256 m rows, so the m-side operand is read once for two MMAs.  Persistent: pair p takes
+// tiles p, p + pairs, ...
+template <int GROUP>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(g16::WideCfg::THREADS, 1)
+cutlass_my_h100_match_no_tail_pair_wide(int M, int N, int K, __nv_bfloat16* C,
+                                        const __grid_constant__ CUtensorMap tensorMapA,
+                                        const __grid_constant__ CUtensorMap tensorMapB) {
     using namespace g16;
     using W_ = WideCfg;
     constexpr int STAGES = W_::STAGES;
-    constexpr uint32_t IDESC = instr_desc(256, W_::TILE_M);  // 256 n rows across the pair per MMA, 256 m columns
+    constexpr uint32_t IDESC = instr_desc(256, W_::TILE_M);       // 256 n rows across the pair per MMA, 256 m columns
 
     extern __shared__ unsigned char smem_raw[];
     const uint32_t raw_addr = smem_u32(smem_raw);
@@ -818,8 +751,6 @@ __device__ __forceinline__ void pair_wide_body(int M, int N, int K, __nv_bfloat1
     const int tiles_n = N / W_::TILE_N;
     const int total_tiles = tiles_m * tiles_n;
     const int k_blocks = K / BLOCK_K;
-    const PairPlan plan = make_pair_plan<SPLIT>(pair, pairs, total_tiles, k_blocks, split.tail);
-    const int items = plan.full + plan.segs;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -849,29 +780,28 @@ __device__ __forceinline__ void pair_wide_body(int M, int N, int K, __nv_bfloat1
     if (warp == 0) {
         // ------------------------- TMA producer (both CTAs) -------------------------
         if (lane == 0) {
-            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tensorMapA)) : "memory");
-            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tensorMapB)) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tensorMapA)) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tensorMapB)) : "memory");
             int stage = 0;
             uint32_t phase = 0;
             int armed = 0;   // stages loaded and not known to be consumed (for the unwind path)
-            for (int i = 0; i < items && !timed_out; ++i) {
-                int t, kb0, kb1, tm, tn;
-                plan_item(plan, i, pair, pairs, k_blocks, t, kb0, kb1);
+            for (int t = pair; t < total_tiles && !timed_out; t += pairs) {
+                int tm, tn;
                 tile_coords(t, tiles_m, tiles_n, tm, tn, GROUP);
                 // This CTA's two n blocks and its half of the m rows.
                 const int n_row0 = tn * W_::TILE_N + static_cast<int>(rank) * 256;
                 const int m_row = tm * W_::TILE_M + static_cast<int>(rank) * W_::HALF;
-                for (int kb = kb0; kb < kb1; ++kb) {
+                for (int kb = 0; kb < k_blocks; ++kb) {
                     if (!mbar_wait_bounded_sleepy(&empty_bar[stage], phase ^ 1u, abort_flag, 40)) {
                         timed_out = true;
                         break;
                     }
                     unsigned char* dst = ring + stage * W_::STAGE_BYTES;
                     const uint32_t leader_full = cluster_addr(&full_bar[stage], 0);
-                    if (leader) mbar_arrive_expect_tx(&full_bar[stage], 2 * W_::STAGE_BYTES);
-                    tma_load_2d_pair(dst, tensorMapB, kb * BLOCK_K, n_row0, leader_full);
-                    tma_load_2d_pair(dst + W_::BLOCK_BYTES, tensorMapB, kb * BLOCK_K, n_row0 + W_::HALF, leader_full);
-                    tma_load_2d_pair(dst + 2 * W_::BLOCK_BYTES, tensorMapA, kb * BLOCK_K, m_row, leader_full);
+                    if (leader) mbar_arrive_expect_tx(&full_bar[stage], 2 * W_::STAGE_BYTES);   // both CTAs' bytes
+                    tma_load_2d_pair(dst, &tensorMapB, kb * BLOCK_K, n_row0, leader_full);
+                    tma_load_2d_pair(dst + W_::BLOCK_BYTES, &tensorMapB, kb * BLOCK_K, n_row0 + W_::HALF, leader_full);
+                    tma_load_2d_pair(dst + 2 * W_::BLOCK_BYTES, &tensorMapA, kb * BLOCK_K, m_row, leader_full);
                     armed = armed < STAGES ? armed + 1 : STAGES;
                     if (++stage == STAGES) {
                         stage = 0;
@@ -887,15 +817,13 @@ __device__ __forceinline__ void pair_wide_body(int M, int N, int K, __nv_bfloat1
             int stage = 0;
             uint32_t phase = 0;
             uint32_t tile_phase = 0;
-            for (int i = 0; i < items && !timed_out; ++i) {
-                int t, kb0, kb1;
-                plan_item(plan, i, pair, pairs, k_blocks, t, kb0, kb1);
+            for (int t = pair; t < total_tiles && !timed_out; t += pairs) {
                 if (!mbar_wait_bounded(acc_empty_bar, tile_phase ^ 1u, abort_flag)) {   // both CTAs drained both accumulators
                     timed_out = true;
                     break;
                 }
                 tc_fence_after();
-                for (int kb = kb0; kb < kb1; ++kb) {
+                for (int kb = 0; kb < k_blocks; ++kb) {
                     if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag)) {
                         timed_out = true;
                         break;
@@ -907,7 +835,7 @@ __device__ __forceinline__ void pair_wide_body(int M, int N, int K, __nv_bfloat1
                     const uint64_t q_desc = smem_desc_k_sw128(base + 2 * W_::BLOCK_BYTES);
 #pragma unroll
                     for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
-                        const uint32_t accumulate = (kb != kb0 || k != 0) ? 1u : 0u;
+                        const uint32_t accumulate = (kb | k) != 0 ? 1u : 0u;
                         umma_bf16_pair(tmem_base, p0_desc + 2u * k, q_desc + 2u * k, IDESC, accumulate);
                         umma_bf16_pair(tmem_base + 256u, p1_desc + 2u * k, q_desc + 2u * k, IDESC, accumulate);
                     }
@@ -931,12 +859,8 @@ __device__ __forceinline__ void pair_wide_body(int M, int N, int K, __nv_bfloat1
         const int quarter = warp & 3;
         const int block = (warp - 2) >> 2;
         uint32_t tile_phase = 0;
-        // Row of this lane inside the pair's 512-row tile, and this warp's flag inside a pair's 16.
-        const int tile_row = static_cast<int>(rank) * 256 + block * W_::HALF + quarter * 32 + lane;
-        const int flag_idx = static_cast<int>(rank) * W_::EPI_WARPS + (warp - 2);
-        for (int i = 0; i < items; ++i) {
-            int t, kb0, kb1, tm, tn;
-            plan_item(plan, i, pair, pairs, k_blocks, t, kb0, kb1);
+        for (int t = pair; t < total_tiles; t += pairs) {
+            int tm, tn;
             tile_coords(t, tiles_m, tiles_n, tm, tn, GROUP);
             const bool ready = lane != 0 || mbar_wait_bounded_sleepy(acc_full_bar, tile_phase, abort_flag, 200);
             if (!__all_sync(0xffffffffu, ready)) {
@@ -944,33 +868,6 @@ __device__ __forceinline__ void pair_wide_body(int M, int N, int K, __nv_bfloat1
                 break;
             }
             tc_fence_after();
-            const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(block * 256);
-            if (SPLIT && kb0 > 0) {
-                // Helper: fp32 accumulators to the tile's slot, column by column so that the 32 lanes
-                // (32 consecutive rows) write one 128-byte line per store; then this warp's flag.
-                const int slot_idx = t - plan.wave_first;
-                float* slot = split.partials + static_cast<size_t>(slot_idx) * (W_::TILE_N * W_::TILE_M) + tile_row;
-#pragma unroll 1
-                for (int c0 = 0; c0 < W_::TILE_M; c0 += 32) {
-                    uint32_t r[32];
-                    tmem_ld_32cols(t_row + c0, r);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int e = 0; e < 32; ++e) __stcg(slot + static_cast<size_t>(c0 + e) * W_::TILE_N, __uint_as_float(r[e]));
-                }
-                // Tensor memory has been read (the stores may still be on their way): the next tail's MMAs can start.
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive_cluster(cluster_addr(acc_empty_bar, 0));
-                __threadfence();
-                __syncwarp();
-                if (lane == 0) {
-                    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(split.flags + slot_idx * 16 + flag_idx), "r"(split.epoch)
-                                 : "memory");
-                }
-                tile_phase ^= 1u;
-                continue;
-            }
             // A lane reads one accumulator row (one n, consecutive m).  Writing that row straight to
             // global memory would make every store instruction touch 32 different lines, 16 bytes
             // each; instead the warp passes 32 rows x 64 columns at a time through shared memory
@@ -978,71 +875,9 @@ __device__ __forceinline__ void pair_wide_body(int M, int N, int K, __nv_bfloat1
             // 128-byte lines: 4 rows per instruction.
             const size_t n_warp = static_cast<size_t>(tn) * W_::TILE_N + rank * 256 + block * W_::HALF + quarter * 32;
             __nv_bfloat16* c_warp = C + n_warp * static_cast<size_t>(M) + static_cast<size_t>(tm) * W_::TILE_M;
+            const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                                   static_cast<uint32_t>(block * 256);
             unsigned char* stage_buf = epi_smem + (warp - 2) * W_::EPI_WARP_BYTES;
-            if (SPLIT && kb1 < k_blocks) {   // kb0 == 0 here: the helpers' items were handled above
-                // Owner: a helper computed the last k-blocks of this tile and left them in the tile's slot;
-                // this warp's rows of the slot must have landed.
-                const int slot_idx = t - plan.wave_first;
-                bool landed = true;
-                if (lane == 0) {
-                    const uint32_t* f = split.flags + slot_idx * 16 + flag_idx;
-                    const unsigned long long t0 = global_timer_ns();
-                    uint32_t v;
-                    for (uint32_t spin = 0;; ++spin) {
-                        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
-                        if (v == split.epoch) break;
-                        if ((spin & 63u) == 63u && (*abort_flag || global_timer_ns() - t0 > kWaitLimitNs)) {
-                            landed = false;
-                            break;
-                        }
-                        __nanosleep(40);
-                    }
-                }
-                if (!__all_sync(0xffffffffu, landed)) {
-                    timed_out = true;
-                    break;
-                }
-                __syncwarp();
-                // 64 columns at a time: the partial sums of those columns are requested first (they come
-                // from L2, a microsecond away), then the accumulator is read, then both are added in pair
-                // order, rounded once and sent out through the staging buffer.
-                const float* slot = split.partials + static_cast<size_t>(slot_idx) * (W_::TILE_N * W_::TILE_M) + tile_row;
-#pragma unroll 1
-                for (int c0 = 0; c0 < W_::TILE_M; c0 += 64) {
-                    float add[64];
-#pragma unroll
-                    for (int e = 0; e < 64; ++e) add[e] = __ldcg(slot + static_cast<size_t>(c0 + e) * W_::TILE_N);
-                    uint32_t r0[32], r1[32];
-                    tmem_ld_32cols(t_row + c0, r0);
-                    tmem_ld_32cols(t_row + c0 + 32, r1);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int ch = 0; ch < 8; ++ch) {
-                        const uint32_t* r = ch < 4 ? &r0[8 * ch] : &r1[8 * (ch - 4)];
-                        const float* a = &add[8 * ch];
-                        uint4 o;
-                        o.x = pack_bf16(__float_as_uint(__uint_as_float(r[0]) + a[0]), __float_as_uint(__uint_as_float(r[1]) + a[1]));
-                        o.y = pack_bf16(__float_as_uint(__uint_as_float(r[2]) + a[2]), __float_as_uint(__uint_as_float(r[3]) + a[3]));
-                        o.z = pack_bf16(__float_as_uint(__uint_as_float(r[4]) + a[4]), __float_as_uint(__uint_as_float(r[5]) + a[5]));
-                        o.w = pack_bf16(__float_as_uint(__uint_as_float(r[6]) + a[6]), __float_as_uint(__uint_as_float(r[7]) + a[7]));
-                        *reinterpret_cast<uint4*>(stage_buf + lane * 128 + ((ch ^ (lane & 7)) << 4)) = o;
-                    }
-                    __syncwarp();
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const int row = 4 * j + (lane >> 3);
-                        const int ch = lane & 7;
-                        const uint4 v = *reinterpret_cast<const uint4*>(stage_buf + row * 128 + ((ch ^ (row & 7)) << 4));
-                        *reinterpret_cast<uint4*>(c_warp + static_cast<size_t>(row) * M + c0 + ch * 8) = v;
-                    }
-                    __syncwarp();
-                }
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive_cluster(cluster_addr(acc_empty_bar, 0));
-                tile_phase ^= 1u;
-                continue;
-            }
             // The whole accumulator row first goes into registers as packed bf16 (256 columns = 128
             // registers), so that tensor memory can be handed back and the next tile's MMAs start
             // while this tile is still on its way to global memory.
@@ -1097,23 +932,6 @@ __device__ __forceinline__ void pair_wide_body(int M, int N, int K, __nv_bfloat1
                      "r"(static_cast<uint32_t>(TMEM_COLS))
                      : "memory");
     }
-}
-
-template <int GROUP>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(g16::WideCfg::THREADS, 1)
-cutlass_my_h100_match_no_tail_pair_wide(int M, int N, int K, __nv_bfloat16* C,
-                                        const __grid_constant__ CUtensorMap tensorMapA,
-                                        const __grid_constant__ CUtensorMap tensorMapB) {
-    pair_wide_body<GROUP, false>(M, N, K, C, &tensorMapA, &tensorMapB, SplitArgs{nullptr, nullptr, 0u});
-}
-
-// The same kernel with the last, partly filled wave of tiles cut along K over all CTA pairs (see PairPlan).
-template <int GROUP>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(g16::WideCfg::THREADS, 1)
-cutlass_my_h100_match_no_tail_pair_wide_split(int M, int N, int K, __nv_bfloat16* C,
-                                              const __grid_constant__ CUtensorMap tensorMapA,
-                                              const __grid_constant__ CUtensorMap tensorMapB, const SplitArgs split) {
-    pair_wide_body<GROUP, true>(M, N, K, C, &tensorMapA, &tensorMapB, split);
 }
 
 namespace {
@@ -1297,150 +1115,20 @@ int launch_gemm_pair(int dev, int M, int N, int K, const void* A, const void* B,
                               (M / P_::BLOCK) * (N / P_::BLOCK), dev, M, N, K, map_a, map_b, C, s);
 }
 
-// ---- workspace of the split form -------------------------------------------------------------
-// One 512 x 256 fp32 slot per CTA pair plus 16 flag words per pair.  Launches on one stream run one
-// after the other and can share a workspace; launches on different streams may overlap and must not,
-// so there is one workspace per (device, stream), created at the first split launch on that stream
-// (a cudaMalloc, i.e. not during a stream capture) and kept until the process ends.  At most
-// kMaxSplitWorkspaces exist; a stream beyond that gets the unsplit kernel.
-struct SplitWorkspace {
-    int dev;
-    cudaStream_t stream;
-    float* partials;
-    uint32_t* flags;
-    uint32_t epoch;
-};
-constexpr int kMaxSplitWorkspaces = 16;
-constexpr size_t kSlotFloats = static_cast<size_t>(g16::WideCfg::TILE_N) * g16::WideCfg::TILE_M;
-SplitWorkspace g_split_ws[kMaxSplitWorkspaces];
-int g_split_ws_count = 0;
-
-// Fills `out` with the workspace of (dev, s) and a fresh epoch; *have = false if none can be had.
-int split_workspace(int dev, cudaStream_t s, int pairs, SplitArgs* out, bool* have) {
-    std::lock_guard<std::mutex> lk(g_launch_mu);
-    *have = false;
-    SplitWorkspace* w = nullptr;
-    for (int i = 0; i < g_split_ws_count; ++i)
-        if (g_split_ws[i].dev == dev && g_split_ws[i].stream == s) w = &g_split_ws[i];
-    if (!w) {
-        if (g_split_ws_count == kMaxSplitWorkspaces) return PRISM_B200_OK;
-        void* mem = nullptr;
-        const size_t flag_bytes = static_cast<size_t>(pairs) * 16 * sizeof(uint32_t);
-        const size_t bytes = static_cast<size_t>(pairs) * kSlotFloats * sizeof(float) + flag_bytes;
-        if (cudaMalloc(&mem, bytes) != cudaSuccess) {
-            (void)cudaGetLastError();   // out of memory is not an error of the call: the unsplit kernel runs instead
-            return PRISM_B200_OK;
-        }
-        w = &g_split_ws[g_split_ws_count];
-        w->dev = dev;
-        w->stream = s;
-        w->partials = static_cast<float*>(mem);
-        w->flags = reinterpret_cast<uint32_t*>(w->partials + static_cast<size_t>(pairs) * kSlotFloats);
-        w->epoch = 0;
-        cudaError_t e = cudaMemsetAsync(w->flags, 0, flag_bytes, s);   // epoch 0 is never used by a launch
-        if (e != cudaSuccess) {
-            cudaFree(mem);
-            return cuda_failed(e, "cudaMemsetAsync(split flags)");
-        }
-        ++g_split_ws_count;
-    }
-    if (++w->epoch == 0) w->epoch = 1;
-    out->partials = w->partials;
-    out->flags = w->flags;
-    out->epoch = w->epoch;
-    *have = true;
-    return PRISM_B200_OK;
-}
-
-}  // namespace
-
-void release_gemm_split_workspace(cudaStream_t stream) {
-    std::lock_guard<std::mutex> lk(g_launch_mu);
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) return;
-    for (int i = 0; i < g_split_ws_count; ++i) {
-        if (g_split_ws[i].dev == dev && g_split_ws[i].stream == stream) {
-            cudaFree(g_split_ws[i].partials);   // flags live in the same allocation
-            g_split_ws[i] = g_split_ws[--g_split_ws_count];
-            return;
-        }
-    }
-}
-
-namespace {
-
-bool g_split_mode_set = false;   // prism_b200_gemm_bf16_split_mode was called: the environment no longer decides
-int g_forced_split = -1;   // 1 (PRISM_B200_GEMM_SPLIT=1 or prism_b200_gemm_bf16_split_mode) asks for the split kernel
-// Cost of one hand-over of partial sums (helper writes 512 KB, owner re-reads them), in main-loop k-blocks.
-constexpr int kSplitDumpKb = 7;
-
 int launch_gemm_pair_wide(int dev, int M, int N, int K, const void* A, const void* B, void* C, cudaStream_t s) {
     using W_ = g16::WideCfg;
     CUtensorMap map_a, map_b;
     if (int rc = get_tensor_map(dev, A, M, K, W_::HALF, &map_a)) return rc;
     if (int rc = get_tensor_map(dev, B, N, K, W_::HALF, &map_b)) return rc;
-    static int max_pairs[64] = {}, max_pairs_split[64] = {};
-    const int tiles = (M / W_::TILE_M) * (N / W_::TILE_N);
-    const int k_blocks = K / g16::BLOCK_K;
-    int pairs_cap = 0;
-    if (int rc = pair_capacity(cutlass_my_h100_match_no_tail_pair_wide_split<16>, max_pairs_split, W_::THREADS,
-                               W_::SMEM_BYTES, dev, &pairs_cap))
-        return rc;
-    // Sharing the last wave's R tiles with the pairs - R idle pairs: a helper with n tails spends n * (tail + hand-over)
-    // k-block times while the owners spend k_blocks - tail, so tail = (k_blocks - n * hand-over) / (n + 1) makes both
-    // end together.  Measured on a B200 (split on and off alternating in one process, median of 30): 8192^3 cut over
-    // 8 / 4 / 2 / 1 GPUs 11 % slower / 2 % faster / equal / 3 % slower, 4096^3 3 % slower, 6144^3 6 % slower, 12288^3
-    // 2 % faster -- handing 512 KB of fp32 sums per tile from one pair to another (write, fence, flag, re-read, add)
-    // costs about as much as the idle pairs are worth.  The split therefore runs only on request
-    // (prism_b200_gemm_bf16_split_mode(1) or PRISM_B200_GEMM_SPLIT=1), wherever the shape allows a tail of >= 1.
-    const int rem = tiles % pairs_cap, helpers = pairs_cap - rem;
-    int tail = 0;
-    if (rem > 0 && helpers > 0) {
-        const int n = (rem + helpers - 1) / helpers;
-        tail = (k_blocks - n * kSplitDumpKb) / (n + 1);
-        if (tail >= k_blocks) tail = k_blocks - 1;
-    }
-    const bool want_split = g_forced_split == 1 && tail >= 1;
-    if (want_split) {
-        SplitArgs split{};
-        bool have = false;
-        if (int rc = split_workspace(dev, s, pairs_cap, &split, &have)) return rc;
-        if (have) {
-            split.tail = tail;
-            cudaLaunchConfig_t cfg;
-            cudaLaunchAttribute attr[1];
-            pair_launch_config(&cfg, attr, W_::THREADS, W_::SMEM_BYTES, s);
-            cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs_cap));   // every pair takes part in the split wave
-            PRISM_CUDA_TRY(cudaLaunchKernelEx(&cfg, cutlass_my_h100_match_no_tail_pair_wide_split<16>, M, N, K,
-                                              static_cast<__nv_bfloat16*>(C), map_a, map_b, split));
-            count_launch();
-            return PRISM_B200_OK;
-        }
-    }
-    return launch_pair_kernel(cutlass_my_h100_match_no_tail_pair_wide<16>, max_pairs, W_::THREADS, W_::SMEM_BYTES, tiles, dev,
-                              M, N, K, map_a, map_b, C, s);
+    static int max_pairs[64] = {};
+    return launch_pair_kernel(cutlass_my_h100_match_no_tail_pair_wide<16>, max_pairs, W_::THREADS, W_::SMEM_BYTES,
+                              (M / W_::TILE_M) * (N / W_::TILE_N), dev, M, N, K, map_a, map_b, C, s);
 }
 
 }  // namespace
 }  // namespace prism_b200
 
 using namespace prism_b200;
-
-extern "C" int prism_b200_gemm_bf16_split_mode(int mode) {
-    if (mode < -1 || mode > 1) return set_error(PRISM_B200_ERR_INVALID_ARGUMENT, "gemm_bf16_split_mode: -1, 0 or 1");
-    std::lock_guard<std::mutex> lk(g_launch_mu);
-    g_split_mode_set = true;
-    g_forced_split = mode;
-    return PRISM_B200_OK;
-}
-
-extern "C" int prism_b200_gemm_bf16_split_plan(int tiles, int pairs, int k_blocks, int tail, int pair, int* out5) {
-    if (!out5 || tiles < 0 || pairs < 1 || k_blocks < 1 || tail < 0 || tail >= k_blocks || pair < 0 || pair >= pairs)
-        return set_error(PRISM_B200_ERR_INVALID_ARGUMENT, "gemm_bf16_split_plan: bad argument");
-    const PairPlan p = make_pair_plan<true>(pair, pairs, tiles, k_blocks, tail);
-    out5[0] = p.full; out5[1] = p.segs; out5[2] = p.first_tile; out5[3] = p.kb0; out5[4] = p.kb1;
-    return PRISM_B200_OK;
-}
 
 extern "C" int prism_b200_gemm_bf16_axpby(int M, int N, int K, float alpha, const uint16_t* A, const uint16_t* B, float beta,
                                           const uint16_t* Cin, uint16_t* D, void* stream) {
@@ -1499,12 +1187,9 @@ extern "C" int prism_b200_gemm_bf16(int M, int N, int K, const uint16_t* A, cons
             if (dev >= 0 && dev < 64) sm_count[dev] = sms;
         }
         if (!env_read) {
-            // PRISM_B200_GEMM_PAIR = 0 / 1 / 2 forces one-CTA / 256 x 256 pair / 512 x 256 pair,
-            // PRISM_B200_GEMM_SPLIT = 0 / 1 forces the 512 x 256 form without / with the split last wave (tests).
+            // PRISM_B200_GEMM_PAIR = 0 / 1 / 2 forces one-CTA / 256 x 256 pair / 512 x 256 pair (tests)
             const char* e = getenv("PRISM_B200_GEMM_PAIR");
             forced = e ? atoi(e) : -1;
-            const char* sp = getenv("PRISM_B200_GEMM_SPLIT");
-            if (!g_split_mode_set) g_forced_split = sp ? atoi(sp) : -1;
             env_read = true;
         }
     }

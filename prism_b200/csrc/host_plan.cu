@@ -70,13 +70,6 @@ void destroy(prism_b200_host_plan* p) {
     cudaFree(p->a);
     cudaFree(p->b);
     cudaFree(p->c);
-    if (p->lane[1]) {   // the kernel lane may own a split-K workspace, on the plan's device
-        int cur = -1;
-        if (cudaGetDevice(&cur) == cudaSuccess && cudaSetDevice(p->device) == cudaSuccess) {
-            release_gemm_split_workspace(p->lane[1]);
-            cudaSetDevice(cur);
-        }
-    }
     for (auto& s : p->lane)
         if (s) cudaStreamDestroy(s);
     if (p->begin) cudaEventDestroy(p->begin);

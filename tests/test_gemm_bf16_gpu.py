@@ -87,21 +87,13 @@ def test_random_shapes_match_fp64_oracle(pb):
     ("1", [(256, 256, 64), (256, 512, 1024), (1024, 2048, 320), (4096, 4096, 256)]),
     # two-CTA kernel, 512 x 256 pair tiles
     ("2", [(256, 512, 64), (512, 512, 1024), (1024, 2048, 320), (4096, 4096, 256), (2048, 8192, 128)]),
-    # the same with the last wave shared between owners and helper pairs: one tile split in two, a few tiles with one
-    # helper each, one full wave plus a last wave whose helpers take three tails each, K not a multiple of the tile's
-    # k-block count times anything, and a shape too shallow to split (runs unsplit)
-    ("2+split", [(256, 512, 8192), (1024, 2048, 1024), (2048, 8192, 2048), (1024, 1024, 4160), (1024, 8192, 2048),
-                 (256, 512, 64)]),
-    ("2-split", [(256, 512, 8192), (2048, 8192, 2048)]),
 ])
 def test_every_kernel_form_forced(mode, shapes):
     """The launcher picks a kernel form by problem size; each form is forced here on small and
     multi-wave shapes (the choice is read from the environment once per process, hence the child)."""
     import os
     import subprocess
-    env = dict(os.environ, PRISM_B200_GEMM_PAIR=mode[0])
-    if len(mode) > 1:
-        env["PRISM_B200_GEMM_SPLIT"] = "1" if mode[1] == "+" else "0"
+    env = dict(os.environ, PRISM_B200_GEMM_PAIR=mode)
     r = subprocess.run([sys.executable, "-c", _CHILD % (str(ROOT), shapes)], env=env, capture_output=True, text=True,
                        timeout=600)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]

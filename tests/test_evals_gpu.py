@@ -1,6 +1,7 @@
 """The evaluation programs (prism_b200/evals) on small sizes: they must pass their own checks against
 cuBLAS / CUB / a CPU loop and print lines in the formats the reference's plotting script parses
-(evals/plot_results.py:18-108; the patterns below restate what that script looks for)."""
+(evals/plot_results.py:18-108).  The lines are read with tests/evals_lines.py, which tests/test_evals_format.py
+pins to what the reference's own script returns on sample outputs."""
 import re
 import subprocess
 import sys
@@ -9,6 +10,9 @@ from pathlib import Path
 import pytest
 
 ROOT = Path(__file__).resolve().parent.parent
+sys.path.insert(0, str(Path(__file__).resolve().parent))
+import evals_lines as L  # noqa: E402
+
 EVALS = ROOT / "prism_b200" / "evals"
 pytestmark = pytest.mark.gpu
 
@@ -38,6 +42,9 @@ def test_sgemm_sweep_format_and_checks(binaries):
     assert [int(k) for k in re.findall(r"^\[My Kernel (\d+)\]", perf, re.M)] == [1, 2, 3, 4, 5] * 2
     vals = re.findall(r"performance:\s+\(\s*([\d.]+)\)\s+GFLOPS.*size:\s+\((\d+)\)", perf)
     assert len(vals) == 12 and all(float(v) > 0 for v, _ in vals)
+    rows = L.sgemm_rows(out)
+    assert set(rows) == {"cuBLAS", *L.SGEMM_NAMES.values()}
+    assert all([s for s, _ in r] == [256, 512] and all(g > 0 for _, g in r) for r in rows.values())
 
 
 def test_scan_bench_format_and_checks(binaries):
@@ -45,11 +52,8 @@ def test_scan_bench_format_and_checks(binaries):
     assert "mismatch" not in out
     lines = out.strip().splitlines()
     assert "Size" in lines[0] and "CUB (GB/s)" in lines[0] and lines[1].startswith("---")
-    rows = []
-    for ln in lines[2:]:
-        parts = re.split(r"\s*\|\s*", ln.strip())
-        rows.append((int(parts[0]), float(parts[1].split()[1]), float(parts[2].split()[1])))
-    assert [r[0] for r in rows] == [1 << 20, 1 << 21]
+    rows = L.scan_rows(out)
+    assert len(rows) == len(lines) - 2 and [r[0] for r in rows] == [1 << 20, 1 << 21]
     assert all(cub > 0 and ours > 0 for _, cub, ours in rows)
 
 
@@ -59,6 +63,7 @@ def test_bf16_bench_format_and_checks(binaries):
     k = re.search(r"Kernel:\s+.*performance:\s+\(\s*([\d.]+)\)\s+TFLOPS.*size:\s+\((\d+)\)", out)
     c = re.search(r"cuBLAS:\s+.*performance:\s+\(\s*([\d.]+)\)\s+TFLOPS.*size:\s+\((\d+)\)", out)
     assert k and c and int(k.group(2)) == 1024 and float(k.group(1)) > 0 and float(c.group(1)) > 0
+    assert L.bf16_rows(out) == [(1024, float(k.group(1)), float(c.group(1)))]
 
 
 def test_reference_sgemm_sweep_relinked_against_this_library():

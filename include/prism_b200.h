@@ -97,12 +97,24 @@ int prism_b200_sgemm(int kernel_id, int M, int N, int K, float alpha,
                      void* stream);
 
 /*
- * Tile of kernel 5: -1 (default) the launcher picks by the number of tiles (128 x 128; 64 x 128 below half a wave
- * of those; 64 x 64 below a quarter of a wave), 0 / 1 / 2 forces 128 x 128 / 64 x 128 / 64 x 64.  Every form gives the same bits.
+ * Tile of kernel 5: -1 (default) the launcher picks among 128 x 128, 64 x 128 and 64 x 64 (and, for the 64-row tiles,
+ * how many CTAs share a tile along K, below) by an estimate of the makespan: rounds of CTAs per SM x k-steps per CTA x
+ * the tile's cost per step; 0 / 1 / 2 forces 128 x 128 / 64 x 128 / 64 x 64.  The three tiles give the same bits.
  * Process-wide; for tests and measurements.  The reference's launcher has one tile per kernel
  * (evals/4090_sgemm/runner.cu:191-243).
  */
 int prism_b200_sgemm_tile_mode(int mode);
+
+/*
+ * CTAs of kernel 5 that share one output tile along K: -1 (default) the launcher picks (1; 2 or 4 where the 64-row
+ * tiles still leave the SMs mostly without a second CTA and K is long enough), 1 / 2 / 4 forces it for the 64 x 128 and
+ * 64 x 64 tiles (halved until K divides into 16-wide steps per CTA; 128 x 128 tiles are never shared).  The S CTAs of a
+ * tile form a thread-block cluster, multiply one range of K each and add the partial tiles through distributed shared
+ * memory in the order of the ranges, so the result is the same on every run; it differs from the unshared forms' in
+ * rounding only (<= 1e-5 relative to fp64 like them).  Process-wide; for tests and measurements.  The reference has
+ * no k-split (evals/4090_sgemm/runner.cu:191-243).
+ */
+int prism_b200_sgemm_k_slices(int slices);
 
 /* ---- uint32 inclusive scan (single pass, decoupled look-back) ------------- */
 

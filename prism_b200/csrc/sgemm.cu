@@ -269,26 +269,63 @@ __device__ __forceinline__ void cp_async16(void* dst_smem, const void* src) {
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t cluster_size() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+    return r;
+}
+// All threads of all CTAs of the cluster; orders shared-memory accesses (remote ones included) before and after it.
+__device__ __forceinline__ void cluster_barrier() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Stores 16 bytes at the place of `local` in the shared memory of CTA `cta` of the cluster.
+__device__ __forceinline__ void store_cluster_f4(const float* local, uint32_t cta, float a, float b, float c, float d) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(local)), "r"(cta));
+    asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(remote), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
 // WARPS_M x WARPS_N warps (four in all), each on a 64 x (16 NV) warp tile; NV = 16-byte B vectors
 // per lane per k.  <2, 2, 4>: the 128 x 128 tile.  <1, 4, 2>: a 64 x 128 tile of 64 x 32 warp
 // tiles (8 x 8 outputs per lane, three CTAs per SM) and <1, 4, 1>: a 64 x 64 tile of 64 x 16 warp
 // tiles (8 x 4 outputs per lane, five CTAs per SM) for problems with few tiles.
-template <bool PACKED, int WARPS_M, int WARPS_N, int NV>
+//
+// KSPLIT (64-row tiles only): the kernel is launched in clusters of S = 2 or 4 CTAs that share one output tile; CTA s
+// of a cluster multiplies the s-th of S equal ranges of K.  The partial tiles are then added through distributed
+// shared memory: the operand buffers, free after the main loop, become S slabs of 64 / S rows; every CTA stores its
+// partial of row slab r into slab [its own s] of CTA r (st.shared::cluster), and after a cluster barrier CTA r adds its
+// S slabs in the order s = 0, 1, ... and writes alpha * sum + beta * C for its rows.  No workspace, no flags, and the
+// order of the additions is fixed, so the result does not depend on timing; it differs from the unsplit forms' in
+// rounding (each range is summed on its own first).
+template <bool PACKED, int WARPS_M, int WARPS_N, int NV, bool KSPLIT = false>
 __global__ void __launch_bounds__(k5::THREADS, NV == 4 ? 2 : (NV == 2 ? 3 : 5))
 my_sgemm_kernel_5(int M, int N, int K, float alpha, float* A, float* B, float beta, float* C, int num_blocks_N) {
     using namespace k5;
     static_assert(WARPS_M * WARPS_N == WARPS, "four warps");
+    static_assert(!KSPLIT || WARPS_M == 1, "the k-split forms have 64-row tiles");
     constexpr int BM = 64 * WARPS_M;          // rows of the CTA tile (shadows k5::BM)
     constexpr int WN = 16 * NV;               // columns of a warp tile
     constexpr int TILE_N = WARPS_N * WN;      // columns of the CTA tile
     constexpr int A_STRIDE = BM + 4;          // floats between consecutive k in the transposed A slice
     constexpr int A_CH = BM * BK / 4 / THREADS;      // 16-byte chunks of A per thread per slice (4 or 2)
     constexpr int B_CH = BK * TILE_N / 4 / THREADS;  // 16-byte chunks of B per thread per slice (4)
-    __shared__ __align__(16) float As[2][BK * A_STRIDE];
-    __shared__ __align__(16) float Bs[2][BK * TILE_N];
+    constexpr int A_FLOATS = 2 * BK * A_STRIDE, B_FLOATS = 2 * BK * TILE_N;
+    constexpr int POOL = (KSPLIT && BM * TILE_N > A_FLOATS + B_FLOATS) ? BM * TILE_N : A_FLOATS + B_FLOATS;
+    __shared__ __align__(16) float pool[POOL];
+    float (*As)[BK * A_STRIDE] = reinterpret_cast<float (*)[BK * A_STRIDE]>(pool);
+    float (*Bs)[BK * TILE_N] = reinterpret_cast<float (*)[BK * TILE_N]>(pool + A_FLOATS);
 
-    const int row0 = (static_cast<int>(blockIdx.x) / num_blocks_N) * BM;
-    const int col0 = (static_cast<int>(blockIdx.x) % num_blocks_N) * TILE_N;
+    const int slices = KSPLIT ? static_cast<int>(cluster_size()) : 1;
+    const int slice = KSPLIT ? static_cast<int>(cluster_rank()) : 0;
+    const int tile = static_cast<int>(blockIdx.x) / slices;
+    const int row0 = (tile / num_blocks_N) * BM;
+    const int col0 = (tile % num_blocks_N) * TILE_N;
+    const int k_begin = slice * (K / slices), k_end = k_begin + K / slices;
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int tm = lane & 7;
@@ -341,16 +378,16 @@ my_sgemm_kernel_5(int M, int N, int K, float alpha, float* A, float* B, float be
             for (int j = 0; j < 4 * NV; ++j) acc[i][j] = 0.f;
     }
 
-    load_a(0);
-    copy_b(0, 0);
+    load_a(k_begin);
+    copy_b(k_begin, 0);
     store_a(0);
     cp_async_wait_all();
     __syncthreads();
 
     int buf = 0;
-    for (int k0 = 0; k0 < K; k0 += BK) {
+    for (int k0 = k_begin; k0 < k_end; k0 += BK) {
         // The other buffer was last read before the barrier that ended the previous slice.
-        const bool more = k0 + BK < K;
+        const bool more = k0 + BK < k_end;
         if (more) {
             load_a(k0 + BK);
             copy_b(k0 + BK, buf ^ 1);
@@ -396,6 +433,63 @@ my_sgemm_kernel_5(int M, int N, int K, float alpha, float* A, float* B, float be
         cp_async_wait_all();
         __syncthreads();
         buf ^= 1;
+    }
+
+    if constexpr (KSPLIT) {
+        // This CTA finishes row slab `slice` of the tile: slab_rows x TILE_N outputs, MAX_OUT 16-byte pieces per
+        // thread at most (S = 2).  Their old values of C are fetched now, so that the loads are in flight while the
+        // partial sums travel.
+        constexpr int MAX_OUT = (BM / 2) * (TILE_N / 4) / THREADS;
+        const int slab_shift = 6 - (slices >> 1);          // 64 / S rows per slab, S = 2 or 4
+        const int slab_rows = 1 << slab_shift;
+        const int outs = slab_rows * (TILE_N / 4);
+        float4 old[MAX_OUT];
+#pragma unroll
+        for (int n = 0; n < MAX_OUT; ++n) {
+            const int e = threadIdx.x + n * THREADS;
+            if (e < outs)
+                old[n] = *reinterpret_cast<const float4*>(C + static_cast<size_t>(row0 + slice * slab_rows + e / (TILE_N / 4)) * N +
+                                                          col0 + (e % (TILE_N / 4)) * 4);
+        }
+        // Every CTA of the cluster is past its main loop (its pool is free) before anyone stores into it.
+        cluster_barrier();
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int r = i < 4 ? tm * 4 + i : 32 + tm * 4 + (i - 4);
+            const float* slot = pool + ((slice << slab_shift) + (r & (slab_rows - 1))) * TILE_N + wn0 + tn * 4;
+#pragma unroll
+            for (int j = 0; j < NV; ++j) {
+                float r0, r1, r2, r3;
+                if constexpr (PACKED) {
+                    unpack2(acc2[i][2 * j + 0], r0, r1);
+                    unpack2(acc2[i][2 * j + 1], r2, r3);
+                } else {
+                    r0 = acc[i][4 * j + 0]; r1 = acc[i][4 * j + 1]; r2 = acc[i][4 * j + 2]; r3 = acc[i][4 * j + 3];
+                }
+                store_cluster_f4(slot + j * 16, static_cast<uint32_t>(r >> slab_shift), r0, r1, r2, r3);
+            }
+        }
+        cluster_barrier();
+        // S partial slabs of slab_rows x TILE_N, added in the order of the k ranges.
+#pragma unroll
+        for (int n = 0; n < MAX_OUT; ++n) {
+            const int e = threadIdx.x + n * THREADS;
+            if (e < outs) {
+                const int lr = e / (TILE_N / 4), c4 = e % (TILE_N / 4);
+                float4 sum = *reinterpret_cast<const float4*>(pool + lr * TILE_N + c4 * 4);
+                for (int sl = 1; sl < slices; ++sl) {
+                    const float4 p = *reinterpret_cast<const float4*>(pool + ((sl << slab_shift) + lr) * TILE_N + c4 * 4);
+                    sum.x += p.x; sum.y += p.y; sum.z += p.z; sum.w += p.w;
+                }
+                float4 v = old[n];
+                v.x = alpha * sum.x + beta * v.x;
+                v.y = alpha * sum.y + beta * v.y;
+                v.z = alpha * sum.z + beta * v.z;
+                v.w = alpha * sum.w + beta * v.w;
+                *reinterpret_cast<float4*>(C + static_cast<size_t>(row0 + slice * slab_rows + lr) * N + col0 + c4 * 4) = v;
+            }
+        }
+        return;
     }
 
     // C = alpha * acc + beta * C, 16 bytes at a time.
@@ -459,6 +553,7 @@ int launch_generic(int M, int N, int K, float alpha, const float* A, const float
 bool g_k5_scalar = false;  // PRISM_B200_SGEMM_SCALAR=1 selects the plain fmaf form of kernel 5 (same bits, slower)
 bool g_k5_env_read = false;
 int g_k5_tile_mode = -1;   // prism_b200_sgemm_tile_mode: -1 = by shape, 0 / 1 / 2 = 128 x 128 / 64 x 128 / 64 x 64 (tests)
+int g_k5_slices = -1;      // prism_b200_sgemm_k_slices: -1 = by shape, 1 / 2 / 4 = CTAs that share a tile along K (tests)
 
 }  // namespace
 }  // namespace prism_b200
@@ -469,6 +564,14 @@ extern "C" int prism_b200_sgemm_tile_mode(int mode) {
     if (mode < -1 || mode > 2) return set_error(PRISM_B200_ERR_INVALID_ARGUMENT, "sgemm_tile_mode: -1, 0, 1 or 2");
     std::lock_guard<std::mutex> lk(g_sgemm_mu);
     g_k5_tile_mode = mode;
+    return PRISM_B200_OK;
+}
+
+extern "C" int prism_b200_sgemm_k_slices(int slices) {
+    if (slices != -1 && slices != 1 && slices != 2 && slices != 4)
+        return set_error(PRISM_B200_ERR_INVALID_ARGUMENT, "sgemm_k_slices: -1, 1, 2 or 4");
+    std::lock_guard<std::mutex> lk(g_sgemm_mu);
+    g_k5_slices = slices;
     return PRISM_B200_OK;
 }
 
@@ -529,14 +632,43 @@ extern "C" int prism_b200_sgemm(int kernel_id, int M, int N, int K, float alpha,
                     g_k5_env_read = true;
                 }
             }
-            // Few tiles: a smaller tile puts more SMs, and more warps per SM, to work.  Every form adds the
-            // products of one output element in the same k order, so all give the same bits.
-            //   0  128 x 128   1  64 x 128 (fewer 128 x 128 tiles than half the SMs)   2  64 x 64 (fewer than a quarter)
-            const long long tiles = static_cast<long long>(M / k5::BM) * (N / k5::BN);
-            int form = g_k5_tile_mode;
-            // Measured on a B200 (TFLOP/s, 128 x 128 / 64 x 128 / 64 x 64 tiles, single launches): 512^3 4.2 / 6.4 / 7.6,
-            // 768^3 10.8 / 16.8 / 20.6, 1024^3 20.4 / 32.4 / 27.3, 1536^3 48.4 / 47.3 / 38.6, 4096^3 62.4 / 59.8 / 45.0.
-            if (form < 0) form = 4 * tiles <= sm_count() ? 2 : (2 * tiles <= sm_count() ? 1 : 0);
+            // Which tile (0: 128 x 128, 1: 64 x 128, 2: 64 x 64) and how many CTAs per tile along K (1, 2 or 4; the 64-row
+            // tiles only): the candidate with the shortest estimated makespan.  An SM works through ceil(CTAs / SMs) CTAs
+            // of K / S k-steps each (plus a fixed start-up and write-out cost, larger where partial tiles are exchanged), at
+            // a cost per k-step that follows the tile's area and its measured rate at 4096^3 (62.4 / 59.8 / 45.0 TFLOP/s),
+            // raised where an SM holds only one or two CTAs at a time.
+            // On a B200 this estimate ranks the candidates as measured within a few per cent from 512^3 to 4096^3 and
+            // for 512 ... 2048 x 4096 x 4096: e.g. 1280^3 36.3 -> 46.2 TFLOP/s and 2048^3 51.6 -> 56.5 with 64 x 128
+            // tiles shared by two CTAs (7 rounds of half-length CTAs instead of 2 rounds of 128 x 128 ones), 512^3
+            // 11.5 -> 18.8 shared by four.  The unshared forms add one element's products in the same k order and give
+            // the same bits; a shared tile sums each range of K first.
+            int form = g_k5_tile_mode, slices = g_k5_slices;
+            {
+                const int sms = sm_count();
+                const int want_form = form, want_slices = form == 0 ? 1 : slices;
+                double best = 0.0;
+                for (int f = 0; f < 3; ++f) {
+                    if (want_form >= 0 && f != want_form) continue;
+                    const long long ctas = static_cast<long long>(M / (f == 0 ? 128 : 64)) * (N / (f == 2 ? 64 : 128));
+                    const double per_step = f == 0 ? 2.0 / 1.043 : (f == 1 ? 1.0 : 0.5 / 0.75);
+                    for (int sl = 1; sl <= (f == 0 ? 1 : 4); sl *= 2) {
+                        // a request for S CTAs is halved until K divides; without a request only dividing S are candidates
+                        if (K % (k5::BK * sl) != 0) continue;
+                        if (want_slices > 0 && sl > want_slices) continue;
+                        const long long rounds = (ctas * sl + sms - 1) / sms;
+                        // one four-warp CTA alone on an SM cannot hide its own latencies; two hide most of them
+                        const double alone = f == 0 ? (rounds >= 2 ? 1.0 : 0.9) : (rounds >= 3 ? 1.0 : (rounds == 2 ? 0.95 : 0.88));
+                        double cost = static_cast<double>(rounds) * (static_cast<double>(K / sl) + (sl == 1 ? 32.0 : 48.0)) *
+                                      per_step / alone;
+                        if (want_slices > 0) cost = -static_cast<double>(sl);      // forced: the largest S that divides
+                        if (best == 0.0 || cost < best) {
+                            best = cost;
+                            form = f;
+                            slices = sl;
+                        }
+                    }
+                }
+            }
             void (*kern)(int, int, int, float, float*, float*, float, float*, int) =
                 form == 2   ? (g_k5_scalar ? my_sgemm_kernel_5<false, 1, 4, 1> : my_sgemm_kernel_5<true, 1, 4, 1>)
                 : form == 1 ? (g_k5_scalar ? my_sgemm_kernel_5<false, 1, 4, 2> : my_sgemm_kernel_5<true, 1, 4, 2>)
@@ -544,8 +676,26 @@ extern "C" int prism_b200_sgemm(int kernel_id, int M, int N, int K, float alpha,
             const int tile_n = form == 2 ? 64 : 128;
             const int nbn = N / tile_n;
             const long long blocks = static_cast<long long>(M / (form == 0 ? 128 : 64)) * nbn;
-            kern<<<static_cast<unsigned>(blocks), k5::THREADS, 0, s>>>(
-                M, N, K, alpha, const_cast<float*>(A), const_cast<float*>(B), beta, C, nbn);
+            if (slices > 1) {
+                kern = form == 2 ? (g_k5_scalar ? my_sgemm_kernel_5<false, 1, 4, 1, true> : my_sgemm_kernel_5<true, 1, 4, 1, true>)
+                                 : (g_k5_scalar ? my_sgemm_kernel_5<false, 1, 4, 2, true> : my_sgemm_kernel_5<true, 1, 4, 2, true>);
+                cudaLaunchConfig_t cfg{};
+                cudaLaunchAttribute attr[1];
+                cfg.gridDim = dim3(static_cast<unsigned>(blocks * slices));
+                cfg.blockDim = dim3(k5::THREADS);
+                cfg.stream = s;
+                attr[0].id = cudaLaunchAttributeClusterDimension;
+                attr[0].val.clusterDim.x = static_cast<unsigned>(slices);
+                attr[0].val.clusterDim.y = 1;
+                attr[0].val.clusterDim.z = 1;
+                cfg.attrs = attr;
+                cfg.numAttrs = 1;
+                PRISM_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, M, N, K, alpha, const_cast<float*>(A), const_cast<float*>(B), beta, C,
+                                                  nbn));
+            } else {
+                kern<<<static_cast<unsigned>(blocks), k5::THREADS, 0, s>>>(
+                    M, N, K, alpha, const_cast<float*>(A), const_cast<float*>(B), beta, C, nbn);
+            }
         } else {
             rc = launch_generic(M, N, K, alpha, A, B, beta, C, s);
         }

@@ -71,7 +71,16 @@ def test_host_sgemm_blocks(pb):
     op(1.5, ah, bh, 0.5, ch)
     torch.cuda.synchronize()
     assert O.sgemm_rel_error(ch.numpy(), O.sgemm_cpu(1.5, A, B, 0.5, C)) <= O.SGEMM_TOL
-    c = torch.from_numpy(C).to(DEV)
-    pb.run_my_kernel(5, M, N, K, 1.5, torch.from_numpy(A).to(DEV), torch.from_numpy(B).to(DEV), 0.5, c)
-    torch.cuda.synchronize()
+    # With no tile shared along K every tile form adds one element's products in the same order, so the plan's
+    # blocks of rows and a whole-matrix call give the same bits whichever tiles they pick.
+    lib = pb.load()
+    try:
+        assert lib.prism_b200_sgemm_k_slices(1) == 0
+        ch.copy_(torch.from_numpy(C))
+        op(1.5, ah, bh, 0.5, ch)
+        c = torch.from_numpy(C).to(DEV)
+        pb.run_my_kernel(5, M, N, K, 1.5, torch.from_numpy(A).to(DEV), torch.from_numpy(B).to(DEV), 0.5, c)
+        torch.cuda.synchronize()
+    finally:
+        lib.prism_b200_sgemm_k_slices(-1)
     assert torch.equal(ch, c.cpu())

@@ -85,10 +85,10 @@ def test_kernel5_scalar_and_packed_fma_agree(pb, monkeypatch):
 
 
 def test_kernel5_every_tile_form(pb):
-    """Kernel 5 runs 128 x 128 tiles, 64 x 128 tiles when fewer than half the SMs would get a tile, and 64 x 64
-    tiles when fewer than a quarter would.  1152 x 1152 (81 tiles of 128 x 128) takes the first form, its top 512 rows
-    (36 tiles) the second and its top 256 rows (18 tiles) the third; all are checked against fp64 and, having the same k
-    order per element, against each other bit for bit.  Then each form is forced on the whole matrix."""
+    """Kernel 5 has 128 x 128, 64 x 128 and 64 x 64 tiles and picks by an estimate of the makespan, so 1152 x 1152, its
+    top 512 rows and its top 256 rows need not run the same form (K = 80 is no multiple of 32, so no tile is shared
+    along K here).  All are checked against fp64 and, having the same k order per element, against each other bit for
+    bit.  Then each form is forced on the whole matrix."""
     M, N, K = 1152, 1152, 80
     A, B, C = O.sgemm_inputs(M, N, K, seed=1152)
     big = _run(pb, 5, 1.5, A, B, 0.5, C)
@@ -105,6 +105,41 @@ def test_kernel5_every_tile_form(pb):
         pb.clear_error()
     finally:
         lib.prism_b200_sgemm_tile_mode(-1)
+
+
+@pytest.mark.parametrize("form", [1, 2])
+@pytest.mark.parametrize("K", [1024, 1056, 1040])
+def test_kernel5_tiles_shared_along_k(pb, form, K):
+    """Clusters of 2 or 4 CTAs multiply one range of K each and add their partial tiles through distributed shared
+    memory.  K = 1024 divides for 2 and 4 CTAs, 1056 = 16 * 66 only for 2 (a request for 4 runs with 2), 1040 = 16 * 65 for
+    neither (runs unshared).  Every result is within the bound of fp64, equal on a second run bit for bit, and -- on
+    small integers, where every sum is exact -- equal to the exact product, which pins which CTA writes which rows."""
+    M, N = 320, 640
+    A, B, C = O.sgemm_inputs(M, N, K, seed=K + form)
+    ref = O.sgemm_cpu(1.5, A, B, 0.5, C)
+    rng = np.random.default_rng(K)
+    Ai, Bi, Ci = (rng.integers(-2, 3, shp).astype(np.float32) for shp in ((M, K), (K, N), (M, N)))
+    exact = (Ai.astype(np.float64) @ Bi.astype(np.float64) + Ci).astype(np.float32)
+    lib = pb.load()
+    outs = {}
+    try:
+        assert lib.prism_b200_sgemm_tile_mode(form) == 0
+        for slices in (1, 2, 4):
+            assert lib.prism_b200_sgemm_k_slices(slices) == 0
+            out = _run(pb, 5, 1.5, A, B, 0.5, C)
+            assert O.sgemm_rel_error(out, ref) <= O.SGEMM_TOL, slices
+            assert np.array_equal(out, _run(pb, 5, 1.5, A, B, 0.5, C)), slices
+            assert np.array_equal(_run(pb, 5, 1.0, Ai, Bi, 1.0, Ci), exact), slices
+            outs[slices] = out
+        assert lib.prism_b200_sgemm_k_slices(3) == 1
+        pb.clear_error()
+    finally:
+        lib.prism_b200_sgemm_tile_mode(-1)
+        lib.prism_b200_sgemm_k_slices(-1)
+    if K == 1056:
+        assert np.array_equal(outs[2], outs[4])        # four CTAs do not divide K: two are used
+    if K == 1040:
+        assert np.array_equal(outs[1], outs[2]) and np.array_equal(outs[1], outs[4])
 
 
 @pytest.mark.parametrize("k", KERNELS)

@@ -112,6 +112,24 @@ def build_evals() -> Path:
     return evals / "build"
 
 
+def build_generated_tile_gemm(force: bool = False) -> Path:
+    """Compile the kernel that the Prism generator emitted for sm_100a (prism_b200/codegen/generated/tile_gemm.cu)
+    into a shared library of its own beside the source; it is an example of the code-generation target, not part
+    of libprism_b200.so."""
+    src = PKG_DIR / "codegen" / "generated" / "tile_gemm.cu"
+    out = src.with_name("libtile_gemm.so")
+    if not force and out.exists() and out.stat().st_mtime >= src.stat().st_mtime:
+        return out
+    tmp = out.with_suffix(".so.tmp")
+    cmd = [_nvcc(), *NVCC_FLAGS, "-diag-suppress", "177", "-shared", str(src), "-o", str(tmp)]
+    r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if r.returncode != 0:
+        sys.stdout.write(r.stdout)
+        raise RuntimeError("codegen/generated/tile_gemm.cu: compilation failed")
+    os.replace(tmp, out)
+    return out
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--force", action="store_true")

@@ -21,13 +21,17 @@ What is here:
   b200_helpers.py  the device helpers a generated kernel calls (mbarrier init / expect / arrive / bounded wait,
                    2-D TMA load, tensor-memory alloc / free, tcgen05 fences), written in the Prism language
                    like the reference's examples/h100_helpers.py and emitted by the reference's own generator.
-  b200_mma_step.py a small Prism program that issues the four MMAs of one 64-wide k-block through the new
-                   intrinsic.
+  b200_mma_step.py small Prism programs on the new intrinsics: the four MMAs of one 64-wide k-block with the commit
+                   that frees the stage, the commit that tells the epilogue a tile is complete, and the read of an
+                   accumulator row out of tensor memory.
+  make_tile_gemm.py  writes generated/tile_gemm.cu: those functions, the helpers and the barrier set-up as emitted,
+                   plus hand-written control flow and a host launcher -- a complete bf16 GEMM kernel, kept in the
+                   tree like the reference's generated/*.cu, that a GPU test runs against the fp64 oracle.
 
 The Prism compiler itself is not part of this package: `import_prism()` puts a checkout of it on the path
 (argument, else the environment variable PRISM_REFERENCE, else a sibling directory `reference`).  Nothing on
 the kernel path of `prism_b200` imports this sub-package; it produces CUDA source text, which
-tests/test_codegen_b200.py checks and cross-compiles for sm_100a.
+tests/test_codegen_b200.py checks, cross-compiles for sm_100a and, for generated/tile_gemm.cu, runs on the GPU.
 """
 from __future__ import annotations
 

@@ -33,17 +33,30 @@ def tcgen05_k_block(tmem_d: uint32_t @ thread[1],
     return
 
 
-# Epilogue step: 32 fp32 columns of each lane's accumulator row, from tensor memory to `out` (lane-major, 32 words
-# per lane), as bit patterns.  (A comment, not a docstring: the generator would emit a string statement as code.)
+# Tells the epilogue that a tile is complete: one tcgen05.commit on the accumulator's "full" barrier, which arrives
+# once every MMA issued so far by this thread has finished.  (A comment, not a docstring: the generator would emit a
+# string statement as code.)
+@attr("static __forceinline__")
+@requires(thread[1])
+@prism("device")
+def tcgen05_signal(bar: ptr(uint64_t) @ block[1]):
+    with group(thread[1]):
+        intrinsic.tcgen05_commit(bar, cta_group=1)
+    return
+
+
+# Epilogue step: 32 fp32 columns of each lane's accumulator row, from tensor memory to `out` (lane l writes 32
+# consecutive words at out + l * stride), as bit patterns.
 @attr("static __forceinline__")
 @requires(thread[32])
 @prism("device")
 def tmem_row_to_global(taddr: uint32_t @ thread[32],
-                       out: ptr(uint32_t) @ thread[32]):
+                       out: ptr(uint32_t) @ thread[32],
+                       stride: int @ thread[32]):
     with group(thread[32]):
         lane: int @ thread[1] = id()
         r: uint32_t[32] @ thread[1]
         intrinsic.tmem_ld32(taddr, out=[r])
         for c in range(0, 32, 1):
-            unsafe("out[lane * 32 + c] = r[c];")
+            unsafe("out[lane * stride + c] = r[c];")
     return

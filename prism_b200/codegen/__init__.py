@@ -26,7 +26,7 @@ What is here:
                    accumulator row out of tensor memory.
   make_tile_gemm.py  writes generated/tile_gemm.cu: those functions, the helpers and the barrier set-up as emitted,
                    plus hand-written control flow and a host launcher -- a complete bf16 GEMM kernel, kept in the
-                   tree like the reference's generated/*.cu, that a GPU test runs against the fp64 oracle.
+                   tree like the reference's generated/*.cu, that a GPU test compares with the product in float64.
 
 The Prism compiler itself is not part of this package: `import_prism()` puts a checkout of it on the path
 (argument, else the environment variable PRISM_REFERENCE, else a sibling directory `reference`).  Nothing on

@@ -13,7 +13,9 @@ taken by `tcgen05.mma` with accumulators in tensor memory, which changes three t
     empty barriers with count 1 and needs no initial consumer arrive;
   * tensor memory has to be allocated by one warp, published through shared memory, and freed before the CTA
     exits                                     -> `BarrierSetup` also emits the allocation and the base address, and
-    `intrinsic.tmem_ld32(...)` reads an accumulator row for the epilogue.
+    `intrinsic.tmem_ld32(...)` reads an accumulator row for the epilogue;
+  * swizzled TMA stages and tcgen05 operand descriptors need 1024-byte-aligned shared memory
+                                              -> a kernel's dynamic shared memory is declared with that alignment.
 
 What is here:
   target.py        `B200CodeGenerator`, a subclass of the reference's `CodeGenerator` with those emissions, and
@@ -24,9 +26,11 @@ What is here:
   b200_mma_step.py small Prism programs on the new intrinsics: the four MMAs of one 64-wide k-block with the commit
                    that frees the stage, the commit that tells the epilogue a tile is complete, and the read of an
                    accumulator row out of tensor memory.
-  make_tile_gemm.py  writes generated/tile_gemm.cu: those functions, the helpers and the barrier set-up as emitted,
-                   plus hand-written control flow and a host launcher -- a complete bf16 GEMM kernel, kept in the
-                   tree like the reference's generated/*.cu, that a GPU test compares with the product in float64.
+  b200_tile_gemm.py  a whole kernel in the Prism language: a bf16 GEMM, one 128 x 128 tile per CTA, whose 192 threads
+                   `match split(thread)` divides into epilogue warps, a TMA producer and a tcgen05.mma issuer.
+  make_tile_gemm.py  writes generated/tile_gemm.cu: that kernel and everything it calls, as emitted, plus a hand-written
+                   host launcher -- kept in the tree like the reference's generated/*.cu; a GPU test compares its
+                   output with the product in float64.
 
 The Prism compiler itself is not part of this package: `import_prism()` puts a checkout of it on the path
 (argument, else the environment variable PRISM_REFERENCE, else a sibling directory `reference`).  Nothing on

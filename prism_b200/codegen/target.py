@@ -8,7 +8,10 @@ Overridden or added, each next to the reference emission it stands in for:
   _emit_tcgen05_mma      the counterpart of `_emit_wgmma256` (prism/codegen.py:663-679): where that emits a call of
                          the harness's `wgmma<256, ...>` template, this emits the PTX itself, as `_emit_mma` does for
                          mma.sync (prism/codegen.py:627-661), because one instruction is the whole operation;
-  visit_BarrierSetup     the counterpart of prism/codegen.py:904-940 for a tcgen05 pipeline (see the method).
+  visit_BarrierSetup     the counterpart of prism/codegen.py:904-940 for a tcgen05 pipeline (see the method);
+  _emit                  raises the alignment of a kernel's dynamic shared memory from the reference's 128 bytes
+                         (prism/codegen.py:365) to 1024: a stage that TMA fills in the 128-byte-swizzled layout and a
+                         tcgen05 operand descriptor both need 1024-byte-aligned shared memory.
 The waits, expects, arrives and phase flips of the reference (prism/codegen.py:861-902) are emitted unchanged:
 they call `wait`, `expect_bytes`, `arrive`, which b200_helpers.py provides under the same names and argument
 lists (its `wait` is bounded).
@@ -32,6 +35,11 @@ __device__ unsigned int prism_b200_wait_gave_up;   // raised by wait() after abo
 
 
 class B200CodeGenerator(CodeGenerator):
+    def _emit(self, line: str = "") -> None:
+        if line == "extern __shared__ __align__(128) char __smem[];":
+            line = "extern __shared__ __align__(1024) char __smem[];"
+        super()._emit(line)
+
     # -- intrinsics ---------------------------------------------------------------------------
 
     def visit_Expr(self, node: ast.Expr) -> None:

@@ -159,16 +159,25 @@ def test_generated_kernel_file_names_its_parts():
                  "tcgen05_signal", "tmem_row_to_global"):
         assert text.index(f"void {name}(int __block_id, int __thread_id, char* __smem") < glue, name
     assert "tcgen05.mma.cta_group::1.kind::f16" in text[:glue] and "tcgen05.mma" not in text[glue:]
+    # the kernel itself is emitted text too, between the two hand-written sections
+    kernel = text.index("__global__ __launch_bounds__(192, 1) void prism_tile_gemm(")
+    assert glue < kernel < text.index("glue written by hand (host side)")
+    body = text[kernel:text.index("glue written by hand (host side)")]
+    assert "extern __shared__ __align__(1024) char __smem[];" in body
+    for call in ("init_barrier(", "tmem_alloc(", "wait(", "expect_bytes(", "load_async(", "tcgen05_k_block(", "tcgen05_signal(",
+                 "tmem_row_to_global(", "tmem_dealloc("):
+        assert call in body, call
+    assert body.count("if (__thread_id_3 >= 0 && __thread_id_3 < ") == 3          # epilogue, producer and issuer roles
     assert "multicast" not in text and "wgmma" not in text and "prism_b200_wait_gave_up = 1u" in text
     from prism_b200 import build
     assert build.build_generated_tile_gemm(force=True).exists()
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("shape", [(128, 128, 64), (256, 384, 512), (1024, 512, 2048), (128, 256, 8192)])
+@pytest.mark.parametrize("shape", [(128, 128, 64), (256, 384, 512), (1024, 512, 2048), (128, 256, 8192), (256, 128, 192)])
 def test_generated_kernel_runs_on_the_gpu_and_matches_fp64(shape):
-    """The kernel made of generator-emitted device code (TMA loads onto mbarriers, tcgen05.mma into tensor memory, a
-    commit per stage, tcgen05.ld in the epilogue) on a B200: fp32 sums of exact bf16 products, so every element is within
+    """The kernel that the generator emitted from the Prism program b200_tile_gemm.py (TMA loads onto mbarriers,
+    tcgen05.mma into tensor memory, a commit per stage, tcgen05.ld in the epilogue) on a B200: fp32 sums of exact bf16 products, so every element is within
     K * 2^-23 * sum |b||a| of the fp64 product; on small integers it is exact, which pins the D[n * M + m] layout, the
     operand roles and the order of the stages."""
     import ctypes

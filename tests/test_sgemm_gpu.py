@@ -114,7 +114,7 @@ def test_kernel5_tiles_shared_along_k(pb, form, K):
     memory.  K = 1024 divides for 2 and 4 CTAs, 1056 = 16 * 66 only for 2 (a request for 4 runs with 2), 1040 = 16 * 65 for
     neither (runs unshared).  Every result is within the bound of fp64, equal on a second run bit for bit, and -- on
     small integers, where every sum is exact -- equal to the exact product, which pins which CTA writes which rows."""
-    M, N = 320, 640
+    M, N = 384, 640                    # multiples of 128: kernel 5's tiled forms (6 x 5 or 6 x 10 tiles)
     A, B, C = O.sgemm_inputs(M, N, K, seed=K + form)
     ref = O.sgemm_cpu(1.5, A, B, 0.5, C)
     rng = np.random.default_rng(K)
@@ -136,6 +136,8 @@ def test_kernel5_tiles_shared_along_k(pb, form, K):
     finally:
         lib.prism_b200_sgemm_tile_mode(-1)
         lib.prism_b200_sgemm_k_slices(-1)
+    if K == 1024:
+        assert not np.array_equal(outs[1], outs[2])    # the shared forms did run: each range of K is rounded on its own
     if K == 1056:
         assert np.array_equal(outs[2], outs[4])        # four CTAs do not divide K: two are used
     if K == 1040:

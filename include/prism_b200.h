@@ -116,6 +116,15 @@ int prism_b200_sgemm_tile_mode(int mode);
  */
 int prism_b200_sgemm_k_slices(int slices);
 
+/*
+ * What the launcher of kernel 5 would take for an M x N x K problem on a device with `sms` SMs, under the two switches
+ * above: *tile = 0 / 1 / 2 (128 x 128 / 64 x 128 / 64 x 64) and *slices = 1 / 2 / 4, or *tile = -1 where no tiled form
+ * divides the shape (M, N multiples of 128 and K of 16 are needed) and the bounds-checked kernel runs.  Host-side
+ * arithmetic only (no GPU needed); the estimate is rounds of CTAs per SM x (K / slices + a fixed cost) x the tile's cost
+ * per k-step, raised where an SM holds only one or two CTAs.  No counterpart in the reference.
+ */
+int prism_b200_sgemm_plan(int M, int N, int K, int sms, int* tile, int* slices);
+
 /* ---- uint32 inclusive scan (single pass, decoupled look-back) ------------- */
 
 /*

@@ -33,6 +33,7 @@ SIGNATURES = {
     "prism_b200_sgemm": (c_int, [c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_float, c_void_p, c_void_p]),
     "prism_b200_sgemm_tile_mode": (c_int, [c_int]),
     "prism_b200_sgemm_k_slices": (c_int, [c_int]),
+    "prism_b200_sgemm_plan": (c_int, [c_int, c_int, c_int, c_int, POINTER(c_int), POINTER(c_int)]),
     "prism_b200_scan_workspace_size": (c_int, [c_size_t, POINTER(c_size_t)]),
     "prism_b200_scan": (c_int, [c_size_t, c_void_p, c_void_p, c_void_p]),
     "prism_b200_scan_f32": (c_int, [c_size_t, c_void_p, c_void_p, c_void_p]),

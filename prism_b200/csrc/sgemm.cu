@@ -555,6 +555,37 @@ bool g_k5_env_read = false;
 int g_k5_tile_mode = -1;   // prism_b200_sgemm_tile_mode: -1 = by shape, 0 / 1 / 2 = 128 x 128 / 64 x 128 / 64 x 64 (tests)
 int g_k5_slices = -1;      // prism_b200_sgemm_k_slices: -1 = by shape, 1 / 2 / 4 = CTAs that share a tile along K (tests)
 
+// Kernel 5's tile (0: 128 x 128, 1: 64 x 128, 2: 64 x 64) and the CTAs per tile along K (1, 2 or 4; the 64-row tiles
+// only) for an M x N x K problem that the tiled forms divide, on a device with `sms` SMs: the candidate with the
+// shortest estimated makespan.  want_form >= 0 restricts the tile; want_slices > 0 fixes the sharing (halved until
+// K divides into 16-wide steps per CTA).
+void k5_plan(int M, int N, int K, int sms, int want_form, int want_slices, int* form, int* slices) {
+    double best = -1.0;
+    for (int f = 0; f < 3; ++f) {
+        if (want_form >= 0 && f != want_form) continue;
+        const long long ctas = static_cast<long long>(M / (f == 0 ? 128 : 64)) * (N / (f == 2 ? 64 : 128));
+        const double per_step = f == 0 ? 2.0 / 1.043 : (f == 1 ? 1.0 : 0.5 / 0.75);
+        const int most = f == 0 ? 1 : 4;
+        int fixed = 0;
+        if (want_slices > 0) {
+            fixed = want_slices < most ? want_slices : most;
+            while (fixed > 1 && K % (k5::BK * fixed) != 0) fixed >>= 1;
+        }
+        for (int sl = 1; sl <= most; sl *= 2) {
+            if (fixed ? sl != fixed : K % (k5::BK * sl) != 0) continue;
+            const long long rounds = (ctas * sl + sms - 1) / sms;
+            // one four-warp CTA alone on an SM cannot hide its own latencies; two hide most of them
+            const double alone = f == 0 ? (rounds >= 2 ? 1.0 : 0.9) : (rounds >= 3 ? 1.0 : (rounds == 2 ? 0.95 : 0.88));
+            const double cost = static_cast<double>(rounds) * (static_cast<double>(K / sl) + (sl == 1 ? 32.0 : 48.0)) * per_step / alone;
+            if (best < 0.0 || cost < best) {
+                best = cost;
+                *form = f;
+                *slices = sl;
+            }
+        }
+    }
+}
+
 }  // namespace
 }  // namespace prism_b200
 
@@ -572,6 +603,24 @@ extern "C" int prism_b200_sgemm_k_slices(int slices) {
         return set_error(PRISM_B200_ERR_INVALID_ARGUMENT, "sgemm_k_slices: -1, 1, 2 or 4");
     std::lock_guard<std::mutex> lk(g_sgemm_mu);
     g_k5_slices = slices;
+    return PRISM_B200_OK;
+}
+
+extern "C" int prism_b200_sgemm_plan(int M, int N, int K, int sms, int* tile, int* slices) {
+    if (!tile || !slices || M <= 0 || N <= 0 || K <= 0 || sms < 1)
+        return set_error(PRISM_B200_ERR_INVALID_ARGUMENT, "sgemm_plan: bad argument");
+    if (M % k5::BM || N % k5::BN || K % k5::BK) {
+        *tile = -1;      // no tiled form divides this shape: the bounds-checked kernel runs
+        *slices = 1;
+        return PRISM_B200_OK;
+    }
+    int want_form, want_slices;
+    {
+        std::lock_guard<std::mutex> lk(g_sgemm_mu);
+        want_form = g_k5_tile_mode;
+        want_slices = g_k5_slices;
+    }
+    k5_plan(M, N, K, sms, want_form, want_slices, tile, slices);
     return PRISM_B200_OK;
 }
 
@@ -642,33 +691,8 @@ extern "C" int prism_b200_sgemm(int kernel_id, int M, int N, int K, float alpha,
             // tiles shared by two CTAs (7 rounds of half-length CTAs instead of 2 rounds of 128 x 128 ones), 512^3
             // 11.5 -> 18.8 shared by four.  The unshared forms add one element's products in the same k order and give
             // the same bits; a shared tile sums each range of K first.
-            int form = g_k5_tile_mode, slices = g_k5_slices;
-            {
-                const int sms = sm_count();
-                const int want_form = form, want_slices = form == 0 ? 1 : slices;
-                double best = 0.0;
-                for (int f = 0; f < 3; ++f) {
-                    if (want_form >= 0 && f != want_form) continue;
-                    const long long ctas = static_cast<long long>(M / (f == 0 ? 128 : 64)) * (N / (f == 2 ? 64 : 128));
-                    const double per_step = f == 0 ? 2.0 / 1.043 : (f == 1 ? 1.0 : 0.5 / 0.75);
-                    for (int sl = 1; sl <= (f == 0 ? 1 : 4); sl *= 2) {
-                        // a request for S CTAs is halved until K divides; without a request only dividing S are candidates
-                        if (K % (k5::BK * sl) != 0) continue;
-                        if (want_slices > 0 && sl > want_slices) continue;
-                        const long long rounds = (ctas * sl + sms - 1) / sms;
-                        // one four-warp CTA alone on an SM cannot hide its own latencies; two hide most of them
-                        const double alone = f == 0 ? (rounds >= 2 ? 1.0 : 0.9) : (rounds >= 3 ? 1.0 : (rounds == 2 ? 0.95 : 0.88));
-                        double cost = static_cast<double>(rounds) * (static_cast<double>(K / sl) + (sl == 1 ? 32.0 : 48.0)) *
-                                      per_step / alone;
-                        if (want_slices > 0) cost = -static_cast<double>(sl);      // forced: the largest S that divides
-                        if (best == 0.0 || cost < best) {
-                            best = cost;
-                            form = f;
-                            slices = sl;
-                        }
-                    }
-                }
-            }
+            int form = 0, slices = 1;
+            k5_plan(M, N, K, sm_count(), g_k5_tile_mode, g_k5_slices, &form, &slices);
             void (*kern)(int, int, int, float, float*, float*, float, float*, int) =
                 form == 2   ? (g_k5_scalar ? my_sgemm_kernel_5<false, 1, 4, 1> : my_sgemm_kernel_5<true, 1, 4, 1>)
                 : form == 1 ? (g_k5_scalar ? my_sgemm_kernel_5<false, 1, 4, 2> : my_sgemm_kernel_5<true, 1, 4, 2>)

@@ -79,6 +79,9 @@ def build_reference(reference: str = DEFAULT_REFERENCE, force: bool = False) -> 
     relink = build_relinked_scan_main(ref, force)
     if relink is not None:
         built["relink_scan_main"] = relink
+    relink = build_relinked_h100_main(ref, force)
+    if relink is not None:
+        built["relink_h100_main"] = relink
     return built
 
 
@@ -112,6 +115,34 @@ def build_relinked_sgemm_sweep(ref: Path, force: bool = False) -> Path | None:
         _run([nvcc, "-arch=sm_100", "-O3", "-w", "-std=c++17", f"-I{main_cu.parent}", f"-I{HERE.parent / 'include'}",
               str(main_cu), str(runner), "-o", str(out), "-lcublas", f"-L{lib.parent}", "-lprism_b200",
               "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/../../prism_b200"])
+    return out
+
+
+def build_relinked_h100_main(ref: Path, force: bool = False) -> Path | None:
+    """The reference's own bf16 benchmark main, compiled from where it lies, on this library's `runmyh100`.
+
+    The program includes "utils.cuh" from its own directory, which is where the Hopper-only kernel lives; the
+    stand-in (oracle/relink_h100_utils.cuh) therefore goes, under that name, into a directory that holds nothing else
+    but a symbolic link to the reference's main.cu: a quoted include is looked up beside the file as it was named."""
+    main_cu = ref / "evals" / "h100_bench" / "main.cu"
+    lib = HERE.parent / "prism_b200" / "libprism_b200.so"
+    if not main_cu.exists() or not lib.exists():
+        return None
+    out = REF_OUT / "relink_h100_main"
+    stand_in = HERE / "relink_h100_utils.cuh"
+    if force or not _newer(out, [stand_in, lib]):
+        work = REF_OUT / "h100_relink"
+        work.mkdir(exist_ok=True)
+        link = work / "main.cu"
+        if link.is_symlink() or link.exists():
+            link.unlink()
+        link.symlink_to(main_cu)
+        shutil.copyfile(stand_in, work / "utils.cuh")
+        nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+        _run([nvcc, "-arch=sm_100", "-O3", "-w", "-std=c++17", f"-I{HERE.parent / 'include'}", str(link), "-o", str(out),
+              "-lcublas", "-lcuda", f"-L{lib.parent}", "-lprism_b200", "-Xlinker", "-rpath", "-Xlinker",
+              "$ORIGIN/../../prism_b200"])
+        shutil.rmtree(work)      # the link points into the reference checkout: nothing to keep, nothing to ship
     return out
 
 

@@ -99,6 +99,22 @@ def test_reference_scan_harness_relinked_against_this_library():
     assert m and float(m.group(1)) > 0
 
 
+def test_reference_bf16_benchmark_relinked_against_this_library():
+    """The reference's bf16 benchmark program (evals/h100_bench/main.cu, unmodified, compiled where a checkout of the
+    reference was present, with a stand-in for its Hopper-only utils.cuh that routes runmyh100 to this library):
+    its own comparison with cuBLAS (0.1 absolute on normal(0, 1) inputs) must pass at 2048 and at its default size
+    6144, and its two result lines must read the way the reference's plotting script reads them."""
+    exe = ROOT / "oracle" / "_ref" / "relink_h100_main"
+    if not exe.exists():
+        pytest.skip("oracle/_ref/relink_h100_main not built (needs a checkout of the reference at build time)")
+    for args, size in (([2048], 2048), ([], 6144)):
+        out = _run([exe, *args])
+        assert "Testing prism_h100::runmyh100" in out and "Passed correctness verification!" in out
+        assert "Divergence" not in out and "Failed" not in out
+        rows = L.bf16_rows(out)
+        assert len(rows) == 1 and rows[0][0] == size and rows[0][1] > 0 and rows[0][2] > 0
+
+
 def test_host_e2e_program_through_the_c_abi_alone(binaries):
     """Host plans driven from C++ with cudaHostAlloc'ed arrays (no Python on the data path), small sizes."""
     out = _run([binaries / "host_e2e", 1024, 512, 23])

@@ -673,6 +673,7 @@ extern "C" int prism_b200_sgemm(int kernel_id, int M, int N, int K, float alpha,
     }
     case 5: {
         if (M % k5::BM == 0 && N % k5::BN == 0 && K % k5::BK == 0 && K > 0 && vec_ok) {
+            int want_form, want_slices;
             {
                 std::lock_guard<std::mutex> lk(g_sgemm_mu);
                 if (!g_k5_env_read) {
@@ -680,6 +681,8 @@ extern "C" int prism_b200_sgemm(int kernel_id, int M, int N, int K, float alpha,
                     g_k5_scalar = e && e[0] == '1';
                     g_k5_env_read = true;
                 }
+                want_form = g_k5_tile_mode;
+                want_slices = g_k5_slices;
             }
             // Which tile (0: 128 x 128, 1: 64 x 128, 2: 64 x 64) and how many CTAs per tile along K (1, 2 or 4; the 64-row
             // tiles only): the candidate with the shortest estimated makespan.  An SM works through ceil(CTAs / SMs) CTAs
@@ -692,7 +695,7 @@ extern "C" int prism_b200_sgemm(int kernel_id, int M, int N, int K, float alpha,
             // 11.5 -> 18.8 shared by four.  The unshared forms add one element's products in the same k order and give
             // the same bits; a shared tile sums each range of K first.
             int form = 0, slices = 1;
-            k5_plan(M, N, K, sm_count(), g_k5_tile_mode, g_k5_slices, &form, &slices);
+            k5_plan(M, N, K, sm_count(), want_form, want_slices, &form, &slices);
             void (*kern)(int, int, int, float, float*, float*, float, float*, int) =
                 form == 2   ? (g_k5_scalar ? my_sgemm_kernel_5<false, 1, 4, 1> : my_sgemm_kernel_5<true, 1, 4, 1>)
                 : form == 1 ? (g_k5_scalar ? my_sgemm_kernel_5<false, 1, 4, 2> : my_sgemm_kernel_5<true, 1, 4, 2>)

@@ -413,8 +413,8 @@ def run_gemm_bf16(args, world, rank, peaks):
     kernel_ms = sum(per) / len(per)     # this rank's kernel: rows x S x S
     achieved = 2.0 * rows * S * S / (kernel_ms * 1e-3) / 1e12
     peak = peaks["bf16_tflops"]
-    roofline = {"bound": "tensor", "kernel": ("cutlass_my_h100_match_no_tail_pair_wide<16> (tcgen05, cta_group::2, 512 x 256 tiles, "
-                                               "persistent over the CTA pairs)"
+    roofline = {"bound": "tensor", "kernel": ("cutlass_my_h100_match_no_tail_pair_wide[_fill]<16> (tcgen05, cta_group::2, 512 x 256 tiles, "
+                                               "persistent over the CTA pairs; a last wave of at most half the pairs' tiles is cut into halves)"
                            if (rows % 256 == 0 and S % 512 == 0 and rows * S * S >= 2 ** 35)
                            else "cutlass_my_h100_match_no_tail family (tcgen05), form chosen by shape"), "achieved": achieved,
                 "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,

@@ -272,6 +272,26 @@ int prism_b200_gemm_bf16(int M, int N, int K, const uint16_t* A, const uint16_t*
 int prism_b200_gemm_bf16_axpby(int M, int N, int K, float alpha, const uint16_t* A, const uint16_t* B, float beta,
                                const uint16_t* Cin, uint16_t* D, void* stream);
 
+/*
+ * How the 512 x 256 two-CTA form of prism_b200_gemm_bf16 deals its output tiles to its CTA pairs.  With `tiles` tiles on
+ * `pairs` pairs, a pair computes the whole tiles pair, pair + pairs, ... of the tiles / pairs full waves.  The
+ * R = tiles mod pairs tiles that remain would occupy R pairs for a whole tile's time while the others idle; with
+ * fill = 1 each of them is cut into its two 256-row blocks of n, which a pair computes on its own over all of K with
+ * nothing to hand over (piece q = pair + j * pairs is block q mod 2 of tile (tiles / pairs) * pairs + q / 2), so where
+ * 2 R <= pairs the last wave takes half a tile's time.  A piece accumulates its k-blocks in the order a whole tile
+ * does, so results are bit-identical with and without the fill.  The launcher fills where that halves the last wave
+ * (on a B200's 74 pairs: 8192^3 cut over 2 GPUs, 256 tiles = 3 waves + 34).
+ *
+ * prism_b200_gemm_bf16_fill_plan writes the items of pair `pair` in the order it computes them, as (tile, block) with
+ * block = -1 for a whole tile, into tile_block[0 .. 2 * min(*count, capacity)) and their number into *count.  Host-side
+ * arithmetic only (no GPU needed); it is the function the kernel evaluates.  The reference's kernel has a fixed grid of
+ * 128 CTAs, one tile each, and nothing like it (generated/cutlass_my_h100_match_no_tail.cu:90-101).
+ */
+int prism_b200_gemm_bf16_fill_plan(int tiles, int pairs, int fill, int pair, int capacity, int* tile_block, int* count);
+/* -1 (default): the launcher decides by shape; 0: never cut the last wave; 2: cut it whenever it is partly filled.
+ * Process-wide; overrides the environment variable PRISM_B200_GEMM_FILL.  For tests and measurements. */
+int prism_b200_gemm_bf16_fill_mode(int mode);
+
 /* ---- one-sided all-gather over peer memory --------------------------------- */
 
 /*

@@ -31,6 +31,8 @@ SIGNATURES = {
     "prism_b200_launch_count": (c_ulonglong, []),
     "prism_b200_selftest_wait_timeout": (c_int, [c_ulonglong, c_void_p]),
     "prism_b200_sgemm": (c_int, [c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_float, c_void_p, c_void_p]),
+    "prism_b200_gemm_bf16_fill_mode": (c_int, [c_int]),
+    "prism_b200_gemm_bf16_fill_plan": (c_int, [c_int, c_int, c_int, c_int, c_int, POINTER(c_int), POINTER(c_int)]),
     "prism_b200_sgemm_tile_mode": (c_int, [c_int]),
     "prism_b200_sgemm_k_slices": (c_int, [c_int]),
     "prism_b200_sgemm_plan": (c_int, [c_int, c_int, c_int, c_int, POINTER(c_int), POINTER(c_int)]),

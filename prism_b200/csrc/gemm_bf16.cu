@@ -709,24 +709,71 @@ struct WideCfg {
     static constexpr int THREADS = 64 + 32 * EPI_WARPS;
     static constexpr uint32_t BLOCK_BYTES = HALF * BLOCK_K * 2;   // one 128-row operand block
     static constexpr uint32_t STAGE_BYTES = 3 * BLOCK_BYTES;      // P0, P1, Q half
-    static constexpr uint32_t BAR_BYTES = 128;                    // barriers, TMEM slot, abort flag
+    static constexpr uint32_t BAR_BYTES = 256;                    // barriers, TMEM slot, abort flag
+    // The ring re-cut for the pieces of a filled last wave: one n block and the m rows, 32 KB per stage.
+    static constexpr int PIECE_STAGES = 6;
+    static constexpr uint32_t PIECE_STAGE_BYTES = 2 * BLOCK_BYTES;
+    static_assert(PIECE_STAGES * PIECE_STAGE_BYTES == STAGES * STAGE_BYTES, "the two cuts cover the same ring");
     static constexpr uint32_t EPI_WARP_BYTES = 32 * 128;          // 32 rows x 64 bf16 per epilogue warp
     static constexpr size_t SMEM_BYTES =
         1024 + static_cast<size_t>(STAGES) * STAGE_BYTES + BAR_BYTES + EPI_WARPS * EPI_WARP_BYTES;
 };
 }  // namespace g16
 
+// The work of one CTA pair of the 512 x 256 form: `full` whole tiles (tile = i * pairs + pair), then, with FILL, its share
+// of the last, partly filled wave.  Without FILL a pair simply takes every pairs-th tile, and in the last wave the
+// pairs beyond the R = tiles mod pairs remaining tiles idle for a whole tile's time.  With FILL every tile of that wave
+// is cut into its two 256-row n blocks, which a pair computes on its own (one 256 x 256 MMA per k-step instead of two,
+// over all of K, nothing to hand over); the 2 R pieces are dealt round-robin to all pairs, so where 2 R <= pairs the
+// wave costs half a tile's time.  A piece accumulates its k-blocks in the order the whole tile does, in the columns of
+// tensor memory the whole tile would use for that block, so the results are bit-identical to the unfilled kernel's.
+struct PairPlan {
+    int full;        // whole tiles
+    int pieces;      // pieces of the last wave that this pair computes
+    int wave_first;  // first tile of the last wave
+};
+
+template <bool FILL>
+__host__ __device__ __forceinline__ PairPlan make_pair_plan(int pair, int pairs, int total_tiles) {
+    PairPlan p;
+    p.pieces = 0;
+    p.wave_first = total_tiles;
+    if (!FILL) {
+        p.full = pair < total_tiles ? (total_tiles - pair + pairs - 1) / pairs : 0;
+    } else {
+        p.full = total_tiles / pairs;
+        p.wave_first = p.full * pairs;
+        const int all = (total_tiles - p.wave_first) * 2;
+        p.pieces = pair < all ? (all - pair + pairs - 1) / pairs : 0;
+    }
+    return p;
+}
+
+// Item i of a pair: a tile and which n block of it (-1 = the whole tile).
+__host__ __device__ __forceinline__ void plan_item(const PairPlan& p, int i, int pair, int pairs, int& tile, int& blk) {
+    if (i < p.full) {
+        tile = i * pairs + pair;
+        blk = -1;
+    } else {
+        const int q = pair + (i - p.full) * pairs;
+        tile = p.wave_first + q / 2;
+        blk = q % 2;
+    }
+}
+
 // 512 x 256 tiles: each CTA of the pair holds two 128-row n blocks (two accumulators of 256 columns, all of tensor
 // memory) against the pair's 256 m rows, so the m-side operand is read once for two MMAs.  Persistent: pair p takes
-// tiles p, p + pairs, ...
-template <int GROUP>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(g16::WideCfg::THREADS, 1)
-cutlass_my_h100_match_no_tail_pair_wide(int M, int N, int K, __nv_bfloat16* C,
-                                        const __grid_constant__ CUtensorMap tensorMapA,
-                                        const __grid_constant__ CUtensorMap tensorMapB) {
+// tiles p, p + pairs, ... (and, with FILL, pieces of the last wave: see PairPlan).  For the pieces the ring is
+// re-cut from four 48 KB stages into six of 32 KB with barriers of their own, so that a piece, which needs 1.33 x the
+// operand bytes per MMA cycle, has as many MMA cycles of loads in flight as the 256 x 256 pair kernel has; the
+// producer switches over once every stage of the first cut has been consumed.
+template <int GROUP, bool FILL>
+__device__ __forceinline__ void pair_wide_body(int M, int N, int K, __nv_bfloat16* C, const CUtensorMap* tensorMapA,
+                                               const CUtensorMap* tensorMapB) {
     using namespace g16;
     using W_ = WideCfg;
     constexpr int STAGES = W_::STAGES;
+    constexpr int PSTAGES = W_::PIECE_STAGES;
     constexpr uint32_t IDESC = instr_desc(256, W_::TILE_M);       // 256 n rows across the pair per MMA, 256 m columns
 
     extern __shared__ unsigned char smem_raw[];
@@ -734,7 +781,9 @@ cutlass_my_h100_match_no_tail_pair_wide(int M, int N, int K, __nv_bfloat16* C,
     unsigned char* ring = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(ring + STAGES * W_::STAGE_BYTES);
     uint64_t* empty_bar = full_bar + STAGES;
-    uint64_t* acc_full_bar = empty_bar + STAGES;   // [1]
+    uint64_t* pfull_bar = empty_bar + STAGES;      // [PSTAGES], the piece ring's (used with FILL only)
+    uint64_t* pempty_bar = pfull_bar + PSTAGES;    // [PSTAGES]
+    uint64_t* acc_full_bar = pempty_bar + PSTAGES; // [1]
     uint64_t* acc_empty_bar = acc_full_bar + 1;    // [1], only the leader's is used
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty_bar + 1);
     volatile uint32_t* abort_flag = tmem_slot + 1;
@@ -751,11 +800,17 @@ cutlass_my_h100_match_no_tail_pair_wide(int M, int N, int K, __nv_bfloat16* C,
     const int tiles_n = N / W_::TILE_N;
     const int total_tiles = tiles_m * tiles_n;
     const int k_blocks = K / BLOCK_K;
+    const PairPlan plan = make_pair_plan<FILL>(pair, pairs, total_tiles);
+    const int items = plan.full + plan.pieces;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(&full_bar[s], 1);
             mbar_init(&empty_bar[s], 1);
+        }
+        for (int s = 0; s < PSTAGES; ++s) {
+            mbar_init(&pfull_bar[s], 1);
+            mbar_init(&pempty_bar[s], 1);
         }
         mbar_init(acc_full_bar, 1);
         mbar_init(acc_empty_bar, 2 * W_::EPI_WARPS);
@@ -780,14 +835,14 @@ cutlass_my_h100_match_no_tail_pair_wide(int M, int N, int K, __nv_bfloat16* C,
     if (warp == 0) {
         // ------------------------- TMA producer (both CTAs) -------------------------
         if (lane == 0) {
-            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tensorMapA)) : "memory");
-            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tensorMapB)) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tensorMapA)) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tensorMapB)) : "memory");
             int stage = 0;
             uint32_t phase = 0;
             int armed = 0;   // stages loaded and not known to be consumed (for the unwind path)
-            for (int t = pair; t < total_tiles && !timed_out; t += pairs) {
+            for (int i = 0; i < plan.full && !timed_out; ++i) {
                 int tm, tn;
-                tile_coords(t, tiles_m, tiles_n, tm, tn, GROUP);
+                tile_coords(i * pairs + pair, tiles_m, tiles_n, tm, tn, GROUP);
                 // This CTA's two n blocks and its half of the m rows.
                 const int n_row0 = tn * W_::TILE_N + static_cast<int>(rank) * 256;
                 const int m_row = tm * W_::TILE_M + static_cast<int>(rank) * W_::HALF;
@@ -799,9 +854,9 @@ cutlass_my_h100_match_no_tail_pair_wide(int M, int N, int K, __nv_bfloat16* C,
                     unsigned char* dst = ring + stage * W_::STAGE_BYTES;
                     const uint32_t leader_full = cluster_addr(&full_bar[stage], 0);
                     if (leader) mbar_arrive_expect_tx(&full_bar[stage], 2 * W_::STAGE_BYTES);   // both CTAs' bytes
-                    tma_load_2d_pair(dst, &tensorMapB, kb * BLOCK_K, n_row0, leader_full);
-                    tma_load_2d_pair(dst + W_::BLOCK_BYTES, &tensorMapB, kb * BLOCK_K, n_row0 + W_::HALF, leader_full);
-                    tma_load_2d_pair(dst + 2 * W_::BLOCK_BYTES, &tensorMapA, kb * BLOCK_K, m_row, leader_full);
+                    tma_load_2d_pair(dst, tensorMapB, kb * BLOCK_K, n_row0, leader_full);
+                    tma_load_2d_pair(dst + W_::BLOCK_BYTES, tensorMapB, kb * BLOCK_K, n_row0 + W_::HALF, leader_full);
+                    tma_load_2d_pair(dst + 2 * W_::BLOCK_BYTES, tensorMapA, kb * BLOCK_K, m_row, leader_full);
                     armed = armed < STAGES ? armed + 1 : STAGES;
                     if (++stage == STAGES) {
                         stage = 0;
@@ -809,41 +864,111 @@ cutlass_my_h100_match_no_tail_pair_wide(int M, int N, int K, __nv_bfloat16* C,
                     }
                 }
             }
-            if (timed_out || *abort_flag) drain_pair_loads(full_bar, stage, phase, armed, STAGES, leader, never_flag);
+            bool in_pieces = false;
+            int pstage = 0, parmed = 0;
+            uint32_t pphase = 0;
+            if (FILL && plan.pieces > 0 && !timed_out) {
+                // Before the ring is cut differently every stage of the first cut must have been consumed: the wait
+                // that would precede the next load into each of them.
+                for (int s = 0; s < STAGES && !timed_out; ++s) {
+                    if (!mbar_wait_bounded_sleepy(&empty_bar[stage], phase ^ 1u, abort_flag, 40)) timed_out = true;
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (!timed_out) {
+                    armed = 0;          // nothing of the first cut is in flight any more
+                    in_pieces = true;
+                }
+                for (int i = plan.full; i < items && !timed_out; ++i) {
+                    int t, blk, tm, tn;
+                    plan_item(plan, i, pair, pairs, t, blk);
+                    tile_coords(t, tiles_m, tiles_n, tm, tn, GROUP);
+                    const int n_row = tn * W_::TILE_N + static_cast<int>(rank) * 256 + blk * W_::HALF;
+                    const int m_row = tm * W_::TILE_M + static_cast<int>(rank) * W_::HALF;
+                    for (int kb = 0; kb < k_blocks; ++kb) {
+                        if (!mbar_wait_bounded_sleepy(&pempty_bar[pstage], pphase ^ 1u, abort_flag, 40)) {
+                            timed_out = true;
+                            break;
+                        }
+                        unsigned char* dst = ring + pstage * W_::PIECE_STAGE_BYTES;
+                        const uint32_t leader_full = cluster_addr(&pfull_bar[pstage], 0);
+                        if (leader) mbar_arrive_expect_tx(&pfull_bar[pstage], 2 * W_::PIECE_STAGE_BYTES);
+                        tma_load_2d_pair(dst, tensorMapB, kb * BLOCK_K, n_row, leader_full);
+                        tma_load_2d_pair(dst + W_::BLOCK_BYTES, tensorMapA, kb * BLOCK_K, m_row, leader_full);
+                        parmed = parmed < PSTAGES ? parmed + 1 : PSTAGES;
+                        if (++pstage == PSTAGES) {
+                            pstage = 0;
+                            pphase ^= 1u;
+                        }
+                    }
+                }
+            }
+            if (timed_out || *abort_flag) {
+                if (in_pieces) drain_pair_loads(pfull_bar, pstage, pphase, parmed, PSTAGES, leader, never_flag);
+                else drain_pair_loads(full_bar, stage, phase, armed, STAGES, leader, never_flag);
+            }
         }
     } else if (warp == 1) {
         // ------------------------- MMA issuer (leader only) -------------------------
         if (leader && lane == 0) {
-            int stage = 0;
-            uint32_t phase = 0;
+            int stage = 0, pstage = 0;
+            uint32_t phase = 0, pphase = 0;
             uint32_t tile_phase = 0;
-            for (int t = pair; t < total_tiles && !timed_out; t += pairs) {
+            for (int i = 0; i < items && !timed_out; ++i) {
+                int t, blk;
+                plan_item(plan, i, pair, pairs, t, blk);
                 if (!mbar_wait_bounded(acc_empty_bar, tile_phase ^ 1u, abort_flag)) {   // both CTAs drained both accumulators
                     timed_out = true;
                     break;
                 }
                 tc_fence_after();
-                for (int kb = 0; kb < k_blocks; ++kb) {
-                    if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag)) {
-                        timed_out = true;
-                        break;
-                    }
-                    tc_fence_after();
-                    const uint32_t base = smem_u32(ring + stage * W_::STAGE_BYTES);
-                    const uint64_t p0_desc = smem_desc_k_sw128(base);
-                    const uint64_t p1_desc = smem_desc_k_sw128(base + W_::BLOCK_BYTES);
-                    const uint64_t q_desc = smem_desc_k_sw128(base + 2 * W_::BLOCK_BYTES);
+                if (!FILL || blk < 0) {
+                    for (int kb = 0; kb < k_blocks; ++kb) {
+                        if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag)) {
+                            timed_out = true;
+                            break;
+                        }
+                        tc_fence_after();
+                        const uint32_t base = smem_u32(ring + stage * W_::STAGE_BYTES);
+                        const uint64_t p0_desc = smem_desc_k_sw128(base);
+                        const uint64_t p1_desc = smem_desc_k_sw128(base + W_::BLOCK_BYTES);
+                        const uint64_t q_desc = smem_desc_k_sw128(base + 2 * W_::BLOCK_BYTES);
 #pragma unroll
-                    for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
-                        const uint32_t accumulate = (kb | k) != 0 ? 1u : 0u;
-                        umma_bf16_pair(tmem_base, p0_desc + 2u * k, q_desc + 2u * k, IDESC, accumulate);
-                        umma_bf16_pair(tmem_base + 256u, p1_desc + 2u * k, q_desc + 2u * k, IDESC, accumulate);
+                        for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
+                            const uint32_t accumulate = (kb | k) != 0 ? 1u : 0u;
+                            umma_bf16_pair(tmem_base, p0_desc + 2u * k, q_desc + 2u * k, IDESC, accumulate);
+                            umma_bf16_pair(tmem_base + 256u, p1_desc + 2u * k, q_desc + 2u * k, IDESC, accumulate);
+                        }
+                        umma_commit_pair(cluster_addr(&empty_bar[stage], 0));
+                        umma_commit_pair(cluster_addr(&empty_bar[stage], 1));
+                        if (++stage == STAGES) {
+                            stage = 0;
+                            phase ^= 1u;
+                        }
                     }
-                    umma_commit_pair(cluster_addr(&empty_bar[stage], 0));
-                    umma_commit_pair(cluster_addr(&empty_bar[stage], 1));
-                    if (++stage == STAGES) {
-                        stage = 0;
-                        phase ^= 1u;
+                } else {
+                    // a piece accumulates in the half of tensor memory that the whole tile would use for its n block
+                    const uint32_t d_piece = tmem_base + static_cast<uint32_t>(blk * 256);
+                    for (int kb = 0; kb < k_blocks; ++kb) {
+                        if (!mbar_wait_bounded(&pfull_bar[pstage], pphase, abort_flag)) {
+                            timed_out = true;
+                            break;
+                        }
+                        tc_fence_after();
+                        const uint32_t base = smem_u32(ring + pstage * W_::PIECE_STAGE_BYTES);
+                        const uint64_t p_desc = smem_desc_k_sw128(base);
+                        const uint64_t q_desc = smem_desc_k_sw128(base + W_::BLOCK_BYTES);
+#pragma unroll
+                        for (int k = 0; k < BLOCK_K / UMMA_K; ++k)
+                            umma_bf16_pair(d_piece, p_desc + 2u * k, q_desc + 2u * k, IDESC, (kb | k) != 0 ? 1u : 0u);
+                        umma_commit_pair(cluster_addr(&pempty_bar[pstage], 0));
+                        umma_commit_pair(cluster_addr(&pempty_bar[pstage], 1));
+                        if (++pstage == PSTAGES) {
+                            pstage = 0;
+                            pphase ^= 1u;
+                        }
                     }
                 }
                 if (timed_out) break;
@@ -859,8 +984,9 @@ cutlass_my_h100_match_no_tail_pair_wide(int M, int N, int K, __nv_bfloat16* C,
         const int quarter = warp & 3;
         const int block = (warp - 2) >> 2;
         uint32_t tile_phase = 0;
-        for (int t = pair; t < total_tiles; t += pairs) {
-            int tm, tn;
+        for (int i = 0; i < items; ++i) {
+            int t, blk, tm, tn;
+            plan_item(plan, i, pair, pairs, t, blk);
             tile_coords(t, tiles_m, tiles_n, tm, tn, GROUP);
             const bool ready = lane != 0 || mbar_wait_bounded_sleepy(acc_full_bar, tile_phase, abort_flag, 200);
             if (!__all_sync(0xffffffffu, ready)) {
@@ -868,6 +994,15 @@ cutlass_my_h100_match_no_tail_pair_wide(int M, int N, int K, __nv_bfloat16* C,
                 break;
             }
             tc_fence_after();
+            if (FILL && blk >= 0 && blk != block) {
+                // The other n block's warps drain this piece.  This warp has waited for it like everybody (which keeps
+                // it in step with the barrier's phases) and hands its share of tensor memory back at once.
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(cluster_addr(acc_empty_bar, 0));
+                tile_phase ^= 1u;
+                continue;
+            }
             // A lane reads one accumulator row (one n, consecutive m).  Writing that row straight to
             // global memory would make every store instruction touch 32 different lines, 16 bytes
             // each; instead the warp passes 32 rows x 64 columns at a time through shared memory
@@ -932,6 +1067,23 @@ cutlass_my_h100_match_no_tail_pair_wide(int M, int N, int K, __nv_bfloat16* C,
                      "r"(static_cast<uint32_t>(TMEM_COLS))
                      : "memory");
     }
+}
+
+template <int GROUP>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(g16::WideCfg::THREADS, 1)
+cutlass_my_h100_match_no_tail_pair_wide(int M, int N, int K, __nv_bfloat16* C,
+                                        const __grid_constant__ CUtensorMap tensorMapA,
+                                        const __grid_constant__ CUtensorMap tensorMapB) {
+    pair_wide_body<GROUP, false>(M, N, K, C, &tensorMapA, &tensorMapB);
+}
+
+// The same kernel with the tiles of the last, partly filled wave cut into their two n blocks, dealt to all CTA pairs.
+template <int GROUP>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(g16::WideCfg::THREADS, 1)
+cutlass_my_h100_match_no_tail_pair_wide_fill(int M, int N, int K, __nv_bfloat16* C,
+                                             const __grid_constant__ CUtensorMap tensorMapA,
+                                             const __grid_constant__ CUtensorMap tensorMapB) {
+    pair_wide_body<GROUP, true>(M, N, K, C, &tensorMapA, &tensorMapB);
 }
 
 namespace {
@@ -1115,20 +1267,87 @@ int launch_gemm_pair(int dev, int M, int N, int K, const void* A, const void* B,
                               (M / P_::BLOCK) * (N / P_::BLOCK), dev, M, N, K, map_a, map_b, C, s);
 }
 
+// ---- the 512 x 256 form and the filling of its last wave ---------------------------------------
+bool g_fill_mode_set = false;   // prism_b200_gemm_bf16_fill_mode was called: the environment no longer decides
+int g_fill_mode = -1;           // -1 by shape, 0 never, 2 whenever the last wave is partly filled
+
+// Main-loop throughput of a piece (one 256 x 256 MMA per k-step on 32 KB of operands per CTA) relative to a whole
+// 512 x 256 tile's, measured on a B200.
+constexpr double kPieceEff = 0.92;
+
+// Time of the 512 x 256 form in units of one whole tile, and whether the tiles of the last wave are cut into their two
+// n blocks to reach it (*fill).  By shape, a fill is taken where it halves the last wave (2 R <= pairs).
+double wide_form_time(long long tiles, int pairs, int mode, bool* fill) {
+    const long long waves = tiles / pairs;
+    const int rem = static_cast<int>(tiles % pairs);
+    bool cut = false;
+    double last = rem ? 1.0 : 0.0;
+    if (rem && mode != 0) {
+        const double pieces = static_cast<double>((2 * rem + pairs - 1) / pairs) / 2.0 / kPieceEff;
+        if (mode == 2 || pieces < 0.9) {
+            cut = true;
+            last = pieces;
+        }
+    }
+    if (fill) *fill = cut;
+    return static_cast<double>(waves) + last;
+}
+
 int launch_gemm_pair_wide(int dev, int M, int N, int K, const void* A, const void* B, void* C, cudaStream_t s) {
     using W_ = g16::WideCfg;
     CUtensorMap map_a, map_b;
     if (int rc = get_tensor_map(dev, A, M, K, W_::HALF, &map_a)) return rc;
     if (int rc = get_tensor_map(dev, B, N, K, W_::HALF, &map_b)) return rc;
-    static int max_pairs[64] = {};
-    return launch_pair_kernel(cutlass_my_h100_match_no_tail_pair_wide<16>, max_pairs, W_::THREADS, W_::SMEM_BYTES,
-                              (M / W_::TILE_M) * (N / W_::TILE_N), dev, M, N, K, map_a, map_b, C, s);
+    static int max_pairs[64] = {}, max_pairs_fill[64] = {};
+    const int tiles = (M / W_::TILE_M) * (N / W_::TILE_N);
+    int pairs_cap = 0;
+    if (int rc = pair_capacity(cutlass_my_h100_match_no_tail_pair_wide_fill<16>, max_pairs_fill, W_::THREADS, W_::SMEM_BYTES,
+                               dev, &pairs_cap))
+        return rc;
+    bool fill = false;
+    (void)wide_form_time(tiles, pairs_cap, g_fill_mode, &fill);
+    if (fill) {
+        cudaLaunchConfig_t cfg;
+        cudaLaunchAttribute attr[1];
+        pair_launch_config(&cfg, attr, W_::THREADS, W_::SMEM_BYTES, s);
+        // every pair that has a tile or a piece: all of them once there is a full wave
+        const long long items = static_cast<long long>(tiles / pairs_cap) * pairs_cap + 2LL * (tiles % pairs_cap);
+        const int pairs = items < pairs_cap ? static_cast<int>(items) : pairs_cap;
+        cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs));
+        PRISM_CUDA_TRY(cudaLaunchKernelEx(&cfg, cutlass_my_h100_match_no_tail_pair_wide_fill<16>, M, N, K,
+                                          static_cast<__nv_bfloat16*>(C), map_a, map_b));
+        count_launch();
+        return PRISM_B200_OK;
+    }
+    return launch_pair_kernel(cutlass_my_h100_match_no_tail_pair_wide<16>, max_pairs, W_::THREADS, W_::SMEM_BYTES, tiles, dev,
+                              M, N, K, map_a, map_b, C, s);
 }
 
 }  // namespace
 }  // namespace prism_b200
 
 using namespace prism_b200;
+
+extern "C" int prism_b200_gemm_bf16_fill_mode(int mode) {
+    if (mode != -1 && mode != 0 && mode != 2)
+        return set_error(PRISM_B200_ERR_INVALID_ARGUMENT, "gemm_bf16_fill_mode: -1, 0 or 2");
+    std::lock_guard<std::mutex> lk(g_launch_mu);
+    g_fill_mode_set = true;
+    g_fill_mode = mode;
+    return PRISM_B200_OK;
+}
+
+extern "C" int prism_b200_gemm_bf16_fill_plan(int tiles, int pairs, int fill, int pair, int capacity, int* tile_block,
+                                              int* count) {
+    if (!count || tiles < 0 || pairs < 1 || (fill != 0 && fill != 1) || pair < 0 || pair >= pairs || capacity < 0 ||
+        (capacity > 0 && !tile_block))
+        return set_error(PRISM_B200_ERR_INVALID_ARGUMENT, "gemm_bf16_fill_plan: bad argument");
+    const PairPlan p = fill ? make_pair_plan<true>(pair, pairs, tiles) : make_pair_plan<false>(pair, pairs, tiles);
+    const int items = p.full + p.pieces;
+    for (int i = 0; i < items && i < capacity; ++i) plan_item(p, i, pair, pairs, tile_block[2 * i], tile_block[2 * i + 1]);
+    *count = items;
+    return PRISM_B200_OK;
+}
 
 extern "C" int prism_b200_gemm_bf16_axpby(int M, int N, int K, float alpha, const uint16_t* A, const uint16_t* B, float beta,
                                           const uint16_t* Cin, uint16_t* D, void* stream) {
@@ -1187,9 +1406,15 @@ extern "C" int prism_b200_gemm_bf16(int M, int N, int K, const uint16_t* A, cons
             if (dev >= 0 && dev < 64) sm_count[dev] = sms;
         }
         if (!env_read) {
-            // PRISM_B200_GEMM_PAIR = 0 / 1 / 2 forces one-CTA / 256 x 256 pair / 512 x 256 pair (tests)
+            // PRISM_B200_GEMM_PAIR = 0 / 1 / 2 forces one-CTA / 256 x 256 pair / 512 x 256 pair,
+            // PRISM_B200_GEMM_FILL = 0 / 2 the 512 x 256 form without / with its partly filled last wave cut in pieces (tests)
             const char* e = getenv("PRISM_B200_GEMM_PAIR");
             forced = e ? atoi(e) : -1;
+            const char* fm = getenv("PRISM_B200_GEMM_FILL");
+            if (!g_fill_mode_set && fm) {
+                const int v = atoi(fm);
+                g_fill_mode = (v == 0 || v == 2) ? v : -1;
+            }
             env_read = true;
         }
     }
@@ -1217,7 +1442,7 @@ extern "C" int prism_b200_gemm_bf16(int M, int N, int K, const uint16_t* A, cons
                 if (t < best) { best = t; form = 1; }
             }
             if (wide_ok) {
-                const double t = waves(static_cast<long long>(M / 256) * (N / 512), pairs) * 2.0;
+                const double t = wide_form_time(static_cast<long long>(M / 256) * (N / 512), pairs, g_fill_mode, nullptr) * 2.0;
                 if (t <= best) { best = t; form = 2; }
             }
         }

@@ -87,16 +87,54 @@ def test_random_shapes_match_fp64_oracle(pb):
     ("1", [(256, 256, 64), (256, 512, 1024), (1024, 2048, 320), (4096, 4096, 256)]),
     # two-CTA kernel, 512 x 256 pair tiles
     ("2", [(256, 512, 64), (512, 512, 1024), (1024, 2048, 320), (4096, 4096, 256), (2048, 8192, 128)]),
+    # the same with the tiles of a partly filled last wave cut into their two n blocks: one tile alone, fewer pieces
+    # than pairs, one full wave plus a last wave with two pieces per pair (128 tiles on 74 pairs), 64 tiles, a k-block
+    # count that is no multiple of either ring's depth, one k-block, and a shape whose tiles fill the pairs exactly
+    ("2/2", [(256, 512, 2048), (1024, 2048, 1024), (2048, 8192, 1024), (1024, 1024, 4160), (1024, 8192, 2048),
+             (256, 512, 64), (9472, 1024, 128)]),
+    ("2/0", [(1024, 2048, 1024), (2048, 8192, 1024)]),
 ])
 def test_every_kernel_form_forced(mode, shapes):
     """The launcher picks a kernel form by problem size; each form is forced here on small and
     multi-wave shapes (the choice is read from the environment once per process, hence the child)."""
     import os
     import subprocess
-    env = dict(os.environ, PRISM_B200_GEMM_PAIR=mode)
+    env = dict(os.environ, PRISM_B200_GEMM_PAIR=mode[0])
+    if len(mode) > 1:
+        env["PRISM_B200_GEMM_FILL"] = mode[2]
     r = subprocess.run([sys.executable, "-c", _CHILD % (str(ROOT), shapes)], env=env, capture_output=True, text=True,
                        timeout=600)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+@pytest.mark.parametrize("shape", [(4096, 8192, 8192), (2048, 8192, 8192), (4096, 4096, 4096)])
+def test_filling_the_last_wave_changes_no_bit(pb, shape):
+    """The benchmark shape cut over 2 and 4 GPUs, and 4096^3 (256, 128 and 128 tiles of 512 x 256 on 74 pairs): with the
+    last wave's tiles computed whole or as their two n blocks, and with the launcher's own choice, the output is the
+    same bit for bit, since every piece accumulates all of K in the order the whole tile does."""
+    M, N, K = shape
+    lib = pb.load()
+    g = torch.Generator(device=DEV).manual_seed(M + N + K)
+    a = torch.randn((M, K), device=DEV, generator=g).to(torch.bfloat16)
+    b = torch.randn((N, K), device=DEV, generator=g).to(torch.bfloat16)
+    outs = {}
+    try:
+        for mode in (0, 2, -1):
+            assert lib.prism_b200_gemm_bf16_fill_mode(mode) == 0
+            c = torch.full((N, M), float("nan"), dtype=torch.bfloat16, device=DEV)
+            pb.runmyh100(M, N, K, a, b, c)
+            torch.cuda.synchronize()
+            assert pb.last_error()[0] == 0, pb.last_error()
+            outs[mode] = c.view(torch.int16)
+    finally:
+        lib.prism_b200_gemm_bf16_fill_mode(-1)
+    for mode in (2, -1):
+        assert torch.equal(outs[0], outs[mode]), f"fill mode {mode} differs from the unfilled kernel"
+    rows = [0, 127, 128, 255, 256, 383, 384, 511, N - 1]
+    ref = (b[rows].double() @ a.double().t()).cpu().numpy()
+    got = outs[0].view(torch.bfloat16)[rows].double().cpu().numpy()
+    rms = float(np.sqrt(np.mean(ref * ref)))
+    assert np.all(np.abs(got - ref) <= 1e-2 * np.abs(ref) + 1e-2 * rms)
 
 
 def test_layout_is_column_major_and_exact_on_small_integers(pb):

@@ -43,6 +43,7 @@ SCAN_NG = 1 << 30
 # from the ncu captures whose summaries sit in the profiles/ folder (None = not captured).
 NCU_TRAFFIC_BYTES = {
     "gemm_bf16": 1045.3e6,  # 8192^3: 917.6 MB read + 127.7 MB written
+    "gemm_bf16_half": 501.6e6,  # 4096 x 8192 x 8192, one of two GPUs' share: 435.0 MB read + 66.6 MB written
     "sgemm": 631.5e6,       # 4096^3: 569.1 MB read + 62.3 MB written
     "scan": 1916.4e6,       # 2^28: 4 x the 479.1 MB captured at 2^26 (an undercount: the last writes are still in L2 when the kernel ends)
 }
@@ -420,7 +421,8 @@ def run_gemm_bf16(args, world, rank, peaks):
                 "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                 "peak_source": f"{peaks['source']} cuBLAS bf16 burst (the timed region is a burst of %d launches)" % args.steps,
                 "frac_of_nominal_2250": achieved / 2250.0,
-                "traffic": NCU_TRAFFIC_BYTES["gemm_bf16"] if (S == GEMM_S and world == 1) else None}
+                "traffic": (NCU_TRAFFIC_BYTES["gemm_bf16"] if (S == GEMM_S and world == 1) else
+                            NCU_TRAFFIC_BYTES["gemm_bf16_half"] if (S == GEMM_S and world == 2) else None)}
     line = {"metric": "bf16 GEMM TFLOP/s (D = A*B^T, M=N=K=%d, fp32 accumulate, bf16 out)" % S, "value": value,
             "unit": "TFLOP/s", "ms_per_step": ms, "scaling": "strong", "dtype": "bf16",
             "config": gemm_bf16_config(S, world),

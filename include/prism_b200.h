@@ -205,6 +205,12 @@ int prism_b200_scan_add_carry(size_t n, uint32_t* x, const uint32_t* totals,
  * for the skew the job can have.  An empty chunk (n = 0) still publishes a zero total and waits.
  * Waiting for every rank's word, together with the two alternating halves of the array, is what
  * makes it safe for a rank to run a whole call ahead of another.  world <= 32.
+ * With phases = 2, rank may equal world: the piece then lies behind every rank's chunk and starts from the sum of
+ * ALL totals.  That is what lets one rank own a head and a tail of the array (prism_b200/sharded.py, the
+ * "head_tail" schedule): it scans the head outright (its prefix is zero), publishes the head's total with
+ * prism_b200_scan_publish_total while the others are still adding up their chunks, and scans the tail, whose total
+ * nobody needs, once all words are in -- 8 bytes per element on that rank instead of 12, so it can own 1.5 chunks
+ * and the whole array finishes in the time of world + 0.5 chunks' worth of 12-byte traffic instead of world.
  * The pieces are also exported on their own: prism_b200_scan_publish_total stores the word for a
  * total computed elsewhere (prism_b200_reduce_u32), prism_b200_scan_seeded_peers is phases = 2
  * with the default limit.  No counterpart in the reference.

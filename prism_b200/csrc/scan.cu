@@ -835,10 +835,14 @@ int scan_launch(size_t n, uint32_t* x, void* workspace, const void* seed_src, in
 int scan_sharded_launch(size_t n, uint32_t* x, void* workspace, const uint64_t* slots, uint64_t* const* peer_slots,
                         int rank, int world, uint32_t epoch, int phases, unsigned long long wait_limit_ns,
                         cudaStream_t stream) {
-    if (world < 1 || world > 32 || rank < 0 || rank >= world || epoch == 0)
-        return set_error(PRISM_B200_ERR_INVALID_ARGUMENT,
-                         "scan_sharded: need 1 <= world <= 32, a rank below world and a non-zero epoch");
     if (phases < 1 || phases > 3) return set_error(PRISM_B200_ERR_INVALID_ARGUMENT, "scan_sharded: phases must be 1, 2 or 3");
+    // rank == world with the scan phase alone: a piece that lies behind every rank's chunk (it publishes nothing and
+    // is seeded with the sum of all the ranks' totals).
+    const bool behind_all = rank == world && phases == kPhaseScan;
+    if (world < 1 || world > 32 || rank < 0 || (rank >= world && !behind_all) || epoch == 0)
+        return set_error(PRISM_B200_ERR_INVALID_ARGUMENT,
+                         "scan_sharded: need 1 <= world <= 32, a rank below world (or equal to it, scan phase only) and a "
+                         "non-zero epoch");
     if (((phases & kPhaseReduce) && !peer_slots) || ((phases & kPhaseScan) && !slots) || !workspace || (n && !x))
         return set_error(PRISM_B200_ERR_INVALID_ARGUMENT, "scan_sharded: null pointer");
     if (n >= (1ull << 32)) return set_error(PRISM_B200_ERR_TOO_LARGE, "scan_sharded: n=%zu must be below 2^32", n);

@@ -47,6 +47,36 @@ def chunk_bounds(n: int, world: int, rank: int, align: int = 4) -> tuple[int, in
     return lo, hi
 
 
+def head_tail_bounds(n: int, world: int, align: int = 8) -> tuple[int, int, int] | None:
+    """Sizes (head, chunk, tail) of the head_tail schedule, or None where n is too small for it.
+
+    Rank 0 owns the first `head` = chunk / 2 elements and the last `tail` <= chunk elements of the array, rank
+    r >= 1 the chunk [head + (r - 1) chunk, head + r chunk).  Rank 0 moves 8 bytes per element (its head needs no
+    prefix, its tail's total is needed by nobody), the others 12 (add up, then scan), so 1.5 chunks on rank 0 take as
+    long as one chunk elsewhere: n = (world + 0.5) chunk.  All piece boundaries are multiples of `align` / 2 elements."""
+    if world < 2:
+        return None
+    chunk = -(-2 * n // (2 * world + 1))          # ceil(n / (world + 0.5))
+    chunk = -(-chunk // align) * align
+    head = chunk // 2
+    tail = n - head - (world - 1) * chunk
+    if chunk == 0 or tail < 0:
+        return None
+    return head, chunk, tail
+
+
+def head_tail_pieces(n: int, world: int, rank: int) -> list[tuple[int, int]]:
+    """The [lo, hi) ranges of the array that `rank` owns under the head_tail schedule, in the order they lie in its
+    local buffer (rank 0: head, then tail)."""
+    b = head_tail_bounds(n, world)
+    if b is None:
+        raise ValueError(f"n = {n} is too small for the head_tail schedule on {world} ranks")
+    head, chunk, tail = b
+    if rank == 0:
+        return [(0, head), (n - tail, n)]
+    return [(head + (rank - 1) * chunk, head + rank * chunk)]
+
+
 def row_shard(M: int, world: int, rank: int, tile: int = 128) -> tuple[int, int]:
     """Rows [lo, hi) of A and C owned by `rank`; M / world must be a multiple of the M tile."""
     if M % world or (M // world) % tile:
@@ -79,6 +109,14 @@ class _CudaOps:
 
     def scan_sharded_(self, x, workspace, slots, peer_slots_dev, rank, world, epoch, wait_limit_s):
         self._pb.scan_sharded_(x, workspace, slots, peer_slots_dev, rank, world, epoch, 3, wait_limit_s)
+
+    def scan_head_tail_(self, head, tail, ws_head, ws_tail, zero, slots, peer_slots_dev, world, epoch, wait_limit_s):
+        """Rank 0 of the head_tail schedule: scan the head, publish its total (its last element, or `zero` for an
+        empty head), then scan the tail from the sum of all the ranks' totals."""
+        if head.numel():
+            self._pb.launch_scan(head.numel(), head, ws_head)
+        self._pb.scan_publish_total(head[-1:] if head.numel() else zero, peer_slots_dev, world, 0, epoch)
+        self._pb.scan_sharded_(tail, ws_tail, slots, peer_slots_dev, world, world, epoch, 2, wait_limit_s)
 
     def check(self, device):
         """Synchronise and raise if a device-side wait ran out."""
@@ -125,9 +163,12 @@ class ShardedScan:
 
     SCHEDULES = ("reduce_then_scan", "scan_then_carry")       # run anywhere a process group runs
     PEER_SCHEDULE = "peer_words"                               # needs CUDA peer access (one node)
+    HEAD_TAIL = "head_tail"    # peer_words with rank 0 owning a head and a tail of the array: see head_tail_bounds
 
     def __init__(self, n_local: int, device, group: Any = None, schedule: str | None = None, ops: Any = None,
-                 wait_limit_s: float = 0.0, checked: bool = False, symmetric_words: Any = _symmetric_words):
+                 wait_limit_s: float = 0.0, checked: bool = False, symmetric_words: Any = _symmetric_words, head: int = 0):
+        """`head` (head_tail schedule, rank 0 only): how many of the n_local elements are the head of the array; the
+        rest of the local buffer is its tail.  Without peer-writable words head_tail cannot run and raises."""
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -135,8 +176,13 @@ class ShardedScan:
         asked = schedule
         if schedule is None:
             schedule = self.PEER_SCHEDULE if (on_cuda and self.world > 1 and ops is None) else "reduce_then_scan"
+        self.head_tail = schedule == self.HEAD_TAIL
+        if self.head_tail:
+            if self.world < 2:
+                raise ValueError("the head_tail schedule needs at least two ranks")
+            schedule = self.PEER_SCHEDULE        # the same words, the same kernels; rank 0 runs them differently
         if schedule not in self.SCHEDULES + (self.PEER_SCHEDULE,):
-            raise ValueError(f"schedule must be one of {self.SCHEDULES + (self.PEER_SCHEDULE,)}")
+            raise ValueError(f"schedule must be one of {self.SCHEDULES + (self.PEER_SCHEDULE, self.HEAD_TAIL)}")
         if schedule == self.PEER_SCHEDULE and self.world > 32:
             raise ValueError("the peer_words schedule handles at most 32 ranks")
         if schedule == self.PEER_SCHEDULE and not on_cuda and ops is None:
@@ -149,7 +195,11 @@ class ShardedScan:
         self.device = device
         self.ops = ops if ops is not None else _CudaOps()
         self.n_local = n_local
+        self.head = int(head) if (self.head_tail and self.rank == 0) else 0
+        if not 0 <= self.head <= n_local or self.head % 4:
+            raise ValueError("head must lie within the local buffer and be a multiple of 4 elements")
         self.workspace = self.ops.workspace(n_local, device)
+        self.workspace_head = self.ops.workspace(self.head, device) if self.head_tail and self.rank == 0 else None
         self.total = torch.zeros(1, dtype=torch.int32, device=device)
         self.totals = torch.zeros(self.world, dtype=torch.int32, device=device)
         if schedule == self.PEER_SCHEDULE and self.world > 1:
@@ -163,6 +213,8 @@ class ShardedScan:
                 if on_cuda:
                     torch.cuda.synchronize(device)
                 dist.barrier(group)   # every rank's words are zero before anyone publishes
+            elif self.head_tail:
+                raise RuntimeError("the head_tail schedule needs peer-writable words (one node with peer access)")
             else:
                 schedule = "reduce_then_scan"
         elif schedule == self.PEER_SCHEDULE and on_cuda and ops is None and asked == self.PEER_SCHEDULE:
@@ -171,7 +223,7 @@ class ShardedScan:
             self.slots = torch.zeros(2, dtype=torch.int64, device=device)
             self._table = torch.tensor([self.slots.data_ptr()], dtype=torch.int64, device=device)
             self.peer_slots_dev = int(self._table.data_ptr())
-        self.schedule = schedule
+        self.schedule = self.HEAD_TAIL if self.head_tail else schedule
         self.fell_back = asked in (None, self.PEER_SCHEDULE) and schedule != self.PEER_SCHEDULE and on_cuda and self.world > 1
 
     def _exchange(self, total: torch.Tensor) -> None:
@@ -183,7 +235,14 @@ class ShardedScan:
     def __call__(self, x_local: torch.Tensor) -> torch.Tensor:
         if x_local.numel() != self.n_local:
             raise ValueError(f"shard has {x_local.numel()} elements, planned for {self.n_local}")
-        if self.schedule == self.PEER_SCHEDULE and self.slots is not None:
+        if self.head_tail and self.rank == 0:
+            self.epoch += 1
+            self.ops.scan_head_tail_(x_local[:self.head], x_local[self.head:], self.workspace_head, self.workspace,
+                                     self.total.zero_(), self.slots, self.peer_slots_dev, self.world, self.epoch,
+                                     self.wait_limit_s)
+            if self.checked:
+                self.ops.check(self.device)
+        elif self.schedule in (self.PEER_SCHEDULE, self.HEAD_TAIL) and self.slots is not None:
             self.epoch += 1
             self.ops.scan_sharded_(x_local, self.workspace, self.slots, self.peer_slots_dev, self.rank, self.world,
                                    self.epoch, self.wait_limit_s)

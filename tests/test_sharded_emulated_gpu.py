@@ -81,6 +81,55 @@ def test_virtual_ranks_on_one_gpu(pb, world, n, high, form):
             assert np.all((w >> 32) == np.array(totals, dtype=np.uint64)[None, :])
 
 
+@pytest.mark.parametrize("world,n", [(2, (1 << 22) + 4096), (3, 5 * 4096 * 7 + 8), (4, 200)])
+def test_head_and_tail_on_virtual_rank_zero(pb, world, n):
+    """The head_tail schedule with virtual ranks on one GPU: rank 0 scans the head outright and publishes its last
+    element as its total, ranks 1 .. add up and publish their chunks, then every rank scans -- rank 0 its tail, as the
+    piece behind all chunks (rank = world, scan phase only), which starts from the sum of all totals.  The pieces,
+    put back in array order, equal the scan of the whole array bit for bit; three epochs."""
+    from prism_b200 import sharded
+    lib = pb.load()
+    stream = ctypes.c_void_p(torch.cuda.current_stream(torch.device(DEV)).cuda_stream)
+    words, table = _setup(world)
+    head, chunk, tail = sharded.head_tail_bounds(n, world)
+    ws = [pb.scan_workspace(max(chunk, tail, head, 1), DEV) for _ in range(world + 1)]
+    zero = torch.zeros(1, dtype=torch.int32, device=DEV)
+    with torch.cuda.device(DEV):
+        for epoch in (1, 2, 3):
+            full = O.scan_inputs(n, seed=7 * world + epoch, high=1 << 24)
+            expect = O.scan_cpu(full)
+            parts = {r: [torch.from_numpy(full[a:b].view(np.int32).copy()).to(DEV) for a, b in
+                         sharded.head_tail_pieces(n, world, r)] for r in range(world)}
+            h, t = parts[0]
+            if h.numel():
+                assert lib.prism_b200_scan(h.numel(), h.data_ptr(), ws[world].data_ptr(), stream) == 0
+            rc = lib.prism_b200_scan_publish_total((h[-1:] if h.numel() else zero).data_ptr(), table.data_ptr(), world, 0, epoch,
+                                                   stream)
+            assert rc == 0, pb.last_error()
+            for r in range(1, world):
+                x = parts[r][0]
+                rc = lib.prism_b200_scan_sharded(x.numel(), x.data_ptr() if x.numel() else None, ws[r].data_ptr(),
+                                                 words[r].data_ptr(), table.data_ptr(), r, world, epoch, 1, 0, stream)
+                assert rc == 0, pb.last_error()
+            rc = lib.prism_b200_scan_sharded(t.numel(), t.data_ptr() if t.numel() else None, ws[0].data_ptr(), words[0].data_ptr(),
+                                             table.data_ptr(), world, world, epoch, 2, 0, stream)
+            assert rc == 0, pb.last_error()
+            for r in range(1, world):
+                x = parts[r][0]
+                rc = lib.prism_b200_scan_sharded(x.numel(), x.data_ptr() if x.numel() else None, ws[r].data_ptr(),
+                                                 words[r].data_ptr(), table.data_ptr(), r, world, epoch, 2, 0, stream)
+                assert rc == 0, pb.last_error()
+            torch.cuda.synchronize()
+            assert pb.last_error()[0] == 0, pb.last_error()
+            got = np.concatenate([h.cpu().numpy()] + [parts[r][0].cpu().numpy() for r in range(1, world)] +
+                                 [t.cpu().numpy()]).view(np.uint32)
+            assert np.array_equal(got, expect), f"epoch {epoch}: first mismatch at {int(np.argmax(got != expect))}"
+    # the piece behind all chunks exists for the scan phase only
+    assert lib.prism_b200_scan_sharded(16, t.data_ptr(), ws[0].data_ptr(), words[0].data_ptr(), table.data_ptr(), world, world,
+                                       4, 3, 0, stream) == 1
+    pb.clear_error()
+
+
 def test_scan_step_gives_up_when_a_word_never_arrives(pb):
     """Nothing publishes rank 1's word: the scan step of rank 0 must come back after its (short) limit with
     a device time-out recorded, and the context must stay usable."""

@@ -50,6 +50,22 @@ for n_small in (3 * world + 1, 4 * (world - 1)):
         scan(x)
         assert np.array_equal(x.cpu().numpy().view(np.uint32), O.scan_cpu(full_s)[lo_s:hi_s]), (n_small, rank, rep)
 
+# the head_tail schedule: rank 0 owns the head and the tail of the array and never adds them up first
+for n_ht in ((1 << 22) + 12345, 40 * world):
+    full_h = O.scan_inputs(n_ht, seed=8, high=1 << 20)
+    expect_h = O.scan_cpu(full_h)
+    pieces = sharded.head_tail_pieces(n_ht, world, rank)
+    local = np.concatenate([full_h[a:b] for a, b in pieces])
+    want = np.concatenate([expect_h[a:b] for a, b in pieces])
+    scan = sharded.ShardedScan(local.size, dev, schedule="head_tail", head=pieces[0][1] - pieces[0][0] if rank == 0 else 0,
+                               wait_limit_s=5.0, checked=True)
+    assert scan.schedule == "head_tail"
+    for rep in range(4):
+        x = torch.from_numpy(local.view(np.int32).copy()).to(dev)
+        scan(x)
+        torch.cuda.synchronize()
+        assert np.array_equal(x.cpu().numpy().view(np.uint32), want), ("head_tail", n_ht, rank, rep)
+
 # bf16 GEMM from host arrays: every rank uploads its rows of A and 1/world of B, B is completed over NVLink
 Mh, Nh, Kh = 256 * world, 2048, 512
 A, B = O.gemm_bf16_inputs(Mh, Nh, Kh, seed=19)

@@ -66,6 +66,21 @@ class OracleOps:
         v = self._np(x)
         v[:] = (O.scan_cpu(v).astype(np.uint64) + carry).astype(np.uint32)
 
+    def scan_head_tail_(self, head, tail, ws_head, ws_tail, zero, slots, peer_slots_dev, world, epoch, wait_limit_s):
+        """Rank 0 of the head_tail schedule: its word carries the head's total; the tail starts from all totals."""
+        h = self._np(head)
+        h[:] = O.scan_cpu(h)
+        total = int(h[-1]) if h.size else 0
+        w = (total << 32) | epoch
+        word = torch.tensor([w - (1 << 64) if w >= (1 << 63) else w], dtype=torch.int64)
+        words = torch.zeros(world, dtype=torch.int64)
+        dist.all_gather_into_tensor(words, word)
+        half = (epoch & 1) * world
+        slots[half:half + world] = words
+        carry = sum((int(w) >> 32) & 0xFFFFFFFF for w in words.tolist()) & 0xFFFFFFFF
+        v = self._np(tail)
+        v[:] = (O.scan_cpu(v).astype(np.uint64) + carry).astype(np.uint32)
+
     def check(self, device):
         pass
 
@@ -207,3 +222,57 @@ def test_sharded_host_gemm_uploads_each_row_of_b_once_across_ranks():
     for rank, ok, worst, h2d, d2h in results:
         assert ok, (rank, worst)
         assert h2d == (256 + 512) * 64 * 2 and d2h == 1024 * 256 * 2
+
+
+def _head_tail_worker(rank, world, port, n, high, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        full = O.scan_inputs(n, seed=91, high=high)
+        pieces = sharded.head_tail_pieces(n, world, rank)
+        local = np.concatenate([full[lo:hi] for lo, hi in pieces])
+        expect = np.concatenate([O.scan_cpu(full)[lo:hi] for lo, hi in pieces])
+        head = pieces[0][1] - pieces[0][0] if rank == 0 else 0
+        scan = sharded.ShardedScan(local.size, "cpu", schedule="head_tail", ops=OracleOps(), symmetric_words=_local_words,
+                                   head=head)
+        ok = True
+        for _ in range(3):
+            x = torch.from_numpy(local.copy().view(np.int32))
+            scan(x)
+            ok = ok and np.array_equal(x.numpy().view(np.uint32), expect)
+        q.put((rank, ok, scan.schedule, pieces))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("n,high", [(100000, 16), (4099, 0xFFFFFFFF), (40, 3)])
+def test_head_tail_schedule_two_ranks(n, high):
+    """Rank 0 owns the head and the tail of the array and never adds its pieces up first; rank 1 the chunk between
+    them.  The pieces cover the array, and every piece equals the scan of the whole array on its range."""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_head_tail_worker, args=(r, 2, port, n, high, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=120) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    covered = sorted(rng for _, _, _, pieces in results for rng in pieces)
+    assert covered[0][0] == 0 and covered[-1][1] == n and all(a[1] == b[0] for a, b in zip(covered, covered[1:]))
+    for rank, ok, used, _ in results:
+        assert used == "head_tail" and ok, f"rank {rank}"
+
+
+def test_head_tail_bounds():
+    for n, world in [(1 << 30, 2), (1 << 30, 8), (100000, 3), (40, 2), (17, 4)]:
+        b = sharded.head_tail_bounds(n, world)
+        if b is None:
+            continue
+        head, chunk, tail = b
+        assert head == chunk // 2 and 0 <= tail <= chunk and head + (world - 1) * chunk + tail == n
+        assert head % 4 == 0 and chunk % 8 == 0
+    head, chunk, tail = sharded.head_tail_bounds(1 << 30, 2)
+    assert abs(chunk - (1 << 30) / 2.5) < 32 and abs(tail - chunk) < 32        # rank 0 owns 1.5 chunks, 8 B/element
+    assert sharded.head_tail_bounds(100, 1) is None and sharded.head_tail_bounds(3, 8) is None

@@ -501,10 +501,13 @@ def run_scan(args, world, rank, peaks, steps=None, warmup=None):
     warmup = warmup or args.warmup
     dev = torch.device("cuda", torch.cuda.current_device())
     n_total = (1 << args.scan_log2n) if args.scan_log2n else (SCAN_N1 if world == 1 else SCAN_NG)
-    # More than one GPU: rank 0 owns a head and a tail of the array (8 B/element there, 12 elsewhere, 1.5 chunks on
-    # rank 0) unless a schedule is asked for by name or the ranks have no peer-writable memory.
+    # Two to four GPUs: rank 0 owns a head and a tail of the array (8 B/element there, 12 elsewhere, 1.5 chunks on
+    # rank 0) unless a schedule is asked for by name or the ranks have no peer-writable memory.  Measured at 2^30:
+    # 2 GPUs 9.36 against 7.93 TB/s with equal chunks, 4 GPUs 16.4 against 15.6, 8 GPUs 28.9 against 29.8 (rank 0's
+    # three launches and the others' wait for its word outweigh the 6 % that the layout saves there), hence the limit.
     scan, head = None, 0
-    if world > 1 and args.scan_schedule in (None, "head_tail") and sharded.head_tail_bounds(n_total, world) is not None:
+    want_head_tail = args.scan_schedule == "head_tail" or (args.scan_schedule is None and 2 <= world <= 4)
+    if world > 1 and want_head_tail and sharded.head_tail_bounds(n_total, world) is not None:
         pieces = sharded.head_tail_pieces(n_total, world, rank)
         n = sum(b - a for a, b in pieces)
         head = pieces[0][1] - pieces[0][0] if rank == 0 else 0
@@ -760,7 +763,7 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=["gemm_bf16", "sgemm", "scan"], default="gemm_bf16")
     ap.add_argument("--scan-schedule", choices=["head_tail", "peer_words", "reduce_then_scan", "scan_then_carry"], default=None,
-                    help="sharded scan schedule (default on more than one GPU: head_tail, else peer_words, where the ranks can write each other's memory)")
+                    help="sharded scan schedule (default: head_tail on 2 to 4 GPUs, peer_words on more, where the ranks can write each other's memory)")
     ap.add_argument("--size", type=int, default=0,
                     help="square GEMM size for --workload gemm_bf16/sgemm (default 8192 / 4096); smaller sizes are for profiling")
     ap.add_argument("--scan-log2n", type=int, default=0, help="scan length 2^k (default: 28 on one GPU, 30 sharded)")

@@ -245,14 +245,14 @@ def _head_tail_worker(rank, world, port, n, high, q):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("n,high", [(100000, 16), (4099, 0xFFFFFFFF), (40, 3)])
-def test_head_tail_schedule_two_ranks(n, high):
-    """Rank 0 owns the head and the tail of the array and never adds its pieces up first; rank 1 the chunk between
-    them.  The pieces cover the array, and every piece equals the scan of the whole array on its range."""
+@pytest.mark.parametrize("world,n,high", [(2, 100000, 16), (2, 4099, 0xFFFFFFFF), (2, 40, 3), (3, 70001, 1 << 20)])
+def test_head_tail_schedule(world, n, high):
+    """Rank 0 owns the head and the tail of the array and never adds its pieces up first; the other ranks the chunks
+    between them.  The pieces cover the array, and every piece equals the scan of the whole array on its range."""
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_head_tail_worker, args=(r, 2, port, n, high, q)) for r in range(2)]
+    procs = [ctx.Process(target=_head_tail_worker, args=(r, world, port, n, high, q)) for r in range(world)]
     for p in procs:
         p.start()
     results = [q.get(timeout=120) for _ in procs]
